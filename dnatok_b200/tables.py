@@ -1,0 +1,358 @@
+"""Turn a Hugging Face tokenizer into the flat integer tables the CUDA kernels read.
+
+This is the counterpart of the reference's one-time discovery step: ``DNATok.discover``
+(reference ``src/dna_tokenizer.py:864-1110``) probes the wrapped tokenizer and builds an ASCII
+LUT (``:633-653``), a k-mer LUT (``_discover_kmer_structure`` ``:655-741``, ``_build_kmer_lut``
+``:743-822``) or hands the tokenizer to ``GPUTokBPEBackend`` (``src/gputok_bpe_backend.py:412-474``),
+which reads ``tokenizer.json`` (``:132-176``), checks the model / pre-tokenizer / normalizer
+(``:265-295``) and extracts the merges in rank order (``:251-262``).
+
+Differences by design: BPE tables are built directly in HF id space (the reference keeps a
+kernel-id -> HF-id remap, ``:447-466``), and a k-mer vocabulary is stored as a ``4**k`` table of
+clean windows plus a single-character table, which is only accepted when probing shows that the
+tokenizer really expands every other window character by character.
+
+Nothing here computes token ids for user input; tables only.
+"""
+from __future__ import annotations
+
+import itertools
+import json
+import re as _re
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import numpy as np
+
+
+class UnsupportedTokenizer(RuntimeError):
+    """The tokenizer cannot be expressed as char / k-mer / BPE tables; there is no CPU fallback."""
+
+
+@dataclass
+class Specials:
+    pad_id: int = 0
+    unk_id: int = 0
+    cls_id: int = -1          # id emitted before the sequence when add_special_tokens, -1: none
+    sep_id: int = -1          # id emitted after the sequence, -1: none
+    padding_side: str = "right"
+
+
+@dataclass
+class TokenizerSpec:
+    kind: str                                   # "char" | "kmer" | "bpe"
+    specials: Specials
+    vocab_size: int
+    lut256: np.ndarray                          # int32[256]: byte -> id (char), single ids (kmer), initial symbols (bpe)
+    k: int = 0
+    kmer_ids: Optional[np.ndarray] = None       # int32[4**k], itertools.product("ACGT", k) order
+    merge_a: Optional[np.ndarray] = None        # int32[n_merges] left operand id, rank order
+    merge_b: Optional[np.ndarray] = None
+    merge_out: Optional[np.ndarray] = None
+    normalizer: Optional[Callable[[str], str]] = None
+    vocab: Dict[str, int] = field(default_factory=dict)
+
+
+# --------------------------------------------------------------------------- normalizer
+# Same accepted steps and same semantics as the reference's compiler
+# (src/gputok_bpe_backend.py:179-248); its known answers are in
+# tests/test_gputok_bpe_backend.py:319-425 of the reference.
+
+def compile_normalizer_step(step: Any) -> Optional[Callable[[str], str]]:
+    if not isinstance(step, dict):
+        return None
+    t = step.get("type")
+    if t == "Strip":
+        left, right = bool(step.get("strip_left", True)), bool(step.get("strip_right", True))
+        if left and right:
+            return str.strip
+        if left:
+            return str.lstrip
+        if right:
+            return str.rstrip
+        return lambda s: s
+    if t == "Replace":
+        pat, content = step.get("pattern"), str(step.get("content", ""))
+        if isinstance(pat, dict) and "String" in pat:
+            lit = pat["String"]
+            return lambda s: s.replace(lit, content)
+        if isinstance(pat, dict) and "Regex" in pat:
+            rx = _re.compile(pat["Regex"])
+            return lambda s: rx.sub(content, s)
+        return None
+    if t == "Prepend":
+        pre = str(step.get("prepend", ""))
+        return lambda s: pre + s
+    if t in (None, "NFC", "NFKC", "NFD", "NFKD", "StripAccents"):
+        return lambda s: s                      # identity on ASCII DNA
+    if t == "Lowercase":
+        return str.lower
+    if t == "Sequence":
+        fns = [compile_normalizer_step(x) for x in step.get("normalizers", [])]
+        if any(f is None for f in fns):
+            return None
+
+        def run(s: str) -> str:
+            for f in fns:
+                s = f(s)
+            return s
+        return run
+    return None
+
+
+def compile_normalizer(cfg: Dict[str, Any]) -> Optional[Callable[[str], str]]:
+    norm = cfg.get("normalizer")
+    if norm is None:
+        return None
+    fn = compile_normalizer_step(norm)
+    if fn is None:
+        raise ValueError("Unsupported normalizer config: %r" % (norm.get("type"),))
+    return fn
+
+
+# --------------------------------------------------------------------------- tokenizer.json
+
+def read_tokenizer_json(tok: Any) -> Optional[Dict[str, Any]]:
+    """tokenizer.json of a fast tokenizer: from its backend object, else from a local path."""
+    import os
+    backend = getattr(tok, "backend_tokenizer", None) or (tok if hasattr(tok, "to_str") else None)
+    to_str = getattr(backend, "to_str", None)
+    if callable(to_str):
+        try:
+            return json.loads(to_str())
+        except Exception:
+            pass
+    for attr in ("name_or_path", "vocab_file"):
+        v = getattr(tok, attr, None)
+        if isinstance(v, str) and v:
+            for cand in (os.path.join(v, "tokenizer.json"), v):
+                if os.path.isfile(cand) and cand.endswith("tokenizer.json"):
+                    with open(cand) as f:
+                        return json.load(f)
+    return None
+
+
+def supported_bpe(cfg: Optional[Dict[str, Any]]) -> Tuple[bool, str]:
+    """Acceptance rule of the reference (src/gputok_bpe_backend.py:265-295) plus the model
+    options this engine does not implement."""
+    if cfg is None:
+        return False, "tokenizer.json not found"
+    model = cfg.get("model") or {}
+    if model.get("type") != "BPE":
+        return False, "model.type=%r (only BPE supported)" % (model.get("type"),)
+    pre = cfg.get("pre_tokenizer")
+    if pre is not None:
+        pt = pre.get("type") if isinstance(pre, dict) else None
+        if pt not in (None, "Whitespace", "Split", "WhitespaceSplit"):
+            return False, "pre_tokenizer=%r" % (pt,)
+    norm = cfg.get("normalizer")
+    if norm is not None and compile_normalizer_step(norm) is None:
+        return False, "unsupported normalizer=%r" % (norm.get("type"),)
+    for opt in ("dropout", "continuing_subword_prefix", "end_of_word_suffix"):
+        if model.get(opt):
+            return False, "model.%s is set" % opt
+    for opt in ("fuse_unk", "byte_fallback", "ignore_merges"):
+        if model.get(opt):
+            return False, "model.%s is set" % opt
+    return True, "ok"
+
+
+def extract_merges(cfg: Dict[str, Any]) -> List[Tuple[str, str]]:
+    out = []
+    for m in cfg.get("model", {}).get("merges", []):
+        if isinstance(m, str):
+            a, b = m.split(" ")
+        elif isinstance(m, (list, tuple)) and len(m) == 2:
+            a, b = m
+        else:
+            raise ValueError("Unrecognised merge entry: %r" % (m,))
+        out.append((a, b))
+    return out
+
+
+def _template_specials(cfg: Dict[str, Any]) -> Tuple[int, int]:
+    """(cls_id, sep_id) of a ``TemplateProcessing`` of the form ``[X] $A [Y]`` (either may be absent)."""
+    post = cfg.get("post_processor")
+    if post is None:
+        return -1, -1
+    if post.get("type") != "TemplateProcessing":
+        raise UnsupportedTokenizer("post_processor=%r" % (post.get("type"),))
+    ids = {k: v["ids"] for k, v in post.get("special_tokens", {}).items()}
+    before, after, seen = [], [], False
+    for piece in post.get("single", []):
+        if "Sequence" in piece:
+            seen = True
+        else:
+            name = piece["SpecialToken"]["id"]
+            (after if seen else before).extend(ids[name])
+    if len(before) > 1 or len(after) > 1:
+        raise UnsupportedTokenizer("more than one special token on a side")
+    return (before[0] if before else -1), (after[0] if after else -1)
+
+
+def bpe_spec_from_json(cfg: Dict[str, Any], *, pad_id: Optional[int] = None,
+                       padding_side: str = "right") -> TokenizerSpec:
+    ok, why = supported_bpe(cfg)
+    if not ok:
+        raise UnsupportedTokenizer("cannot accelerate this tokenizer: " + why)
+    model = cfg["model"]
+    vocab: Dict[str, int] = model["vocab"]
+    merges = extract_merges(cfg)
+    if not merges:
+        raise UnsupportedTokenizer("tokenizer has no merges")
+    unk = model.get("unk_token")
+    unk_id = vocab.get(unk, -1) if unk is not None else -1
+    if unk_id < 0:
+        raise UnsupportedTokenizer("BPE model without an unk token: characters outside the "
+                                   "alphabet would be dropped, which this engine does not do")
+    n = len(merges)
+    a = np.empty(n, np.int32)
+    b = np.empty(n, np.int32)
+    o = np.empty(n, np.int32)
+    for r, (x, y) in enumerate(merges):
+        try:
+            a[r], b[r], o[r] = vocab[x], vocab[y], vocab[x + y]
+        except KeyError as e:
+            raise UnsupportedTokenizer("merge %d names a token missing from the vocab: %s" % (r, e))
+    lut = np.full(256, unk_id, np.int32)
+    for tok_str, i in vocab.items():
+        if len(tok_str) == 1 and ord(tok_str) < 128:
+            lut[ord(tok_str)] = i
+    for added in cfg.get("added_tokens", []):
+        c = added.get("content", "")
+        if len(c) == 1 and ord(c) < 128:
+            raise UnsupportedTokenizer("single-character added token %r" % c)
+    cls_id, sep_id = _template_specials(cfg)
+    if pad_id is None:
+        pad_id = vocab.get("[PAD]", vocab.get("<pad>", 0))
+    vs = max(max(vocab.values()) + 1, max((t["id"] for t in cfg.get("added_tokens", [])), default=-1) + 1)
+    return TokenizerSpec("bpe", Specials(pad_id, unk_id, cls_id, sep_id, padding_side), vs, lut,
+                         merge_a=a, merge_b=b, merge_out=o, normalizer=compile_normalizer(cfg),
+                         vocab=dict(vocab))
+
+
+# --------------------------------------------------------------------------- probing (char / k-mer)
+
+def _ids(tok: Any, texts: List[str]) -> List[List[int]]:
+    enc = tok(texts, add_special_tokens=False)
+    return [list(map(int, r)) for r in enc["input_ids"]]
+
+
+def _probe_specials(tok: Any) -> Tuple[int, int]:
+    plain = _ids(tok, ["A"])[0]
+    full = list(map(int, tok(["A"], add_special_tokens=True)["input_ids"][0]))
+    if full == plain:
+        return -1, -1
+    n = len(plain)
+    for lead in range(len(full) - n + 1):
+        if full[lead:lead + n] == plain:
+            before, after = full[:lead], full[lead + n:]
+            if len(before) <= 1 and len(after) <= 1:
+                return (before[0] if before else -1), (after[0] if after else -1)
+    raise UnsupportedTokenizer("special-token layout is not [X] seq [Y]")
+
+
+def _printable_ascii() -> List[int]:
+    return [c for c in range(33, 127)]
+
+
+def detect_kmer(tok: Any) -> int:
+    """k of a non-overlapping k-mer tokenizer, 0 if it is not one (rule of the reference:
+    ``"A"*24`` must give 24/k tokens for k in 2..8, likewise C, G, T and a mixed string)."""
+    try:
+        n = len(_ids(tok, ["A" * 24])[0])
+    except Exception:
+        return 0
+    if n == 0 or 24 % n or not 2 <= 24 // n <= 8:
+        return 0
+    k = 24 // n
+    probes = ["C" * 24, "G" * 24, "T" * 24, ("ACGT" * 6)]
+    return k if all(len(r) == n for r in _ids(tok, probes)) else 0
+
+
+def spec_from_probing(tok: Any) -> TokenizerSpec:
+    """Char or k-mer tables by asking the tokenizer, as the reference's discovery does."""
+    pad_id = int(getattr(tok, "pad_token_id", 0) or 0)
+    unk_id = getattr(tok, "unk_token_id", None)
+    unk_id = int(unk_id) if unk_id is not None else 0
+    side = getattr(tok, "padding_side", "right")
+    cls_id, sep_id = _probe_specials(tok)
+    try:
+        vocab = dict(tok.get_vocab())
+    except Exception:
+        vocab = {}
+    vs = max(int(getattr(tok, "vocab_size", 0) or 0), (max(vocab.values()) + 1) if vocab else 0)
+    sp = Specials(pad_id, unk_id, cls_id, sep_id, side)
+
+    singles = np.full(256, unk_id, np.int32)
+    chars = [c for c in range(1, 128) if not chr(c).isspace()]
+    got = _ids(tok, [chr(c) for c in chars])
+    for c, r in zip(chars, got):
+        if len(r) != 1:
+            if chr(c) in "ACGTNacgtn":
+                raise UnsupportedTokenizer("character %r gives %d tokens" % (chr(c), len(r)))
+            continue
+        singles[c] = r[0]
+    # bytes >= 128 and whitespace are outside the supported input domain; they read as unk.
+
+    k = detect_kmer(tok)
+    if k == 0:
+        # one token per character, and the id must not depend on position (the reference
+        # keeps a second "continuation" LUT for tokenizers where it does; not supported here).
+        probes = ["ACGTACGT", "NNACGTNN", "acgtnACG", "TTTTTTTT", "AN", "NA", "Xx"]
+        for p, r in zip(probes, _ids(tok, probes)):
+            if r != [int(singles[ord(ch)]) for ch in p]:
+                raise UnsupportedTokenizer("not a position-independent per-character tokenizer (probe %r)" % p)
+        return TokenizerSpec("char", sp, vs, singles, vocab=vocab)
+
+    clean = ["".join(t) for t in itertools.product("ACGT", repeat=k)]
+    kmer_ids = np.empty(4 ** k, np.int32)
+    for lo in range(0, len(clean), 4096):
+        for j, r in enumerate(_ids(tok, clean[lo:lo + 4096])):
+            if len(r) != 1:
+                raise UnsupportedTokenizer("k-mer %r gives %d tokens" % (clean[lo + j], len(r)))
+            kmer_ids[lo + j] = r[0]
+    # Every window holding a non-ACGT character must expand character by character, and the
+    # frame must stay aligned after it; check all 5**k windows over ACGTN (as the reference
+    # tabulates them) followed by a clean window, plus tails and lower case.
+    dirty = ["".join(t) for t in itertools.product("ACGTN", repeat=k) if "N" in t]
+    tail = "ACGTAC"[:k - 1] if k > 1 else ""
+    probes = [d + clean[(7 * i) % len(clean)] + tail for i, d in enumerate(dirty)]
+    probes += [clean[5] + "acgtn"[:k - 1], "a" + clean[9][1:] + clean[3], clean[1][:k - 1], "N" * (2 * k + 1)]
+    for lo in range(0, len(probes), 4096):
+        chunk = probes[lo:lo + 4096]
+        for p, r in zip(chunk, _ids(tok, chunk)):
+            if r != expected_kmer_ids(p, k, kmer_ids, singles):
+                raise UnsupportedTokenizer("k-mer tokenizer is not window-aligned with single-character "
+                                           "fallback (probe %r)" % p)
+    return TokenizerSpec("kmer", sp, vs, singles, k=k, kmer_ids=kmer_ids, vocab=vocab)
+
+
+def expected_kmer_ids(s: str, k: int, kmer_ids: np.ndarray, singles: np.ndarray) -> List[int]:
+    """Table semantics spelled out (used only to validate a probed table)."""
+    code = {"A": 0, "C": 1, "G": 2, "T": 3}
+    out: List[int] = []
+    for w in range(0, len(s), k):
+        win = s[w:w + k]
+        if len(win) == k and all(ch in code for ch in win):
+            idx = 0
+            for ch in win:
+                idx = idx * 4 + code[ch]
+            out.append(int(kmer_ids[idx]))
+        else:
+            out.extend(int(singles[ord(ch)]) for ch in win)
+    return out
+
+
+def spec_from_tokenizer(tok: Any) -> TokenizerSpec:
+    """Pick the path the way the reference does: BPE by its tokenizer.json, else probe."""
+    cfg = read_tokenizer_json(tok)
+    if cfg is not None and (cfg.get("model") or {}).get("type") == "BPE":
+        pad = getattr(tok, "pad_token_id", None)
+        spec = bpe_spec_from_json(cfg, pad_id=int(pad) if pad is not None else None,
+                                  padding_side=getattr(tok, "padding_side", "right"))
+        u = getattr(tok, "unk_token_id", None)
+        if u is not None and int(u) != spec.specials.unk_id:
+            raise UnsupportedTokenizer("unk id mismatch between tokenizer and tokenizer.json")
+        return spec
+    return spec_from_probing(tok)
