@@ -1,0 +1,528 @@
+#!/usr/bin/env python
+"""Benchmark of the tokenisation hot path: Mbp/s encoded, bit-exact vs Hugging Face.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload kmer6|char|byte|bpe4k|bpe32k] [--scale S] [--no-extra]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic DNA.  The headline
+workload is benchmark shape 2 (non-overlapping 6-mers, rows of 6,000 bp, right-padded to 1,000
+tokens, int64 ids + int64 mask) scaled to 32,768 rows so that a step moves ~0.7 GB, far more
+than the 126 MB L2.  ``value`` is measured with inputs resident in HBM (CUDA events on the
+launching stream); ``e2e`` goes through ``dnatok_encode_host`` with pinned HOST buffers, so both
+PCIe copies are inside the timed region.  ``per_config`` carries the other four shapes, each at
+its literal size (launch-latency bound) and at a scaled size.
+
+Multi-GPU (launched with torch.distributed.run): rows are sharded by sequence, every rank encodes
+its own shard on its own GPU with no collective in the timed region (weak scaling: the per-GPU
+shard has the single-GPU size); rank 0 prints max-over-ranks timing.
+
+``--impl reference`` times the CPU side of the same workload on a bounded sample: the C
+restatement in ``oracle/`` on all host threads (the line's value) and the live Hugging Face
+``tokenizers`` call next to it.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from dnatok_b200 import synth  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+# ----------------------------------------------------------------------------- workloads
+
+def fixture_json(name):
+    import gzip
+    with gzip.open(os.path.join(ROOT, "tests", "golden", name + ".tokenizer.json.gz"), "rt") as f:
+        return json.load(f)
+
+
+def spec_for(kind):
+    """Tables for the five shapes without touching Hugging Face (the product path)."""
+    import itertools
+    from dnatok_b200.tables import Specials, TokenizerSpec, bpe_spec_from_json
+    if kind == "char":
+        lut = np.full(256, 1, np.int32)
+        for i, c in enumerate("ACGTN"):
+            lut[ord(c)] = 5 + i
+        return TokenizerSpec("char", Specials(0, 1, 2, 3), 10, lut)
+    if kind == "byte":
+        return TokenizerSpec("char", Specials(1, 0, -1, -1), 512, np.arange(256, dtype=np.int32))
+    if kind == "kmer6":
+        lut = np.full(256, 1, np.int32)
+        for i, c in enumerate("ACGTN"):
+            lut[ord(c)] = 4101 + i
+        return TokenizerSpec("kmer", Specials(0, 1, -1, -1), 4106, lut, k=6,
+                             kmer_ids=np.arange(5, 5 + 4096, dtype=np.int32))
+    if kind == "bpe4k":
+        return bpe_spec_from_json(fixture_json("bpe4096"))
+    if kind == "bpe32k":
+        return bpe_spec_from_json(fixture_json("bpe32000"))
+    raise KeyError(kind)
+
+
+def make_workload(kind, scale, seed_shift=0):
+    """(flat uint8, offsets int64, call kwargs, description)."""
+    if kind == "kmer6":
+        rows = 256 * scale
+        a = synth.config2(batch=rows, seed=synth.seed_for(2) + seed_shift)
+        f, o = synth.pack_rows(a)
+        return f, o, dict(padding="max_length", max_length=1000, truncation=True, add_special_tokens=False), \
+            "cfg2 6-mer, %d x 6000 bp, pad to 1000, int64 ids+mask" % rows
+    if kind == "char":
+        rows = 64 * scale
+        f, o = synth.pack_rows(synth.config1(batch=rows, seed=synth.seed_for(1) + seed_shift))
+        return f, o, dict(padding="longest"), "cfg1 char, %d x 1024 bp, [CLS]..[SEP], int64 ids+mask" % rows
+    if kind == "byte":
+        rows = 8 * scale
+        f, o = synth.pack_rows(synth.config4(batch=rows, seed=synth.seed_for(4) + seed_shift))
+        return f, o, dict(padding="longest", ids_dtype="int32", return_attention_mask=False), \
+            "cfg4 byte-level, %d x 1048576 bp, int32 ids" % rows
+    if kind == "bpe4k":
+        rows = 1024 * scale
+        f, o = synth.pack_rows(synth.config3(batch=rows, seed=synth.seed_for(3) + seed_shift))
+        return f, o, dict(padding="longest"), "cfg3 BPE vocab 4096, %d x 1024 bp, [CLS]..[SEP], pad to longest" % rows
+    if kind == "bpe32k":
+        f, o = synth.config5(n_reads=16384, seed=None if seed_shift == 0 else synth.seed_for(5) + seed_shift)
+        if scale > 1:
+            lens = np.diff(o)
+            f = np.tile(f, scale)
+            o = np.concatenate([[0], np.cumsum(np.tile(lens, scale))]).astype(np.int64)
+        return f, o, dict(padding=False), "cfg5 BPE vocab 32000, %d reads 150..10000 bp, ragged ids" % (16384 * scale)
+    raise KeyError(kind)
+
+
+def algorithmic_bytes(total_in, n_rows, enc, ragged):
+    """Input ASCII + (ragged only) offsets + every element of the returned ids / mask tensors."""
+    b = int(total_in)
+    if ragged:
+        b += 8 * (n_rows + 1)
+    for k in ("input_ids", "attention_mask"):
+        if k in enc:
+            b += enc[k].numel() * enc[k].element_size()
+    return b
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with NVML while the timed region runs (read only)."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            pass
+
+    def _names(self, bits):
+        nv = self.nv
+        table = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        return [k for k, v in table.items() if bits & v]
+
+    def _one(self):
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            get = getattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                self.nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.reasons.update(self._names(get(self.h)))
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._one()
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.ok:
+            self.t = threading.Thread(target=self._run, daemon=True)
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        if self.ok:
+            self._one()
+            self._stop.set()
+            self.t.join()
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def torch_dtype(name):
+    import torch
+    return getattr(torch, name)
+
+
+def device_kwargs(call):
+    kw = dict(call)
+    if "ids_dtype" in kw:
+        kw["ids_dtype"] = torch_dtype(kw["ids_dtype"])
+    return kw
+
+
+def time_device(tok, d_bytes, d_off, offsets, call, steps, warmup, barrier=None):
+    """CUDA-event timing of ``steps`` encodes with inputs resident on the device.  Outputs and scratch
+    are allocated once (first warm-up) and reused, so the timed region launches kernels only."""
+    import torch
+    from dnatok_b200 import _cabi
+    kw = device_kwargs(call)
+    ragged = kw.get("padding") is False
+    enc = tok.encode_device(d_bytes, d_off, host_offsets=offsets, **kw)          # sizes + correctness of the call
+    out = {k: enc[k] for k in ("input_ids", "attention_mask") if k in enc}
+    need = _cabi.lib().dnatok_scratch_bytes(tok.handle.ptr, len(offsets) - 1, int(d_bytes.shape[0]))
+    scratch = torch.empty(max(need, 1), dtype=torch.uint8, device=d_bytes.device)
+    if not ragged and kw.get("padding") == "longest":
+        # the stride is known now; later steps use it directly so no host sync sits in the loop
+        kw = dict(kw, padding="max_length", max_length=int(enc["input_ids"].shape[1]))
+    run = lambda: tok.encode_device(d_bytes, d_off, host_offsets=offsets, out=out, scratch=scratch, check=False, **kw)
+    if ragged:
+        run = make_ragged_runner(tok, d_bytes, d_off, offsets, kw, scratch, enc)
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    l0 = _cabi.lib().dnatok_launch_count()
+    for a, b in ev:
+        a.record()
+        run()
+        b.record()
+    torch.cuda.synchronize()
+    launches = _cabi.lib().dnatok_launch_count() - l0
+    if barrier:
+        barrier()
+    per = np.array([a.elapsed_time(b) for a, b in ev])
+    total_ms = ev[0][0].elapsed_time(ev[-1][1])
+    return enc, per, total_ms, launches
+
+
+def make_ragged_runner(tok, d_bytes, d_off, offsets, kw, scratch, enc):
+    """Ragged output with preallocated buffers through the C ABI directly (no host sync per step)."""
+    import torch
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    B = len(offsets) - 1
+    total = int(d_bytes.shape[0])
+    fmt = tok._format(id_bits=64, mask_bits=0, add_special=kw.get("add_special_tokens", True), max_tokens=0, out_stride=0)
+    bound = L.dnatok_max_tokens(tok.handle.ptr, B, total, ctypes.byref(fmt))
+    ids = torch.empty(bound, dtype=torch.int64, device=d_bytes.device)
+    out_off = torch.empty(B + 1, dtype=torch.int64, device=d_bytes.device)
+    lengths = torch.empty(B, dtype=torch.int32, device=d_bytes.device)
+    status = torch.empty(B, dtype=torch.int32, device=d_bytes.device)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+
+    def run():
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _cabi.check(L.dnatok_encode(tok.handle.ptr, p(d_bytes), p(d_off), B, total, ctypes.byref(fmt), p(ids), None,
+                                    p(lengths), p(out_off), p(status), p(scratch), int(scratch.numel()), stream))
+    return run
+
+
+def time_e2e(tok, flat, offsets, call, steps, warmup):
+    """Host buffers in, host buffers out, through dnatok_encode_host; wall clock (the call returns
+    when the results are in host memory)."""
+    import torch
+    kw = dict(call)
+    ids_dt = np.dtype(kw.pop("ids_dtype", "int64"))
+    pin = lambda a: torch.from_numpy(a).pin_memory().numpy()
+    flat_p, off_p = pin(np.ascontiguousarray(flat)), pin(offsets)
+    first = tok.encode_host((flat_p, off_p), ids_dtype=ids_dt, **kw)
+    n_ids = first["input_ids"].size
+    out_ids = torch.empty(max(n_ids, 1) if kw.get("padding") is not False else int(offsets[-1]) + 2 * len(offsets),
+                          dtype=torch_dtype(ids_dt.name)).pin_memory().numpy()
+    out_mask = torch.empty(max(n_ids, 1), dtype=torch.int64).pin_memory().numpy() if "attention_mask" in first else None
+    for _ in range(max(warmup - 1, 0)):
+        tok.encode_host((flat_p, off_p), ids_dtype=ids_dt, out_ids=out_ids, out_mask=out_mask, **kw)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        r = tok.encode_host((flat_p, off_p), ids_dtype=ids_dt, out_ids=out_ids, out_mask=out_mask, **kw)
+    dt = time.perf_counter() - t0
+    h2d = flat.nbytes + offsets.nbytes
+    d2h = r["input_ids"].nbytes + (r["attention_mask"].nbytes if "attention_mask" in r else 0) + 8 * (len(offsets) - 1)
+    if "offsets" in r:
+        d2h += r["offsets"].nbytes
+    return dt / steps, h2d, d2h
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def run_ours(args):
+    import torch
+    from dnatok_b200.tokenizer import B200Tokenizer
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the encode path has no CPU fallback")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    barrier = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())
+
+    peak, peak_src = peaks()
+    kind = args.workload
+    scale = args.scale or {"kmer6": 128, "char": 1024, "byte": 16, "bpe4k": 64, "bpe32k": 2}[kind]
+    tok = B200Tokenizer(spec_for(kind), device=local)
+    flat, offsets, call, desc = make_workload(kind, scale, seed_shift=7919 * rank)
+    d_bytes = torch.from_numpy(flat).cuda()
+    d_off = torch.from_numpy(offsets).cuda()
+    total_bp = int(offsets[-1])
+
+    with ClockSampler(local) as clk:
+        enc, per, total_ms, launches = time_device(tok, d_bytes, d_off, offsets, call, args.steps, args.warmup, barrier)
+    ragged = call.get("padding") is False
+    abytes = algorithmic_bytes(total_bp, len(offsets) - 1, enc, ragged)
+
+    # end to end through the host-buffer entry point (rank-local; max over ranks below)
+    e2e_s, h2d, d2h = time_e2e(tok, flat, offsets, call, max(3, min(args.steps, 10)), 2)
+
+    t = torch.tensor([total_ms, e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_s = float(t[0]), float(t[1])
+    ms_per_step = total_ms / args.steps
+    value = world * total_bp / (ms_per_step * 1e-3) / 1e6
+    kernel_ms = float(np.mean(per))
+    achieved = abytes / (kernel_ms * 1e-3) / 1e9
+
+    line = {
+        "metric": "Mbp/s encoded (bit-exact vs HF)", "value": round(value, 1), "unit": "Mbp/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8->int64",
+        "data": "synthetic (seeded; stands in for genomic reads and the NT-v2 tokenizer)",
+        "config": {"workload": desc, "rows_per_gpu": len(offsets) - 1, "bp_per_gpu": total_bp,
+                   "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" % (abytes / 1e6)
+                   if abytes > 2 * L2_BYTES else "working set fits L2",
+                   "sharding": "by sequence, no collective in the timed region"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "kernel": {"kmer6": "kmer_rows_kernel", "char": "emit_padded_kernel", "byte": "emit_padded_kernel",
+                                "bpe4k": "bpe_merge_kernel", "bpe32k": "bpe_merge_kernel"}[kind],
+                     "algorithmic_bytes_per_launch": abytes, "kernel_ms": round(kernel_ms, 5)},
+        "e2e": {"value": round(world * total_bp / e2e_s / 1e6, 1), "unit": "Mbp/s",
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "path": "dnatok_encode_host, pinned host buffers"},
+        "gpu_launches": int(launches), "clocks": clk.summary(),
+    }
+    if rank == 0 and world == 1:
+        line["roofline"]["traffic"] = TRAFFIC.get(kind)
+        line["cpu_baseline"] = cpu_baseline(kind, 1)
+        if not args.no_extra:
+            line["per_config"] = per_config(local, peak, args)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+# dram bytes per launch of the dominant kernel from the committed ncu summaries (profiles/), scaled to
+# the default workload where the capture ran on a smaller case; None until a capture exists.
+TRAFFIC = {}
+
+
+def per_config(local, peak, args):
+    """The other shapes: literal size (latency bound, many launches timed) and a scaled size."""
+    import torch
+    from dnatok_b200.tokenizer import B200Tokenizer
+    out = {}
+    plan = [("char", 1, 1024), ("kmer6", 1, None), ("bpe4k", 1, 32), ("byte", 1, 16), ("bpe32k", 1, None)]
+    for kind, lit, big in plan:
+        tok = B200Tokenizer(spec_for(kind), device=local)
+        for label, sc in (("literal", lit), ("scaled", big)):
+            if sc is None or (kind == args.workload and label == "scaled"):
+                continue
+            flat, offsets, call, desc = make_workload(kind, sc)
+            d_bytes, d_off = torch.from_numpy(flat).cuda(), torch.from_numpy(offsets).cuda()
+            steps = 50 if label == "literal" else 10
+            enc, per, total_ms, launches = time_device(tok, d_bytes, d_off, offsets, call, steps, 3)
+            ragged = call.get("padding") is False
+            if ragged:
+                n_tok = int(enc["offsets"][-1].item())
+                ab = int(offsets[-1]) + 8 * len(offsets) + 8 * n_tok
+            else:
+                ab = algorithmic_bytes(int(offsets[-1]), len(offsets) - 1, enc, False)
+            ms = total_ms / steps
+            out["%s/%s" % (kind, label)] = {
+                "workload": desc, "ms_per_step": round(ms, 5), "Mbp/s": round(int(offsets[-1]) / ms / 1e3, 1),
+                "algorithmic_GB/s": round(ab / ms / 1e6, 1), "frac_of_hbm_peak": round(ab / ms / 1e6 / peak, 4),
+                "launches_per_step": launches // steps}
+            del d_bytes, d_off, enc
+            torch.cuda.empty_cache()
+    return out
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_sample(kind):
+    """A bounded sample of the workload: ~10-30 s of CPU work in total."""
+    scale = {"kmer6": 64, "char": 64, "byte": 1, "bpe4k": 16, "bpe32k": 1}[kind]
+    flat, offsets, call, desc = make_workload(kind, scale)
+    if kind == "bpe32k":
+        n = 4096
+        flat, offsets = flat[:offsets[n]], offsets[:n + 1].copy()
+        desc = "first 4096 reads of cfg5"
+    return flat, offsets, call, desc
+
+
+def cpu_baseline(kind, reps=1):
+    """The C restatement (oracle/, all host threads) and live Hugging Face tokenizers on a bounded
+    sample of the same workload, on this box's host cores."""
+    from oracle import oracle as orc
+    from dnatok_b200.tables import TokenizerSpec
+    flat, offsets, call, desc = cpu_sample(kind)
+    spec = spec_for(kind)
+    threads = os.cpu_count() or 1
+    table = orc.BpeTable(spec.merge_a, spec.merge_b, spec.merge_out) if spec.kind == "bpe" else None
+    pad = call.get("padding")
+    best = None
+    for _ in range(1 + reps):
+        t0 = time.perf_counter()
+        ids, counts = orc.encode_ragged(spec.kind, flat, offsets, lut256=spec.lut256, k=spec.k, kmer_ids=spec.kmer_ids,
+                                        table=table, threads=threads)
+        if pad is not False:     # the padded int64 ids + mask the GPU path also produces
+            sp = spec.specials
+            orc.assemble(orc.rows(ids, offsets, counts), pad_id=sp.pad_id, cls_id=sp.cls_id, sep_id=sp.sep_id,
+                         add_special=call.get("add_special_tokens", True), max_length=call.get("max_length", 0) or 0,
+                         truncation=call.get("truncation", False), padding=pad)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    res = {"value": round(int(offsets[-1]) / best / 1e6, 2), "unit": "Mbp/s", "cores": threads, "kind": "port",
+           "sample": "%s: %d rows, %.1f Mbp" % (desc, len(offsets) - 1, offsets[-1] / 1e6),
+           "what": "oracle/dnatok_oracle.c (pthreads) + numpy padding/mask assembly"}
+    res["hf_tokenizers"] = hf_baseline(kind, flat, offsets, call)
+    return res
+
+
+def hf_baseline(kind, flat, offsets, call):
+    """Live Hugging Face fast tokenizer on (a prefix of) the sample, default Rayon threading."""
+    try:
+        os.environ.setdefault("TOKENIZERS_PARALLELISM", "true")
+        from oracle import hf_oracle
+        import tokenizers
+        tok = {"char": hf_oracle.char_tokenizer, "kmer6": hf_oracle.kmer_tokenizer, "byte": hf_oracle.byte_tokenizer,
+               "bpe4k": lambda: hf_oracle.bpe_tokenizer("bpe4096"), "bpe32k": lambda: hf_oracle.bpe_tokenizer("bpe32000")}[kind]()
+        n_rows = len(offsets) - 1
+        budget_bp = {"char": 4e6, "byte": 4e6, "kmer6": 60e6, "bpe4k": 60e6, "bpe32k": 30e6}[kind]
+        n = int(min(n_rows, max(1, np.searchsorted(offsets, budget_bp))))
+        strs = synth.rows_to_strings(flat, offsets[:n + 1])
+        kw = {k: v for k, v in call.items() if k in ("padding", "max_length", "truncation", "add_special_tokens")}
+        if kw.get("padding") == "longest":
+            kw["padding"] = True
+        tok(strs[:8], **kw)
+        t0 = time.perf_counter()
+        tok(strs, return_tensors="np" if kw.get("padding") else None, **kw)
+        dt = time.perf_counter() - t0
+        return {"value": round(int(offsets[n]) / dt / 1e6, 2), "unit": "Mbp/s", "threads": os.cpu_count(),
+                "tokenizers": tokenizers.__version__, "sample_rows": n}
+    except Exception as e:                                   # the baseline is context, never fatal
+        return {"unavailable": "%s: %s" % (type(e).__name__, e)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind = args.workload
+    flat, offsets, call, desc = cpu_sample(kind)
+    base = None
+    times = []
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        b = cpu_baseline_once(kind, flat, offsets, call)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+        base = b
+    ms = 1e3 * float(np.mean(times))
+    value = int(offsets[-1]) / (ms * 1e-3) / 1e6
+    cpu = {"value": round(value, 2), "unit": "Mbp/s", "cores": os.cpu_count() or 1, "kind": "port",
+           "sample": "%s: %d rows, %.1f Mbp per step" % (desc, len(offsets) - 1, offsets[-1] / 1e6),
+           "what": "oracle/dnatok_oracle.c (pthreads) + numpy padding/mask assembly",
+           "hf_tokenizers": hf_baseline(kind, flat, offsets, call)}
+    print(json.dumps({
+        "impl": "reference", "metric": "Mbp/s encoded (bit-exact vs HF)", "value": round(value, 2), "unit": "Mbp/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8->int64", "data": "synthetic (seeded)",
+        "config": {"workload": desc, "note": "CPU arm runs a bounded sample of the GPU arm's workload per step"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": round(value, 2), "unit": "Mbp/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def cpu_baseline_once(kind, flat, offsets, call):
+    from oracle import oracle as orc
+    spec = spec_for(kind)
+    table = _TABLES.get(kind)
+    if spec.kind == "bpe" and table is None:
+        table = _TABLES[kind] = orc.BpeTable(spec.merge_a, spec.merge_b, spec.merge_out)
+    ids, counts = orc.encode_ragged(spec.kind, flat, offsets, lut256=spec.lut256, k=spec.k, kmer_ids=spec.kmer_ids,
+                                    table=table, threads=os.cpu_count() or 1)
+    pad = call.get("padding")
+    if pad is not False:
+        sp = spec.specials
+        return orc.assemble(orc.rows(ids, offsets, counts), pad_id=sp.pad_id, cls_id=sp.cls_id, sep_id=sp.sep_id,
+                            add_special=call.get("add_special_tokens", True), max_length=call.get("max_length", 0) or 0,
+                            truncation=call.get("truncation", False), padding=pad)
+    return ids, counts
+
+
+_TABLES = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="kmer6", choices=["kmer6", "char", "byte", "bpe4k", "bpe32k"])
+    ap.add_argument("--scale", type=int, default=0, help="batch multiplier over the literal shape (0: default)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per_config section")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

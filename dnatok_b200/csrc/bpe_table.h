@@ -1,0 +1,35 @@
+// Host-side construction of the BPE merge table the kernels read.
+//
+// The table is a perfect hash of the pair (left id, right id) by row displacement: every left
+// token `a` owns a row offset disp[a]; the pair (a, b) lives in slots[disp[a] + b], which holds
+// (a << 16) | rank.  A lookup is two dependent loads and an equality test, with no probing and
+// no false positives.  Ids are Hugging Face ids, so the kernels emit final ids with no remap.
+// (The reference keeps a cuco::static_map keyed by a 64-bit pair and remaps kernel ids to HF
+// ids afterwards: src/dnatok_bpe_kernel/dnatok_bpe.cu:123-132,761-791,822-837 and
+// src/gputok_bpe_backend.py:447-466.)
+#pragma once
+#include <stdint.h>
+#include <string>
+#include <vector>
+
+namespace dnatok {
+
+struct BpeHostTable {
+    std::vector<uint32_t> disp;        // [n_tokens]
+    std::vector<uint32_t> slots;       // [max disp + n_tokens], 0xFFFFFFFF when empty
+    std::vector<uint16_t> merge_out;   // [n_merges] id created by each rank
+    std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
+    uint32_t n_tokens = 0;
+    uint32_t n_merges = 0;
+    // True when every merge's operands are created by lower ranks (or are initial symbols).
+    // Then a pair that contains a freshly created token always ranks above the merge that
+    // created it, and all non-overlapping occurrences of the lowest rank can be merged in
+    // one pass.  Otherwise the kernel merges one occurrence per pass.
+    bool batch_safe = false;
+};
+
+// Returns 0, or a negative code with a message in *err.
+int build_bpe_table(const int32_t* merge_a, const int32_t* merge_b, const int32_t* merge_out,
+                    int32_t n_merges, const int32_t byte_ids[256], BpeHostTable* out, std::string* err);
+
+}  // namespace dnatok

@@ -1,0 +1,614 @@
+// C ABI of the library (see include/dnatok_b200.h): handles, table upload, format resolution,
+// kernel launches and the host-buffer pipeline.  No PyTorch, no allocation inside the device
+// entry points other than the one-time table upload per device.
+#include "../../include/dnatok_b200.h"
+
+#include <atomic>
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "bpe_kernel.cuh"
+#include "bpe_table.h"
+#include "emit_kernel.cuh"
+#include "kmer_kernel.cuh"
+
+using namespace dnatok;
+
+namespace {
+
+thread_local std::string g_err;
+std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t e_ = (expr);                                                                \
+        if (e_ != cudaSuccess) return fail(DNATOK_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+#define LAUNCH_CHECK(name)                                                                      \
+    do {                                                                                        \
+        ++g_launches;                                                                           \
+        cudaError_t e_ = cudaGetLastError();                                                    \
+        if (e_ != cudaSuccess) return fail(DNATOK_ERR_CUDA, "launch of %s: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+struct DeviceTables {
+    int32_t* lut256 = nullptr;       // char LUT / k-mer single ids
+    int32_t* kmer_ids = nullptr;
+    uint32_t* disp = nullptr;
+    uint32_t* slots = nullptr;
+    uint16_t* merge_out = nullptr;
+    uint16_t* byte_tok = nullptr;
+    int sm_count = 0;
+    // host-pipeline staging (grow only)
+    uint8_t* st_bytes = nullptr;  size_t st_bytes_cap = 0;
+    int64_t* st_offsets = nullptr; size_t st_offsets_cap = 0;
+    void* st_ids = nullptr;       size_t st_ids_cap = 0;
+    void* st_mask = nullptr;      size_t st_mask_cap = 0;
+    int32_t* st_lengths = nullptr; size_t st_rows_cap = 0;
+    int32_t* st_status = nullptr;
+    int64_t* st_out_offsets = nullptr;
+    void* st_scratch = nullptr;   size_t st_scratch_cap = 0;
+    cudaStream_t stream = nullptr;
+};
+
+}  // namespace
+
+struct dnatok_handle {
+    int kind = 0;
+    dnatok_specials sp{};
+    std::vector<int32_t> lut256;
+    int k = 0;
+    std::vector<int32_t> kmer_ids;
+    BpeHostTable bpe;
+    std::mutex mu;
+    std::map<int, DeviceTables> dev;
+};
+
+namespace {
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+template <typename T>
+int upload(T** dst, const std::vector<T>& src) {
+    CUDA_TRY(cudaMalloc((void**)dst, src.size() * sizeof(T)));
+    CUDA_TRY(cudaMemcpy(*dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+// Tables of the handle on the current device (uploaded on first use).
+int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(h->mu);
+    auto it = h->dev.find(dev);
+    if (it == h->dev.end()) {
+        DeviceTables d;
+        CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        int rc = upload(&d.lut256, h->lut256);
+        if (rc) return rc;
+        if (h->kind == DNATOK_KIND_KMER && (rc = upload(&d.kmer_ids, h->kmer_ids))) return rc;
+        if (h->kind == DNATOK_KIND_BPE) {
+            if ((rc = upload(&d.disp, h->bpe.disp))) return rc;
+            if ((rc = upload(&d.slots, h->bpe.slots))) return rc;
+            if ((rc = upload(&d.merge_out, h->bpe.merge_out))) return rc;
+            if ((rc = upload(&d.byte_tok, h->bpe.byte_tok))) return rc;
+        }
+        it = h->dev.emplace(dev, d).first;
+    }
+    *out = &it->second;
+    return 0;
+}
+
+int check_format(const dnatok_format* f, bool host) {
+    if (!f) return fail(DNATOK_ERR_INVALID, "format is NULL");
+    if (f->id_bits != 32 && f->id_bits != 64) return fail(DNATOK_ERR_INVALID, "id_bits must be 32 or 64");
+    if (f->mask_bits != 0 && f->mask_bits != 8 && f->mask_bits != 32 && f->mask_bits != 64)
+        return fail(DNATOK_ERR_INVALID, "mask_bits must be 0, 8, 32 or 64");
+    if (f->max_tokens < 0) return fail(DNATOK_ERR_INVALID, "max_tokens < 0");
+    if (f->out_stride < (host ? -1 : 0)) return fail(DNATOK_ERR_INVALID, "out_stride < 0");
+    return 0;
+}
+
+int n_special(const dnatok_handle* h, const dnatok_format* f) {
+    return f->add_special ? (h->sp.cls_id >= 0) + (h->sp.sep_id >= 0) : 0;
+}
+
+// stride: the padded width in effect (0 = ragged / not yet known).
+int resolve(const dnatok_handle* h, const dnatok_format* f, int64_t stride, RowFormat* r) {
+    const int ns = n_special(h, f);
+    r->out_stride = stride;
+    r->cls_id = f->add_special ? h->sp.cls_id : -1;
+    r->sep_id = f->add_special ? h->sp.sep_id : -1;
+    r->pad_id = h->sp.pad_id;
+    r->pad_left = f->pad_left ? 1 : 0;
+    r->mask_bits = f->mask_bits;
+    int64_t cap = INT64_MAX;
+    r->clip_is_error = 0;
+    if (f->max_tokens > 0) {
+        if (f->max_tokens < ns) return fail(DNATOK_ERR_INVALID, "max_tokens smaller than the special tokens");
+        cap = f->max_tokens - ns;
+    }
+    if (stride > 0) {
+        if (stride < ns) return fail(DNATOK_ERR_INVALID, "out_stride smaller than the special tokens");
+        if (stride - ns < cap) { cap = stride - ns; r->clip_is_error = 1; }
+    }
+    r->cap_content = cap;
+    return 0;
+}
+
+struct BpeScratch {
+    uint16_t* tokens;       // [total_bytes] merged tokens at the input offsets
+    int32_t* counts;        // [n_rows] content tokens per row
+    int32_t* class_count;   // [8]
+    int32_t* work;          // [8]
+    int32_t* class_list;    // [BPE_N_CLASSES * n_rows]
+    size_t bytes;
+};
+
+BpeScratch bpe_scratch_layout(void* base, int64_t n_rows, int64_t total_bytes) {
+    BpeScratch s;
+    size_t o = 0;
+    uint8_t* b = (uint8_t*)base;
+    s.tokens = (uint16_t*)(b + o);      o += align_up((size_t)total_bytes * 2 + 16, 256);
+    s.counts = (int32_t*)(b + o);       o += align_up((size_t)n_rows * 4 + 4, 256);
+    s.class_count = (int32_t*)(b + o);  o += 32;
+    s.work = (int32_t*)(b + o);         o += 32;
+    o = align_up(o, 256);
+    s.class_list = (int32_t*)(b + o);   o += align_up((size_t)n_rows * 4 * BPE_N_CLASSES + 4, 256);
+    s.bytes = o;
+    return s;
+}
+
+template <int C>
+int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, int cls, const uint8_t* bytes,
+                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status,
+                     cudaStream_t st) {
+    const int slot = bpe_slot_bytes(C);
+    int warps = (200 * 1024) / slot;
+    if (warps > 32) warps = 32;
+    if (warps < 1) warps = 1;
+    const size_t smem = (size_t)warps * slot;
+    static std::mutex mu;
+    static std::map<int, int> blocks_per_sm;     // device -> resident blocks (also marks the attribute as set)
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    int bps = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = blocks_per_sm.find(dev);
+        if (it == blocks_per_sm.end()) {
+            CUDA_TRY(cudaFuncSetAttribute(bpe_merge_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_merge_kernel<C>, warps * 32, smem));
+            if (bps < 1) bps = 1;
+            blocks_per_sm[dev] = bps;
+        } else bps = it->second;
+    }
+    // Resident-size grid: every warp pulls words from the class's shared counter.
+    int64_t grid = (int64_t)d.sm_count * bps;
+    const int64_t need = (n_rows + warps - 1) / warps;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    bpe_merge_kernel<C><<<(unsigned)grid, warps * 32, smem, st>>>(
+        bytes, offsets, s.class_list + (int64_t)cls * n_rows, s.class_count + cls, s.work + cls, t,
+        s.tokens, s.counts, status);
+    LAUNCH_CHECK("bpe_merge_kernel");
+    return 0;
+}
+
+int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
+                  int64_t n_rows, int64_t total_bytes, int32_t* status, void* scratch, size_t scratch_bytes,
+                  cudaStream_t st) {
+    if (!scratch) return fail(DNATOK_ERR_SCRATCH, "BPE needs a scratch buffer (dnatok_scratch_bytes)");
+    if (reinterpret_cast<uintptr_t>(scratch) & 255) return fail(DNATOK_ERR_SCRATCH, "scratch must be 256-byte aligned");
+    BpeScratch s = bpe_scratch_layout(scratch, n_rows, total_bytes);
+    if (s.bytes > scratch_bytes) return fail(DNATOK_ERR_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, s.bytes);
+    if (n_rows == 0) return 0;
+    CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 64, st));   // class_count and work are adjacent
+    bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
+                                                                       s.class_list, s.counts, status);
+    LAUNCH_CHECK("bpe_classify_kernel");
+    BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
+    int rc;
+    // longest class first: its few, slow words start while nothing else competes for the SMs
+    if ((rc = launch_bpe_class<16384>(d, t, 6, bytes, offsets, n_rows, s, status, st))) return rc;
+    if ((rc = launch_bpe_class<8192>(d, t, 5, bytes, offsets, n_rows, s, status, st))) return rc;
+    if ((rc = launch_bpe_class<4096>(d, t, 4, bytes, offsets, n_rows, s, status, st))) return rc;
+    if ((rc = launch_bpe_class<2048>(d, t, 3, bytes, offsets, n_rows, s, status, st))) return rc;
+    if ((rc = launch_bpe_class<1024>(d, t, 2, bytes, offsets, n_rows, s, status, st))) return rc;
+    if ((rc = launch_bpe_class<512>(d, t, 1, bytes, offsets, n_rows, s, status, st))) return rc;
+    if ((rc = launch_bpe_class<256>(d, t, 0, bytes, offsets, n_rows, s, status, st))) return rc;
+    return 0;
+}
+
+template <typename SrcT, bool LUT>
+int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, const int32_t* counts,
+                int64_t n_rows, int64_t total_bytes, const RowFormat& rf, int id_bits, void* ids, void* mask,
+                int32_t* lengths, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
+    if (n_rows == 0) return 0;
+    if (rf.out_stride > 0) {
+        const int64_t tpr = (rf.out_stride + EMIT_TILE - 1) / EMIT_TILE;
+        const int64_t n_tiles = tpr * n_rows;
+        const unsigned grid = (unsigned)(n_tiles < (int64_t)d.sm_count * 64 ? n_tiles : (int64_t)d.sm_count * 64);
+        if (id_bits == 64)
+            emit_padded_kernel<SrcT, int64_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, offsets, counts, n_rows, d.lut256, rf,
+                                                                                  (int64_t*)ids, mask, lengths, status, tpr, n_tiles);
+        else
+            emit_padded_kernel<SrcT, int32_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, offsets, counts, n_rows, d.lut256, rf,
+                                                                                  (int32_t*)ids, mask, lengths, status, tpr, n_tiles);
+        LAUNCH_CHECK("emit_padded_kernel");
+    } else {
+        const int64_t bound = total_bytes + 2 * n_rows;
+        const int64_t n_tiles = (bound + EMIT_TILE - 1) / EMIT_TILE;
+        if (n_tiles == 0) return 0;
+        const unsigned grid = (unsigned)(n_tiles < (int64_t)d.sm_count * 64 ? n_tiles : (int64_t)d.sm_count * 64);
+        if (id_bits == 64)
+            emit_ragged_kernel<SrcT, int64_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, offsets, out_offsets, n_rows, d.lut256, rf,
+                                                                                  (int64_t*)ids, mask, n_tiles);
+        else
+            emit_ragged_kernel<SrcT, int32_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, offsets, out_offsets, n_rows, d.lut256, rf,
+                                                                                  (int32_t*)ids, mask, n_tiles);
+        LAUNCH_CHECK("emit_ragged_kernel");
+    }
+    return 0;
+}
+
+template <bool COUNT_ONLY>
+int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
+                int64_t n_rows, const RowFormat& rf, int id_bits, void* ids, void* mask,
+                const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets,
+                int32_t* status, cudaStream_t st) {
+    if (n_rows == 0) return 0;
+    const int k = h->k;
+    const size_t smem = (size_t)((KMER_TILE_W * k + 32 + 15) & ~15) + (size_t)KMER_TILE_W * k * 4;
+    const unsigned grid = (unsigned)(n_rows < (int64_t)d.sm_count * 64 ? n_rows : (int64_t)d.sm_count * 64);
+    if (id_bits == 64)
+        kmer_rows_kernel<int64_t, COUNT_ONLY><<<grid, KMER_THREADS, smem, st>>>(bytes, offsets, n_rows, k, d.kmer_ids, d.lut256, rf,
+                                                                                (int64_t*)ids, mask, lengths_in, lengths_out, out_offsets, status);
+    else
+        kmer_rows_kernel<int32_t, COUNT_ONLY><<<grid, KMER_THREADS, smem, st>>>(bytes, offsets, n_rows, k, d.kmer_ids, d.lut256, rf,
+                                                                                (int32_t*)ids, mask, lengths_in, lengths_out, out_offsets, status);
+    LAUNCH_CHECK("kmer_rows_kernel");
+    return 0;
+}
+
+int launch_span_lengths(const int64_t* offsets, const int32_t* counts, int64_t n_rows, const RowFormat& rf,
+                        int32_t* lengths, int32_t* status, cudaStream_t st) {
+    if (n_rows == 0) return 0;
+    span_lengths_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, counts, n_rows, rf, lengths, status);
+    LAUNCH_CHECK("span_lengths_kernel");
+    return 0;
+}
+
+int check_batch(const dnatok_handle* h, const void* bytes, const void* offsets, int64_t n_rows, int64_t total) {
+    if (!h) return fail(DNATOK_ERR_INVALID, "handle is NULL");
+    if (n_rows < 0 || total < 0) return fail(DNATOK_ERR_INVALID, "negative size");
+    if (n_rows > INT32_MAX) return fail(DNATOK_ERR_INVALID, "more than 2^31-1 rows");
+    if (!offsets) return fail(DNATOK_ERR_INVALID, "offsets is NULL");
+    if (total > 0 && !bytes) return fail(DNATOK_ERR_INVALID, "bytes is NULL");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dnatok_version(void) { return DNATOK_ABI_VERSION; }
+const char* dnatok_last_error(void) { return g_err.c_str(); }
+int64_t dnatok_launch_count(void) { return g_launches.load(); }
+
+static int check_specials(const dnatok_specials* sp) {
+    if (!sp) return fail(DNATOK_ERR_INVALID, "specials is NULL");
+    if (sp->pad_id < 0) return fail(DNATOK_ERR_INVALID, "pad_id < 0");
+    return 0;
+}
+
+int dnatok_create_char(const int32_t lut[256], const dnatok_specials* sp, dnatok_handle** out) {
+    if (!lut || !out) return fail(DNATOK_ERR_INVALID, "NULL argument");
+    if (int rc = check_specials(sp)) return rc;
+    auto* h = new (std::nothrow) dnatok_handle();
+    if (!h) return fail(DNATOK_ERR_INVALID, "out of memory");
+    h->kind = DNATOK_KIND_CHAR; h->sp = *sp;
+    h->lut256.assign(lut, lut + 256);
+    *out = h;
+    return DNATOK_OK;
+}
+
+int dnatok_create_kmer(int k, const int32_t* kmer_ids, const int32_t single_ids[256],
+                       const dnatok_specials* sp, dnatok_handle** out) {
+    if (!kmer_ids || !single_ids || !out) return fail(DNATOK_ERR_INVALID, "NULL argument");
+    if (k < 1 || k > KMER_MAX_K) return fail(DNATOK_ERR_UNSUPPORTED, "k must be in 1..%d", KMER_MAX_K);
+    if (int rc = check_specials(sp)) return rc;
+    auto* h = new (std::nothrow) dnatok_handle();
+    if (!h) return fail(DNATOK_ERR_INVALID, "out of memory");
+    h->kind = DNATOK_KIND_KMER; h->sp = *sp; h->k = k;
+    h->lut256.assign(single_ids, single_ids + 256);
+    h->kmer_ids.assign(kmer_ids, kmer_ids + ((size_t)1 << (2 * k)));
+    *out = h;
+    return DNATOK_OK;
+}
+
+int dnatok_create_bpe(const int32_t* a, const int32_t* b, const int32_t* o, int32_t n,
+                      const int32_t byte_ids[256], const dnatok_specials* sp, dnatok_handle** out) {
+    if (!a || !b || !o || !byte_ids || !out) return fail(DNATOK_ERR_INVALID, "NULL argument");
+    if (int rc = check_specials(sp)) return rc;
+    auto* h = new (std::nothrow) dnatok_handle();
+    if (!h) return fail(DNATOK_ERR_INVALID, "out of memory");
+    h->kind = DNATOK_KIND_BPE; h->sp = *sp;
+    h->lut256.assign(byte_ids, byte_ids + 256);
+    std::string err;
+    if (int rc = build_bpe_table(a, b, o, n, byte_ids, &h->bpe, &err)) {
+        delete h;
+        return fail(rc, "%s", err.c_str());
+    }
+    *out = h;
+    return DNATOK_OK;
+}
+
+void dnatok_destroy(dnatok_handle* h) {
+    if (!h) return;
+    int cur = 0;
+    cudaGetDevice(&cur);
+    for (auto& kv : h->dev) {
+        DeviceTables& d = kv.second;
+        if (cudaSetDevice(kv.first) != cudaSuccess) continue;
+        if (d.stream) cudaStreamSynchronize(d.stream);
+        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.byte_tok, d.st_bytes, d.st_offsets,
+                        d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
+        for (void* p : ptrs) if (p) cudaFree(p);
+        if (d.stream) cudaStreamDestroy(d.stream);
+    }
+    if (!h->dev.empty()) cudaSetDevice(cur);
+    delete h;
+}
+
+int dnatok_kind(const dnatok_handle* h) { return h ? h->kind : DNATOK_ERR_INVALID; }
+
+size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes) {
+    if (!h || h->kind != DNATOK_KIND_BPE || n_rows < 0 || total_bytes < 0) return 0;
+    return bpe_scratch_layout(nullptr, n_rows, total_bytes).bytes;
+}
+
+int64_t dnatok_max_tokens(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes, const dnatok_format* f) {
+    if (!h || !f) return 0;
+    return total_bytes + (int64_t)n_special(h, f) * n_rows;
+}
+
+int dnatok_scan_lengths(const int32_t* d_lengths, int64_t n_rows, int64_t* d_out_offsets, dnatok_stream stream) {
+    if (!d_lengths || !d_out_offsets || n_rows < 0) return fail(DNATOK_ERR_INVALID, "bad argument");
+    scan_lengths_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(d_lengths, n_rows, d_out_offsets);
+    LAUNCH_CHECK("scan_lengths_kernel");
+    return DNATOK_OK;
+}
+
+int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets, int64_t n_rows,
+                   int64_t total_bytes, const dnatok_format* fmt, int32_t* d_lengths, int32_t* d_status,
+                   void* d_scratch, size_t scratch_bytes, dnatok_stream stream) {
+    if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
+    if (int rc = check_format(fmt, false)) return rc;
+    if (!d_lengths) return fail(DNATOK_ERR_INVALID, "d_lengths is NULL");
+    cudaStream_t st = (cudaStream_t)stream;
+    DeviceTables* d;
+    if (int rc = tables_for_current_device(h, &d)) return rc;
+    RowFormat rf;
+    if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
+    if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
+    switch (h->kind) {
+        case DNATOK_KIND_CHAR:
+            return launch_span_lengths(d_offsets, nullptr, n_rows, rf, d_lengths, d_status, st);
+        case DNATOK_KIND_KMER:
+            return launch_kmer<true>(h, *d, d_bytes, d_offsets, n_rows, rf, 64, nullptr, nullptr, nullptr, d_lengths,
+                                     nullptr, d_status, st);
+        default: {
+            if (int rc = run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, st))
+                return rc;
+            BpeScratch s = bpe_scratch_layout(d_scratch, n_rows, total_bytes);
+            return launch_span_lengths(d_offsets, s.counts, n_rows, rf, d_lengths, d_status, st);
+        }
+    }
+}
+
+int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets, int64_t n_rows,
+                 int64_t total_bytes, const dnatok_format* fmt, const int32_t* d_lengths,
+                 const int64_t* d_out_offsets, void* d_ids, void* d_mask, int32_t* d_status, void* d_scratch,
+                 size_t scratch_bytes, dnatok_stream stream) {
+    if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
+    if (int rc = check_format(fmt, false)) return rc;
+    if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
+    if (fmt->mask_bits && !d_mask && fmt->out_stride > 0) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
+    if (fmt->out_stride == 0 && !d_out_offsets) return fail(DNATOK_ERR_INVALID, "ragged output needs d_out_offsets");
+    cudaStream_t st = (cudaStream_t)stream;
+    DeviceTables* d;
+    if (int rc = tables_for_current_device(h, &d)) return rc;
+    RowFormat rf;
+    if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
+    switch (h->kind) {
+        case DNATOK_KIND_CHAR:
+            return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits,
+                                              d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
+        case DNATOK_KIND_KMER:
+            if (fmt->out_stride > 0 && fmt->pad_left && !d_lengths)
+                return fail(DNATOK_ERR_INVALID, "left padding needs d_lengths from dnatok_prepare");
+            return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, rf, fmt->id_bits, d_ids, d_mask, d_lengths,
+                                      nullptr, d_out_offsets, d_status, st);
+        default: {
+            if (!d_scratch) return fail(DNATOK_ERR_SCRATCH, "BPE write needs the scratch filled by dnatok_prepare");
+            BpeScratch s = bpe_scratch_layout(d_scratch, n_rows, total_bytes);
+            if (s.bytes > scratch_bytes) return fail(DNATOK_ERR_SCRATCH, "scratch too small");
+            return launch_emit<uint16_t, false>(*d, s.tokens, d_offsets, s.counts, n_rows, total_bytes, rf, fmt->id_bits,
+                                                d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
+        }
+    }
+}
+
+int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets, int64_t n_rows,
+                  int64_t total_bytes, const dnatok_format* fmt, void* d_ids, void* d_mask, int32_t* d_lengths,
+                  int64_t* d_out_offsets, int32_t* d_status, void* d_scratch, size_t scratch_bytes,
+                  dnatok_stream stream) {
+    if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
+    if (int rc = check_format(fmt, false)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool ragged = fmt->out_stride == 0;
+    if (ragged && (!d_lengths || !d_out_offsets))
+        return fail(DNATOK_ERR_INVALID, "ragged output needs d_lengths and d_out_offsets");
+    DeviceTables* d;
+    if (int rc = tables_for_current_device(h, &d)) return rc;
+    RowFormat rf;
+    if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
+
+    const bool need_prepare = ragged || h->kind == DNATOK_KIND_BPE ||
+                              (h->kind == DNATOK_KIND_KMER && fmt->pad_left);
+    if (need_prepare) {
+        if (!d_lengths) return fail(DNATOK_ERR_INVALID, "this format needs d_lengths");
+        if (int rc = dnatok_prepare(h, d_bytes, d_offsets, n_rows, total_bytes, fmt, d_lengths, d_status, d_scratch,
+                                    scratch_bytes, stream))
+            return rc;
+        if (ragged) {
+            if (int rc = dnatok_scan_lengths(d_lengths, n_rows, d_out_offsets, stream)) return rc;
+        }
+        return dnatok_write(h, d_bytes, d_offsets, n_rows, total_bytes, fmt, d_lengths, d_out_offsets, d_ids, d_mask,
+                            d_status, d_scratch, scratch_bytes, stream);
+    }
+    // padded char / right-padded k-mer: one kernel, lengths written on the way
+    if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
+    if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
+    if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
+    if (h->kind == DNATOK_KIND_CHAR)
+        return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits, d_ids,
+                                          d_mask, d_lengths, nullptr, d_status, st);
+    return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
+                              nullptr, d_status, st);
+}
+
+// ------------------------------------------------------------------ host-buffer pipeline
+
+static int grow(void** p, size_t* cap, size_t need) {
+    if (need <= *cap) return 0;
+    if (*p) CUDA_TRY(cudaFree(*p));
+    *p = nullptr; *cap = 0;
+    const size_t sz = align_up(need + need / 8, 1 << 20);
+    CUDA_TRY(cudaMalloc(p, sz));
+    *cap = sz;
+    return 0;
+}
+
+int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, const int64_t* h_offsets,
+                       int64_t n_rows, const dnatok_format* fmt, void* h_ids, int64_t ids_capacity, void* h_mask,
+                       int32_t* h_lengths, int64_t* h_out_offsets, int32_t* h_status, int64_t* out_stride_used) {
+    if (!h) return fail(DNATOK_ERR_INVALID, "handle is NULL");
+    if (int rc = check_format(fmt, true)) return rc;
+    if (n_rows < 0 || !h_offsets) return fail(DNATOK_ERR_INVALID, "bad batch");
+    const int64_t total = h_offsets[n_rows] - h_offsets[0];
+    if (h_offsets[0] != 0) return fail(DNATOK_ERR_INVALID, "offsets must start at 0");
+    if (int rc = check_batch(h, h_bytes, h_offsets, n_rows, total)) return rc;
+    CUDA_TRY(cudaSetDevice(device));
+    DeviceTables* d;
+    if (int rc = tables_for_current_device(h, &d)) return rc;
+    if (!d->stream) CUDA_TRY(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+    cudaStream_t st = d->stream;
+    const int ns = n_special(h, fmt);
+    const size_t id_sz = fmt->id_bits / 8, mask_sz = fmt->mask_bits / 8;
+
+    if (int rc = grow((void**)&d->st_bytes, &d->st_bytes_cap, (size_t)total + 64)) return rc;
+    if (int rc = grow((void**)&d->st_offsets, &d->st_offsets_cap, (size_t)(n_rows + 1) * 8)) return rc;
+    if ((size_t)n_rows + 1 > d->st_rows_cap) {
+        for (void** p : {(void**)&d->st_lengths, (void**)&d->st_status, (void**)&d->st_out_offsets})
+            if (*p) { CUDA_TRY(cudaFree(*p)); *p = nullptr; }
+        const size_t cap = (size_t)n_rows + n_rows / 8 + 1024;
+        CUDA_TRY(cudaMalloc((void**)&d->st_lengths, cap * 4));
+        CUDA_TRY(cudaMalloc((void**)&d->st_status, cap * 4));
+        CUDA_TRY(cudaMalloc((void**)&d->st_out_offsets, cap * 8));
+        d->st_rows_cap = cap;
+    }
+    const size_t scratch_need = dnatok_scratch_bytes(h, n_rows, total);
+    if (scratch_need) if (int rc = grow(&d->st_scratch, &d->st_scratch_cap, scratch_need)) return rc;
+
+    CUDA_TRY(cudaMemcpyAsync(d->st_bytes, h_bytes, (size_t)total, cudaMemcpyHostToDevice, st));
+    CUDA_TRY(cudaMemcpyAsync(d->st_offsets, h_offsets, (size_t)(n_rows + 1) * 8, cudaMemcpyHostToDevice, st));
+
+    dnatok_format f = *fmt;
+    int64_t stride = fmt->out_stride;
+    bool prepared = false;
+    if (stride < 0) {
+        // pad to the longest row: char rows are sized on the host, the other kinds by the sizing pass
+        int64_t longest = 0;
+        if (h->kind == DNATOK_KIND_CHAR) {
+            const int64_t cap = fmt->max_tokens > 0 ? fmt->max_tokens - ns : INT64_MAX;
+            for (int64_t i = 0; i < n_rows; ++i) {
+                int64_t n = h_offsets[i + 1] - h_offsets[i];
+                if (n > cap) n = cap;
+                if (n + ns > longest) longest = n + ns;
+            }
+        } else {
+            f.out_stride = 0;
+            if (int rc = dnatok_prepare(h, d->st_bytes, d->st_offsets, n_rows, total, &f, d->st_lengths, d->st_status,
+                                        d->st_scratch, d->st_scratch_cap, st))
+                return rc;
+            std::vector<int32_t> tmp;
+            int32_t* hl = h_lengths;
+            if (!hl) { tmp.resize((size_t)n_rows + 1); hl = tmp.data(); }
+            CUDA_TRY(cudaMemcpyAsync(hl, d->st_lengths, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+            CUDA_TRY(cudaStreamSynchronize(st));
+            for (int64_t i = 0; i < n_rows; ++i) if (hl[i] > longest) longest = hl[i];
+            prepared = true;
+        }
+        stride = longest;
+        if (stride == 0) { if (out_stride_used) *out_stride_used = 0; CUDA_TRY(cudaStreamSynchronize(st)); return DNATOK_OK; }
+    }
+    f.out_stride = stride;
+    const bool ragged = stride == 0;
+    const int64_t out_elems = ragged ? dnatok_max_tokens(h, n_rows, total, fmt) : n_rows * stride;
+    if (!ragged && out_elems > ids_capacity) return fail(DNATOK_ERR_CAPACITY, "ids buffer holds %lld elements, %lld needed",
+                                                         (long long)ids_capacity, (long long)out_elems);
+    if (int rc = grow(&d->st_ids, &d->st_ids_cap, (size_t)out_elems * id_sz + 64)) return rc;
+    if (mask_sz && h_mask) if (int rc = grow(&d->st_mask, &d->st_mask_cap, (size_t)out_elems * mask_sz + 64)) return rc;
+    void* dmask = (mask_sz && h_mask) ? d->st_mask : nullptr;
+    if (!dmask) f.mask_bits = 0;
+
+    int rc;
+    if (prepared) {
+        rc = dnatok_write(h, d->st_bytes, d->st_offsets, n_rows, total, &f, d->st_lengths, nullptr, d->st_ids, dmask,
+                          d->st_status, d->st_scratch, d->st_scratch_cap, st);
+    } else {
+        rc = dnatok_encode(h, d->st_bytes, d->st_offsets, n_rows, total, &f, d->st_ids, dmask, d->st_lengths,
+                           d->st_out_offsets, d->st_status, d->st_scratch, d->st_scratch_cap, st);
+    }
+    if (rc) return rc;
+
+    int64_t n_out = out_elems;
+    if (ragged) {
+        int64_t tot = 0;
+        CUDA_TRY(cudaMemcpyAsync(&tot, d->st_out_offsets + n_rows, 8, cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaStreamSynchronize(st));
+        n_out = tot;
+        if (n_out > ids_capacity) return fail(DNATOK_ERR_CAPACITY, "ids buffer holds %lld elements, %lld needed",
+                                              (long long)ids_capacity, (long long)n_out);
+        if (h_out_offsets)
+            CUDA_TRY(cudaMemcpyAsync(h_out_offsets, d->st_out_offsets, (size_t)(n_rows + 1) * 8, cudaMemcpyDeviceToHost, st));
+    }
+    if (n_out) CUDA_TRY(cudaMemcpyAsync(h_ids, d->st_ids, (size_t)n_out * id_sz, cudaMemcpyDeviceToHost, st));
+    if (dmask && n_out) CUDA_TRY(cudaMemcpyAsync(h_mask, dmask, (size_t)n_out * mask_sz, cudaMemcpyDeviceToHost, st));
+    if (h_lengths && n_rows) CUDA_TRY(cudaMemcpyAsync(h_lengths, d->st_lengths, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+    if (h_status && n_rows) CUDA_TRY(cudaMemcpyAsync(h_status, d->st_status, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    if (out_stride_used) *out_stride_used = ragged ? n_out : stride;
+    return DNATOK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+"""Sharding a batch by sequence over the GPUs of one box.
+
+Rows are independent, so the hot path has no collective: each rank encodes its own rows on its
+own GPU.  ``partition`` picks the rows; ``gather_padded`` is the optional step that brings
+fixed-width results to rank 0 over NCCL (or gloo on CPU tensors in tests).  The reference has
+no multi-GPU code at all (one process, one device: ``src/dnatok_bpe_kernel/dnatok_bpe.cu:869-870``).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import numpy as np
+
+
+def partition(lengths: np.ndarray, world: int, mode: str = "contiguous") -> List[np.ndarray]:
+    """Row indices per rank.
+
+    ``contiguous``: consecutive blocks with near-equal total bases (order preserving; a
+    concatenation of the rank outputs is the batch output).  ``greedy``: longest-first bin
+    packing by bases for ragged read sets; use ``restore_order`` on the gathered rows.
+    """
+    lengths = np.asarray(lengths, dtype=np.int64)
+    n = lengths.shape[0]
+    if world <= 1:
+        return [np.arange(n, dtype=np.int64)]
+    if mode == "contiguous":
+        csum = np.concatenate([[0], np.cumsum(lengths)])
+        total = csum[-1]
+        cuts = [0]
+        for r in range(1, world):
+            target = total * r / world
+            j = int(np.searchsorted(csum, target, side="left"))
+            j = min(max(j, cuts[-1]), n)
+            # choose the nearer of j-1 / j
+            if j > cuts[-1] and abs(csum[j - 1] - target) <= abs(csum[j] - target):
+                j -= 1
+            cuts.append(j)
+        cuts.append(n)
+        return [np.arange(cuts[r], cuts[r + 1], dtype=np.int64) for r in range(world)]
+    if mode == "greedy":
+        order = np.argsort(-lengths, kind="stable")
+        load = np.zeros(world, dtype=np.int64)
+        bins: List[List[int]] = [[] for _ in range(world)]
+        for i in order.tolist():
+            r = int(np.argmin(load))
+            bins[r].append(i)
+            load[r] += lengths[i]
+        return [np.sort(np.asarray(b, dtype=np.int64)) for b in bins]
+    raise ValueError("mode must be 'contiguous' or 'greedy'")
+
+
+def take_rows(flat: np.ndarray, offsets: np.ndarray, rows: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+    """The sub-batch (flat bytes, offsets) made of ``rows``."""
+    lens = (offsets[1:] - offsets[:-1])[rows]
+    out_off = np.zeros(rows.shape[0] + 1, dtype=np.int64)
+    np.cumsum(lens, out=out_off[1:])
+    if rows.shape[0] and np.all(np.diff(rows) == 1):
+        return flat[offsets[rows[0]]:offsets[rows[-1] + 1]], out_off
+    out = np.empty(int(out_off[-1]), dtype=np.uint8)
+    for j, i in enumerate(rows.tolist()):
+        out[out_off[j]:out_off[j + 1]] = flat[offsets[i]:offsets[i + 1]]
+    return out, out_off
+
+
+def restore_order(parts: List[np.ndarray], rows_per_rank: List[np.ndarray]) -> np.ndarray:
+    """Inverse of a partition for fixed-width results: parts[r] is [len(rows_per_rank[r]), W]."""
+    n = sum(p.shape[0] for p in parts)
+    width = max((p.shape[1] for p in parts if p.ndim == 2), default=0)
+    out = np.zeros((n, width), dtype=parts[0].dtype if parts else np.int64)
+    for p, rows in zip(parts, rows_per_rank):
+        out[rows, :p.shape[1]] = p
+    return out
+
+
+def gather_padded(ids, n_rows_per_rank: List[int], width: int, pad_id: int, dst: int = 0, group=None):
+    """Optional gather of fixed-width rows to ``dst`` with torch.distributed (NCCL for CUDA tensors,
+    gloo for CPU tensors).  Every rank passes its [rows_r, w_r] tensor; rows are right-padded to
+    ``width`` with ``pad_id`` first.  Returns the [sum rows, width] tensor on ``dst``, else None.
+    Not part of the timed hot path."""
+    import torch
+    import torch.distributed as dist
+    rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    mine = torch.full((n_rows_per_rank[rank], width), pad_id, dtype=ids.dtype, device=ids.device)
+    mine[:, :ids.shape[1]] = ids
+    max_rows = max(n_rows_per_rank)
+    buf = torch.full((max_rows, width), pad_id, dtype=ids.dtype, device=ids.device)
+    buf[:mine.shape[0]] = mine
+    if rank == dst:
+        bucket = [torch.empty_like(buf) for _ in range(world)]
+        dist.gather(buf, bucket, dst=dst, group=group)
+        return torch.cat([bucket[r][:n_rows_per_rank[r]] for r in range(world)], dim=0)
+    dist.gather(buf, None, dst=dst, group=group)
+    return None

@@ -1,0 +1,143 @@
+/* dnatok_b200 - C ABI of the B200 (sm_100a) genomic tokenizer kernels.
+ *
+ * Plain pointers and sizes only; no torch, no C++ types.  Every function returns DNATOK_OK (0)
+ * or a negative error code, never throws and never aborts; dnatok_last_error() gives the text
+ * of the last failure on the calling thread.  Device buffers are owned by the caller; a handle
+ * owns only its lookup tables (uploaded once per device on first use) and, for the *_host
+ * entry point, its staging buffers.  Calls on distinct handles are thread safe; one call per
+ * handle at a time.
+ *
+ * Which reference interface each entry point stands in for (paths inside eniktab/DNAtok):
+ *   dnatok_create_char    the ASCII LUT built by DNATok.discover, src/dna_tokenizer.py:995-1030
+ *                         (_build_ascii_lut_probe_all :633-653)
+ *   dnatok_create_kmer    _build_kmer_lut, src/dna_tokenizer.py:743-822 (+ tail LUT :957-971)
+ *   dnatok_create_bpe     DNATokBPE(merges_path, byte_to_id_lut, max_iters) constructor,
+ *                         src/dnatok_bpe_kernel/dnatok_bpe.cu:797-862 (build_vocab_from_merges :761-791)
+ *   dnatok_encode         char: _encode_batch_ascii_lut_numpy :1779-1820 / _map_ascii_bytes_to_ids_cuda
+ *                         :2653-2723; k-mer: _encode_batch_kmer_numpy_partial :1369-1474 with
+ *                         _encode_kmer_fallback_from_lut :1896-1953 / _map_kmer_bytes_to_ids_cuda
+ *                         :2826-2940; BPE: DNATokBPE::tokenize_batch, dnatok_bpe.cu:865-947, plus the
+ *                         remap / trim / pad / mask tail of GPUTokBPEBackend.encode_batch,
+ *                         src/gputok_bpe_backend.py:577-601; padding and masks of
+ *                         encode_batch_with_padding, src/dna_tokenizer.py:2150-2236
+ *   dnatok_prepare/write  the two halves of dnatok_encode for callers that size the output from
+ *                         the longest row (the reference's lens.max().item(), gputok_bpe_backend.py:584-585)
+ *   dnatok_encode_host    the same path fed from host memory: host packing + H2D of
+ *                         dnatok_bpe.cu:872-887 and the D2H of src/dna_tokenizer.py:2067-2083
+ */
+#ifndef DNATOK_B200_H
+#define DNATOK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DNATOK_ABI_VERSION 1
+
+/* return codes */
+#define DNATOK_OK               0
+#define DNATOK_ERR_INVALID     (-1)   /* bad argument */
+#define DNATOK_ERR_CUDA        (-2)   /* a CUDA runtime call failed */
+#define DNATOK_ERR_UNSUPPORTED (-3)   /* tables outside what the kernels implement */
+#define DNATOK_ERR_SCRATCH     (-4)   /* scratch buffer missing or too small */
+#define DNATOK_ERR_CAPACITY    (-5)   /* output buffer too small */
+
+/* per-row status bits written to d_status (0 = fine) */
+#define DNATOK_ROW_TOO_LONG       1   /* BPE word longer than the kernel's shared-memory slot; row left empty */
+#define DNATOK_ROW_NOT_CONVERGED  2   /* BPE pass limit reached (cannot happen for a consistent table) */
+#define DNATOK_ROW_CLIPPED        4   /* row had more tokens than out_stride and was cut to fit */
+
+#define DNATOK_KIND_CHAR 0
+#define DNATOK_KIND_KMER 1
+#define DNATOK_KIND_BPE  2
+
+#define DNATOK_BPE_MAX_WORD 16384     /* longest BPE word (bytes) the merge kernel accepts */
+
+typedef struct dnatok_handle dnatok_handle;
+typedef void* dnatok_stream;          /* a cudaStream_t */
+
+typedef struct {
+    int32_t pad_id;
+    int32_t unk_id;
+    int32_t cls_id;                   /* emitted before the row when add_special; -1: none */
+    int32_t sep_id;                   /* emitted after the row when add_special; -1: none */
+} dnatok_specials;
+
+typedef struct {
+    int32_t id_bits;                  /* 32 or 64: element type of the ids output */
+    int32_t mask_bits;                /* 0: no mask output; 8, 32 or 64: element type of the mask */
+    int32_t add_special;              /* attach cls/sep */
+    int32_t pad_left;                 /* 0: right padding (HF default), 1: left (DNATok default) */
+    int64_t max_tokens;               /* truncate rows to this many tokens, specials included; 0: off */
+    int64_t out_stride;               /* > 0: ids/mask are [n_rows, out_stride]; 0: ragged (ids only,
+                                         d_out_offsets gives row starts); -1 (host entry point only):
+                                         pad to the longest row */
+} dnatok_format;
+
+int dnatok_version(void);
+const char* dnatok_last_error(void);
+
+int dnatok_create_char(const int32_t lut[256], const dnatok_specials* sp, dnatok_handle** out);
+int dnatok_create_kmer(int k, const int32_t* kmer_ids /* 4^k, product("ACGT") order */,
+                       const int32_t single_ids[256], const dnatok_specials* sp, dnatok_handle** out);
+int dnatok_create_bpe(const int32_t* merge_a, const int32_t* merge_b, const int32_t* merge_out,
+                      int32_t n_merges, const int32_t byte_ids[256], const dnatok_specials* sp,
+                      dnatok_handle** out);
+void dnatok_destroy(dnatok_handle* h);
+int dnatok_kind(const dnatok_handle* h);
+
+/* Bytes of caller-owned device scratch dnatok_prepare / dnatok_encode need for this batch
+ * (0 for char).  The scratch must be 256-byte aligned. */
+size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes);
+
+/* Upper bound on the number of ids a ragged output can hold for this batch. */
+int64_t dnatok_max_tokens(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes,
+                          const dnatok_format* fmt);
+
+/* Row i is d_bytes[d_offsets[i] .. d_offsets[i+1]).  All pointers are device pointers on the
+ * current device; work is enqueued on `stream` and nothing is synchronised.
+ *
+ * dnatok_prepare: d_lengths[i] (int32) = tokens of row i after truncation, specials included.
+ *   For BPE the merged tokens stay in d_scratch for the dnatok_write that follows.
+ * dnatok_write:   fills d_ids / d_mask.  Padded: out_stride columns per row.  Ragged:
+ *   d_out_offsets (int64[n_rows+1], input) gives each row's start; d_mask may be NULL.
+ *   d_lengths must come from dnatok_prepare on the same batch, format and scratch.
+ * dnatok_encode:  both steps.  Ragged: d_out_offsets is an output (exclusive scan of lengths).
+ *   d_lengths and d_status may be NULL for char/k-mer padded output. */
+int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets,
+                   int64_t n_rows, int64_t total_bytes, const dnatok_format* fmt,
+                   int32_t* d_lengths, int32_t* d_status, void* d_scratch, size_t scratch_bytes,
+                   dnatok_stream stream);
+int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets,
+                 int64_t n_rows, int64_t total_bytes, const dnatok_format* fmt,
+                 const int32_t* d_lengths, const int64_t* d_out_offsets, void* d_ids, void* d_mask,
+                 int32_t* d_status, void* d_scratch, size_t scratch_bytes, dnatok_stream stream);
+int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets,
+                  int64_t n_rows, int64_t total_bytes, const dnatok_format* fmt,
+                  void* d_ids, void* d_mask, int32_t* d_lengths, int64_t* d_out_offsets,
+                  int32_t* d_status, void* d_scratch, size_t scratch_bytes, dnatok_stream stream);
+
+/* Exclusive scan: d_out_offsets[0] = 0, d_out_offsets[i+1] = sum of d_lengths[0..i]. */
+int dnatok_scan_lengths(const int32_t* d_lengths, int64_t n_rows, int64_t* d_out_offsets,
+                        dnatok_stream stream);
+
+/* Same path with HOST buffers on device `device`: copies bytes and offsets in, runs the kernels,
+ * copies ids / mask / lengths / status back and returns when they are in host memory.  Pinned
+ * host buffers make the copies asynchronous; pageable ones work.  ids_capacity counts elements
+ * of h_ids (and of h_mask when given).  With fmt->out_stride == -1 rows are padded to the
+ * longest row; *out_stride_used receives the stride (or the total id count when ragged). */
+int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes,
+                       const int64_t* h_offsets, int64_t n_rows, const dnatok_format* fmt,
+                       void* h_ids, int64_t ids_capacity, void* h_mask, int32_t* h_lengths,
+                       int64_t* h_out_offsets, int32_t* h_status, int64_t* out_stride_used);
+
+/* Number of kernels this library has launched from the calling process (for accounting). */
+int64_t dnatok_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DNATOK_B200_H */

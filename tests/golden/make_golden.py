@@ -1,0 +1,166 @@
+"""Generate the committed golden vectors.  Run where ``/root/reference`` and Hugging Face
+``tokenizers`` are available:
+
+    python tests/golden/make_golden.py
+
+Writes ``tests/golden/golden.json`` (hashes + small literal cases) from three sources:
+  * live Hugging Face tokenizers built by ``oracle/hf_oracle.py`` - the parity target;
+  * the reference's own CPU paths imported from ``/root/reference/src``: ``DNATok`` (numpy LUT and
+    k-mer paths) wrapped around those tokenizers, and ``dnatok_compat.Evo2ByteTokenizer``;
+  * the reference's normaliser known answers (``tests/test_gputok_bpe_backend.py:319-425``),
+    re-derived by calling its ``_compile_normalizer_step``.
+The reference cannot travel to the GPU box; these vectors can.
+"""
+import hashlib
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import transformers  # noqa: E402,F401  (must be imported before the reference's dnatok_compat)
+import torch  # noqa: E402
+
+from dnatok_b200 import synth  # noqa: E402
+from oracle import hf_oracle  # noqa: E402
+
+REF_SRC = "/root/reference/src"
+
+
+def sha(a) -> str:
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+ADVERSARIAL = [
+    "", "A", "N", "AC", "ACGTA", "ACGTAC", "ACGTACG", "NNNNNN", "ACGTNACGTACGT", "ACGTACNACGTAC",
+    "acgtACGTacgt", "ACGTRYKMACGT", "A" * 7, "A" * 64, "A" * 255, "C" * 1024, "AC" * 300, "ACG" * 333,
+    "N" * 50, "ACGT" * 3 + "N" * 7 + "ACGT" * 5 + "n", "TTTTTTTTTTTTTTA" * 20, "GATTACA" * 100 + "N",
+    "ACGTAC" * 10 + "ACGTA", "NACGTA" * 5, "ACGTAN" * 5, "AAAAACAAAAAGAAAAAAT" * 30,
+]
+
+
+def hf_batch(tok, strs, **kw):
+    enc = tok(strs, return_tensors="np", **kw)
+    return enc["input_ids"], enc["attention_mask"]
+
+
+class _Embedder(torch.nn.Module):
+    def __init__(self, tokenizer):
+        super().__init__()
+        self.tokenizer = tokenizer
+        self.pad_id = tokenizer.pad_token_id
+        self.max_position_embeddings = None
+        self._embed = torch.nn.Embedding(8, 2)
+
+    def embed_tokens(self, input_ids, rc_invariant=False):
+        return self._embed(input_ids.clamp(max=7))
+
+
+def main():
+    sys.path.insert(0, REF_SRC)
+    from dna_tokenizer import DNATok                      # reference, CPU numpy paths
+    import gputok_bpe_backend as ref_backend              # reference normaliser compiler
+    from dnatok_compat import Evo2ByteTokenizer           # reference byte-level tokenizer
+
+    G = {"tokenizers_version": __import__("tokenizers").__version__, "configs": {}, "adversarial": {}}
+
+    toks = {
+        "char": hf_oracle.char_tokenizer(),
+        "kmer6": hf_oracle.kmer_tokenizer(),
+        "bpe4096": hf_oracle.bpe_tokenizer("bpe4096"),
+        "byte": hf_oracle.byte_tokenizer(),
+        "bpe32000": hf_oracle.bpe_tokenizer("bpe32000"),
+    }
+
+    def record(name, flat, offs, tok, call, keep_rows=2):
+        strs = synth.rows_to_strings(flat, offs)
+        ids, mask = hf_batch(tok, strs, **call)
+        G["configs"][name] = {
+            "input_sha256": sha(flat), "n_rows": len(strs), "call": {k: v for k, v in call.items()},
+            "shape": list(ids.shape), "ids_sha256": sha(ids.astype(np.int64)),
+            "mask_sha256": sha(mask.astype(np.int64)),
+            "first_rows": ids[:keep_rows, :64].tolist(),
+            "n_tokens": int(mask.sum()),
+        }
+        return strs, ids, mask
+
+    f, o = synth.pack_rows(synth.config1())
+    s1, ids1, _ = record("cfg1_char", f, o, toks["char"], dict(padding=True))
+    f, o = synth.pack_rows(synth.config2())
+    s2, ids2, _ = record("cfg2_kmer6", f, o, toks["kmer6"], dict(padding="max_length", max_length=1000, truncation=True))
+    f, o = synth.pack_rows(synth.config3())
+    record("cfg3_bpe4096", f, o, toks["bpe4096"], dict(padding=True))
+    f, o = synth.pack_rows(synth.config4(batch=2, length=131072))
+    s4, ids4, _ = record("cfg4_byte_2x131072", f, o, toks["byte"], dict(padding=True))
+    f, o = synth.config5(n_reads=512)
+    record("cfg5_bpe32000_512reads", f, o, toks["bpe32000"], dict(padding=True))
+
+    # ragged (no padding) outputs of config 5: hash of the concatenated rows and the offsets
+    strs = synth.rows_to_strings(f, o)
+    rows = toks["bpe32000"](strs)["input_ids"]
+    cat = np.concatenate([np.asarray(r, dtype=np.int64) for r in rows])
+    G["configs"]["cfg5_bpe32000_512reads"]["ragged_ids_sha256"] = sha(cat)
+    G["configs"]["cfg5_bpe32000_512reads"]["ragged_offsets_sha256"] = sha(
+        np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int64))
+
+    # adversarial strings, ids without and with specials, per tokenizer
+    for name, tok in toks.items():
+        G["adversarial"][name] = {
+            "plain": [list(map(int, r)) for r in tok(ADVERSARIAL, add_special_tokens=False)["input_ids"]],
+            "special": [list(map(int, r)) for r in tok(ADVERSARIAL, add_special_tokens=True)["input_ids"]],
+        }
+    G["adversarial_inputs"] = ADVERSARIAL
+
+    # the reference's own CPU paths on the same inputs (no special tokens in the reference)
+    ref = {}
+    for name, tok, strs in (("cfg1_char", toks["char"], s1), ("cfg2_kmer6", toks["kmer6"], s2),
+                            ("cfg4_byte_2x131072", toks["byte"], s4)):
+        h = DNATok(_Embedder(tok), padding_side="right")
+        h.discover()
+        out = h.encode_batch_to_ids(strs)
+        plain = np.asarray(tok(strs, add_special_tokens=False, padding=True, return_tensors="np")["input_ids"])
+        ref[name] = {"path": "kmer" if getattr(h, "kmer_k", None) else "ascii_lut",
+                     "shape": list(out.shape), "ids_sha256": sha(out.numpy().astype(np.int64)),
+                     "equals_hf_plain": bool(np.array_equal(out.numpy(), plain))}
+    evo = Evo2ByteTokenizer(vocab_size=512)
+    seg = s4[0][:4096]
+    e_ids = evo(seg)["input_ids"]
+    ref["evo2_byte_first4096"] = {"ids_sha256": sha(np.asarray(e_ids, dtype=np.int64)),
+                                  "pad_token_id": evo.pad_token_id, "unk_token_id": evo.unk_token_id}
+    G["reference_paths"] = ref
+
+    # normaliser known answers, produced by the reference's compiler
+    cases = [
+        ({"type": "Strip", "strip_left": True, "strip_right": True}, ["  ACGT  ", "ACGT"]),
+        ({"type": "Strip", "strip_left": True, "strip_right": False}, ["  ACGT  "]),
+        ({"type": "Replace", "pattern": {"String": "N"}, "content": "-"}, ["ACGTNNACGT"]),
+        ({"type": "Replace", "pattern": {"Regex": "N{10,}"}, "content": "-"},
+         ["ACGT" + "N" * 9 + "ACGT", "ACGT" + "N" * 10 + "ACGT"]),
+        ({"type": "Prepend", "prepend": "_"}, ["ACGT", ""]),
+        ({"type": "Lowercase"}, ["ACGTACGT"]),
+        ({"type": "NFC"}, ["ACGT"]), ({"type": "NFKD"}, ["ACGT"]), ({"type": "StripAccents"}, ["ACGT"]),
+        ({"type": "Sequence", "normalizers": [{"type": "Strip", "strip_left": True, "strip_right": True},
+                                              {"type": "Replace", "pattern": {"Regex": "N{10,}"}, "content": "-"}]},
+         ["   " + "N" * 12 + "ACGT  "]),
+    ]
+    norm = []
+    for step, inputs in cases:
+        fn = ref_backend._compile_normalizer_step(step)
+        norm.append({"step": step, "inputs": inputs, "outputs": [fn(x) for x in inputs]})
+    rejected = [{"type": "BertNormalizer"}, {"type": "Nmt"}, {"type": "Precompiled"}, {"type": "SomeNewThingHFAdds"},
+                {"type": "Sequence", "normalizers": [{"type": "Strip"}, {"type": "BertNormalizer"}]}]
+    for step in rejected:
+        assert ref_backend._compile_normalizer_step(step) is None
+    G["normalizer"] = {"accepted": norm, "rejected": rejected}
+
+    with open(os.path.join(HERE, "golden.json"), "w") as fh:
+        json.dump(G, fh, indent=1, sort_keys=True)
+    print("wrote golden.json;", {k: v["shape"] for k, v in G["configs"].items()})
+    print("reference paths:", json.dumps(ref, indent=1))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,202 @@
+"""GPU parity: the CUDA kernels, called through the C ABI (ctypes), against the CPU checker,
+the committed golden vectors and live Hugging Face.  Bit-exact everywhere (integer work)."""
+import numpy as np
+import pytest
+
+from dnatok_b200 import synth
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def toks():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from dnatok_b200.tokenizer import B200Tokenizer
+    return {n: B200Tokenizer(H.spec(n), device=0) for n in H.TOKENIZERS}
+
+
+def dev(flat, offs):
+    d_b = torch.from_numpy(np.ascontiguousarray(flat)).cuda() if len(flat) else torch.empty(0, dtype=torch.uint8, device="cuda")
+    return d_b, torch.from_numpy(offs).cuda()
+
+
+def run_device(tok, flat, offs, **kw):
+    d_b, d_o = dev(flat, offs)
+    enc = tok.encode_device(d_b, d_o, host_offsets=offs, **kw)
+    torch.cuda.synchronize()
+    return enc
+
+
+@pytest.mark.parametrize("cfg", H.ALL_CONFIGS)
+def test_golden_configs_device(golden, toks, cfg):
+    g = golden["configs"][cfg]
+    name, flat, offs = H.config_inputs(cfg)
+    kw = H.call_to_kwargs(g["call"])
+    enc = run_device(toks[name], flat, offs, **kw)
+    ids = enc["input_ids"].cpu().numpy()
+    mask = enc["attention_mask"].cpu().numpy()
+    assert ids.dtype == np.int64 and mask.dtype == np.int64
+    assert list(ids.shape) == g["shape"]
+    o_ids, o_mask = H.oracle_batch(name, flat, offs, **kw)
+    assert np.array_equal(ids, o_ids)
+    assert np.array_equal(mask, o_mask)
+    assert H.sha(ids) == g["ids_sha256"] and H.sha(mask) == g["mask_sha256"]
+
+
+@pytest.mark.parametrize("cfg", H.ALL_CONFIGS)
+def test_golden_configs_host_entry(golden, toks, cfg):
+    """Same through dnatok_encode_host (host buffers in and out)."""
+    g = golden["configs"][cfg]
+    name, flat, offs = H.config_inputs(cfg)
+    kw = H.call_to_kwargs(g["call"])
+    enc = toks[name].encode_host((flat, offs), **kw)
+    assert H.sha(enc["input_ids"]) == g["ids_sha256"]
+    assert H.sha(enc["attention_mask"]) == g["mask_sha256"]
+
+
+def test_ragged_output_config5(golden, toks):
+    g = golden["configs"]["cfg5_bpe32000_512reads"]
+    name, flat, offs = H.config_inputs("cfg5_bpe32000_512reads")
+    enc = run_device(toks[name], flat, offs, padding=False)
+    assert H.sha(enc["input_ids"].cpu().numpy()) == g["ragged_ids_sha256"]
+    assert H.sha(enc["offsets"].cpu().numpy()) == g["ragged_offsets_sha256"]
+    enc = toks[name].encode_host((flat, offs), padding=False)
+    assert H.sha(enc["input_ids"]) == g["ragged_ids_sha256"]
+    assert H.sha(enc["offsets"]) == g["ragged_offsets_sha256"]
+
+
+def test_config4_int32_ids(toks):
+    name, flat, offs = H.config_inputs("cfg4_byte_2x131072")
+    enc = run_device(toks[name], flat, offs, ids_dtype=torch.int32, return_attention_mask=False)
+    ids = enc["input_ids"].cpu().numpy()
+    assert ids.dtype == np.int32
+    assert np.array_equal(ids.reshape(-1), flat.astype(np.int32))
+
+
+@pytest.mark.parametrize("name", H.TOKENIZERS)
+def test_adversarial_strings(golden, toks, name):
+    strs = golden["adversarial_inputs"]
+    flat, offs = H.pack_strs(strs)
+    for key, special in (("plain", False), ("special", True)):
+        enc = run_device(toks[name], flat, offs, padding=False, add_special_tokens=special)
+        ids = enc["input_ids"].cpu().numpy()
+        oo = enc["offsets"].cpu().numpy()
+        got = [ids[oo[i]:oo[i + 1]].tolist() for i in range(len(strs))]
+        assert got == golden["adversarial"][name][key]
+        # and padded, both sides, with a mask
+        for left in (False, True):
+            toks[name].padding_side = "left" if left else "right"
+            try:
+                enc = run_device(toks[name], flat, offs, padding="longest", add_special_tokens=special)
+            finally:
+                toks[name].padding_side = "right"
+            o_ids, o_mask = H.oracle_batch(name, flat, offs, add_special=special, pad_left=left)
+            assert np.array_equal(enc["input_ids"].cpu().numpy(), o_ids)
+            assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
+
+
+@pytest.mark.parametrize("name", H.TOKENIZERS)
+@pytest.mark.parametrize("ids_dtype,mask_dtype", [("int64", "int64"), ("int32", "uint8"), ("int64", "int32")])
+def test_ragged_lengths_truncation_dtypes(toks, name, ids_dtype, mask_dtype):
+    rng = np.random.default_rng(3)
+    B = 97
+    lens = rng.integers(0, 3000, size=B)
+    lens[:6] = [0, 1, 5, 6, 7, 2999]
+    a = synth.config4(batch=B, length=3000, seed=9) if name == "byte" else synth.config1(batch=B, length=3000, seed=9)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat = np.concatenate([a[i, :lens[i]] for i in range(B)])
+    for kw in (dict(padding="longest"), dict(padding="max_length", max_length=333, truncation=True),
+               dict(padding="longest", max_length=101, truncation=True, add_special_tokens=False)):
+        enc = run_device(toks[name], flat, offs, ids_dtype=getattr(torch, ids_dtype),
+                         mask_dtype=getattr(torch, mask_dtype), **kw)
+        okw = dict(kw)
+        okw["add_special"] = okw.pop("add_special_tokens", True)
+        o_ids, o_mask = H.oracle_batch(name, flat, offs, id_dtype=getattr(np, ids_dtype),
+                                       mask_dtype=getattr(np, mask_dtype), **okw)
+        assert np.array_equal(enc["input_ids"].cpu().numpy(), o_ids)
+        assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
+        assert np.array_equal(enc["lengths"].cpu().numpy(), o_mask.sum(axis=1))
+
+
+@pytest.mark.parametrize("name", ["bpe4096", "bpe32000"])
+def test_bpe_homopolymers_and_long_words(toks, name):
+    words = [b"A" * n for n in (1, 2, 3, 4, 5, 8, 9, 31, 32, 33, 64, 100, 255, 256, 257, 1024, 4097)]
+    words += [b"AC" * 300, b"ACG" * 333, b"T" * 511 + b"A", b"N" * 70, b"ACGTNNNACGTnnacgt" * 40]
+    words += [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (255, 256, 257, 511, 513, 2047, 2049, 8191, 8193, 16384)]
+    flat, offs = H.pack_strs(words)
+    enc = run_device(toks[name], flat, offs, padding=False, add_special_tokens=False)
+    ids = enc["input_ids"].cpu().numpy()
+    oo = enc["offsets"].cpu().numpy()
+    want = H.oracle_rows(name, flat, offs)
+    for i in range(len(words)):
+        assert ids[oo[i]:oo[i + 1]].tolist() == want[i].tolist(), "word %d (len %d)" % (i, len(words[i]))
+
+
+def test_bpe_word_over_limit_raises(toks):
+    flat, offs = H.pack_strs([b"ACGT" * 5000])          # 20,000 bytes > 16,384
+    with pytest.raises(RuntimeError, match="word limit"):
+        run_device(toks["bpe4096"], flat, offs, padding=False)
+
+
+def test_clipping_without_truncation_raises(toks):
+    flat, offs = H.pack_strs(["ACGT" * 50, "AC"])
+    with pytest.raises(ValueError, match="truncation is off"):
+        run_device(toks["char"], flat, offs, padding="max_length", max_length=16)
+
+
+def test_determinism_and_empty_batch(toks):
+    name, flat, offs = H.config_inputs("cfg3_bpe4096")
+    a = run_device(toks[name], flat, offs)["input_ids"].clone()
+    b = run_device(toks[name], flat, offs)["input_ids"]
+    assert torch.equal(a, b)
+    enc = run_device(toks["char"], np.zeros(0, np.uint8), np.zeros(1, np.int64), padding="longest")
+    assert tuple(enc["input_ids"].shape) == (0, 0)
+
+
+def test_hf_call_surface_matches_live_hf(toks):
+    """B200Tokenizer.__call__ against the live Hugging Face tokenizer objects, same kwargs."""
+    strs = ["ACGTNACGT" * 7, "ACG", "", "TTTTNNNNACGTACGTAC", "acgtACGT"]
+    for name in H.TOKENIZERS:
+        hf, mine = H.hf(name), toks[name]
+        for kw in (dict(padding=True), dict(padding="max_length", max_length=24, truncation=True),
+                   dict(padding=True, add_special_tokens=False)):
+            want = hf(strs, return_tensors="np", **kw)
+            got = mine(strs, return_tensors="pt", **kw)
+            assert got["input_ids"].dtype == torch.int64 and got["attention_mask"].dtype == torch.int64
+            assert np.array_equal(got["input_ids"].cpu().numpy(), want["input_ids"]), (name, kw)
+            assert np.array_equal(got["attention_mask"].cpu().numpy(), want["attention_mask"]), (name, kw)
+        want = hf(strs)
+        got = mine(strs)
+        assert got["input_ids"] == [list(r) for r in want["input_ids"]]
+        assert mine.encode(strs[0]) == hf.encode(strs[0])
+        assert mine.pad_token_id == hf.pad_token_id
+
+
+def test_bpe_backend_dropin(toks):
+    """GPUTokBPEBackend / DnatokBpeKernel keep the reference's return contract."""
+    from dnatok_b200.gputok_bpe_backend import DnatokBpeKernel, GPUTokBPEBackend
+    hf = H.hf("bpe4096")
+    assert GPUTokBPEBackend.is_supported(hf)
+    be = GPUTokBPEBackend(hf, engine="dnatok")
+    strs = synth.rows_to_strings(*synth.pack_rows(synth.config3(batch=33, length=700, seed=4))) + ["ACGTN" * 3, "A"]
+    ids, mask = be.encode_batch(strs, device="cuda")
+    assert ids.dtype == torch.int64 and mask.dtype == torch.uint8 and ids.is_cuda
+    want = hf(strs, padding=True, add_special_tokens=False, return_tensors="np")
+    assert np.array_equal(ids.cpu().numpy(), want["input_ids"])
+    assert np.array_equal(mask.cpu().numpy(), want["attention_mask"].astype(np.uint8))
+    assert (be.pad_id, be.unk_id, be.vocab_size) == (hf.pad_token_id, hf.unk_token_id, hf.vocab_size)
+    with pytest.raises(ValueError):
+        be.encode_batch([])
+    k = DnatokBpeKernel.from_spec(H.spec("bpe4096"))
+    kids, klens = k.tokenize_batch(strs)
+    assert kids.dtype == torch.int32 and klens.dtype == torch.int32
+    lens = want["attention_mask"].sum(axis=1)
+    assert np.array_equal(klens.cpu().numpy(), lens)
+    kid = kids.cpu().numpy()
+    for i, n in enumerate(lens):
+        assert np.array_equal(kid[i, :n], want["input_ids"][i, :n]) and not kid[i, n:].any()
