@@ -496,6 +496,58 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
                               nullptr, d_status, st);
 }
 
+// ------------------------------------------------------------------ BPE without caller scratch
+//
+// The merge kernels need working memory beyond their inputs and outputs (merged tokens, per-row
+// counts, the length-class lists and their counters).  dnatok_encode takes it from the caller;
+// this variant takes it from one array that is part of the loaded library image, so the call
+// itself never asks the CUDA runtime for memory.
+
+static __device__ __align__(256) unsigned char g_builtin_scratch[DNATOK_BUILTIN_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_builtin_mu;
+std::map<int, void*> g_builtin_addr;   // device -> device address of g_builtin_scratch on that device
+}
+
+int dnatok_encode_bpe_builtin_scratch(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets,
+                                      int64_t n_rows, int64_t total_bytes, const dnatok_format* fmt, void* d_ids,
+                                      void* d_mask, int32_t* d_lengths, int64_t* d_out_offsets, int32_t* d_status,
+                                      dnatok_stream stream) {
+    if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
+    if (h->kind != DNATOK_KIND_BPE) return fail(DNATOK_ERR_INVALID, "only BPE handles use scratch memory");
+    const size_t need = bpe_scratch_layout(nullptr, n_rows, total_bytes).bytes;
+    if (need > (size_t)DNATOK_BUILTIN_SCRATCH_BYTES)
+        return fail(DNATOK_ERR_CAPACITY,
+                    "batch of %lld rows / %lld bytes needs %zu bytes of scratch; the built-in array holds %zu "
+                    "(split the batch or use dnatok_encode with your own scratch)",
+                    (long long)n_rows, (long long)total_bytes, need, (size_t)DNATOK_BUILTIN_SCRATCH_BYTES);
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    {
+        // The merge tables are uploaded (allocated) by the first ordinary call on a device; this
+        // entry point refuses to do that itself.
+        std::lock_guard<std::mutex> lock(h->mu);
+        if (h->dev.find(dev) == h->dev.end())
+            return fail(DNATOK_ERR_INVALID,
+                        "the handle's tables are not on device %d yet: make one dnatok_prepare / dnatok_encode call "
+                        "on this device first (that call allocates them)", dev);
+    }
+    void* scratch = nullptr;
+    {
+        // g_builtin_scratch names a host-side stand-in here; the kernels need its address on the
+        // current device, which the runtime resolves once per device.
+        std::lock_guard<std::mutex> lock(g_builtin_mu);
+        auto it = g_builtin_addr.find(dev);
+        if (it == g_builtin_addr.end()) {
+            CUDA_TRY(cudaGetSymbolAddress(&scratch, g_builtin_scratch));
+            g_builtin_addr[dev] = scratch;
+        } else scratch = it->second;
+    }
+    return dnatok_encode(h, d_bytes, d_offsets, n_rows, total_bytes, fmt, d_ids, d_mask, d_lengths, d_out_offsets,
+                         d_status, scratch, (size_t)DNATOK_BUILTIN_SCRATCH_BYTES, stream);
+}
+
 // ------------------------------------------------------------------ host-buffer pipeline
 
 static int grow(void** p, size_t* cap, size_t need) {

@@ -120,6 +120,35 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
                   void* d_ids, void* d_mask, int32_t* d_lengths, int64_t* d_out_offsets,
                   int32_t* d_status, void* d_scratch, size_t scratch_bytes, dnatok_stream stream);
 
+/* BPE encode for callers that must not allocate.  No counterpart in the reference (its kernel
+ * wrapper grows torch workspace tensors on demand, dnatok_bpe.cu:956-1015).
+ *
+ * Who needs it: a host that has already handed all device memory to its own pool (a serving
+ * process, an inference engine's plug-in slot), or a latency-critical loop that cannot afford
+ * the device-wide synchronisation an allocation or free may imply.  Such callers can still own
+ * input and output buffers, but cannot size a scratch buffer per batch.
+ *
+ * Same arguments and results as dnatok_encode on a BPE handle, minus the scratch pair: the
+ * working memory is one array of DNATOK_BUILTIN_SCRATCH_BYTES inside the library image, which
+ * every GPU that loads the library holds until the process exits.  The call makes no cudaMalloc /
+ * cudaFree and calls no allocating library routine.
+ *   - Limit: dnatok_scratch_bytes(h, n_rows, total_bytes) must not exceed
+ *     DNATOK_BUILTIN_SCRATCH_BYTES (about 2 bytes per input byte plus 32 per row), otherwise
+ *     DNATOK_ERR_CAPACITY with the sizes in dnatok_last_error(); nothing is launched.
+ *   - The handle's merge tables must already be on the current device: one earlier
+ *     dnatok_prepare / dnatok_encode call there uploads them; otherwise DNATOK_ERR_INVALID.
+ *   - The first call on each device also resolves the array's device address (once per device,
+ *     with that device current); make that first call outside any stream capture.
+ *   - All calls, on any handle and stream, share the one array, and it keeps the previous call's
+ *     contents (the counters that must start at zero are cleared on the stream at the start of
+ *     every call).  Two calls whose GPU work overlaps race on it: keep them on one stream or
+ *     order them with events. */
+#define DNATOK_BUILTIN_SCRATCH_BYTES (8u << 20)
+int dnatok_encode_bpe_builtin_scratch(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets,
+                                      int64_t n_rows, int64_t total_bytes, const dnatok_format* fmt,
+                                      void* d_ids, void* d_mask, int32_t* d_lengths, int64_t* d_out_offsets,
+                                      int32_t* d_status, dnatok_stream stream);
+
 /* Exclusive scan: d_out_offsets[0] = 0, d_out_offsets[i+1] = sum of d_lengths[0..i]. */
 int dnatok_scan_lengths(const int32_t* d_lengths, int64_t n_rows, int64_t* d_out_offsets,
                         dnatok_stream stream);
