@@ -269,13 +269,43 @@ int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, 
     return 0;
 }
 
+template <typename IdT, int K>
+void launch_kmer_warp_k(const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets, int64_t n_rows,
+                        int64_t total_bytes, const RowFormat& rf, void* ids, void* mask, const int32_t* lengths_in,
+                        int32_t* lengths_out, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
+    const unsigned grid = (unsigned)((n_rows + KW_WARPS - 1) / KW_WARPS);
+    kmer_warp_rows_kernel<IdT, K><<<grid, KW_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, total_bytes, d.kmer_ids, d.lut256, rf,
+                                                                 (IdT*)ids, mask, lengths_in, lengths_out, out_offsets, status);
+}
+
+template <typename IdT>
+void launch_kmer_warp(int k, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets, int64_t n_rows,
+                      int64_t total_bytes, const RowFormat& rf, void* ids, void* mask, const int32_t* lengths_in,
+                      int32_t* lengths_out, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
+#define KCASE(KK) case KK: launch_kmer_warp_k<IdT, KK>(d, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in, \
+                                                       lengths_out, out_offsets, status, st); break;
+    switch (k) { KCASE(1) KCASE(2) KCASE(3) KCASE(4) KCASE(5) KCASE(6) KCASE(7) KCASE(8) }
+#undef KCASE
+}
+
+// Rows of ordinary length go one per warp; batches of very long rows keep the block-per-row kernel.
+constexpr int64_t KMER_WARP_MAX_AVG_LEN = 32768;
+
 template <bool COUNT_ONLY>
 int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
-                int64_t n_rows, const RowFormat& rf, int id_bits, void* ids, void* mask,
+                int64_t n_rows, int64_t total_bytes, const RowFormat& rf, int id_bits, void* ids, void* mask,
                 const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets,
                 int32_t* status, cudaStream_t st) {
     if (n_rows == 0) return 0;
     const int k = h->k;
+    if (!COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
+        if (id_bits == 64) launch_kmer_warp<int64_t>(k, d, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
+                                                     lengths_out, out_offsets, status, st);
+        else launch_kmer_warp<int32_t>(k, d, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
+                                       lengths_out, out_offsets, status, st);
+        LAUNCH_CHECK("kmer_warp_rows_kernel");
+        return 0;
+    }
     const size_t smem = (size_t)((KMER_TILE_W * k + 32 + 15) & ~15) + (size_t)KMER_TILE_W * k * 4;
     const unsigned grid = (unsigned)(n_rows < (int64_t)d.sm_count * 64 ? n_rows : (int64_t)d.sm_count * 64);
     if (id_bits == 64)
@@ -413,7 +443,7 @@ int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_of
         case DNATOK_KIND_CHAR:
             return launch_span_lengths(d_offsets, nullptr, n_rows, rf, d_lengths, d_status, st);
         case DNATOK_KIND_KMER:
-            return launch_kmer<true>(h, *d, d_bytes, d_offsets, n_rows, rf, 64, nullptr, nullptr, nullptr, d_lengths,
+            return launch_kmer<true>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, 64, nullptr, nullptr, nullptr, d_lengths,
                                      nullptr, d_status, st);
         default: {
             if (int rc = run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, st))
@@ -445,7 +475,7 @@ int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
         case DNATOK_KIND_KMER:
             if (fmt->out_stride > 0 && fmt->pad_left && !d_lengths)
                 return fail(DNATOK_ERR_INVALID, "left padding needs d_lengths from dnatok_prepare");
-            return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, rf, fmt->id_bits, d_ids, d_mask, d_lengths,
+            return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, d_lengths,
                                       nullptr, d_out_offsets, d_status, st);
         default: {
             if (!d_scratch) return fail(DNATOK_ERR_SCRATCH, "BPE write needs the scratch filled by dnatok_prepare");
@@ -492,7 +522,7 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     if (h->kind == DNATOK_KIND_CHAR)
         return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits, d_ids,
                                           d_mask, d_lengths, nullptr, d_status, st);
-    return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
+    return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
                               nullptr, d_status, st);
 }
 

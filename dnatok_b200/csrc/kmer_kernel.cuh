@@ -177,3 +177,194 @@ kmer_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 }
 
 }  // namespace dnatok
+
+// ---------------------------------------------------------------------------------------------
+// Warp-per-row variant for batches of short and medium rows (reads, 6,000-bp windows): no shared
+// memory and no block-wide barrier.  Per iteration a warp covers 64 windows; each lane owns two
+// consecutive windows (2K bytes), fetched as aligned 32-bit words and re-aligned with funnel
+// shifts, turned into 2-bit codes four bytes at a time, and - when every window of the chunk is a
+// clean k-mer, the common case - stored as one 16-byte pair of ids at position base + 2*lane.  A
+// chunk holding any other window (N, lower case, the len%K tail) takes the general route: per-lane
+// token counts, a warp scan, scalar stores.
+namespace dnatok {
+
+constexpr int KW_WARPS = 8;
+
+// 2-bit codes of four ASCII bytes at once (A C G T -> 0 1 2 3 in each byte's low bits), and a word
+// that is zero exactly in the bytes that are one of A, C, G, T.
+__device__ __forceinline__ void acgt_codes4(uint32_t w, uint32_t* code, uint32_t* diff) {
+    uint32_t c = (w >> 1) & 0x03030303u;
+    c ^= (c >> 1) & 0x01010101u;
+    const uint32_t c0 = c & 0x01010101u, c1 = (c >> 1) & 0x01010101u, c01 = c0 & c1;
+    // 'A' + {0, 2, 6, 19}[code] is the only byte value that maps to this code legitimately
+    const uint32_t expect = 0x41414141u + 2u * c0 + 6u * c1 + 11u * c01;
+    *code = c;
+    *diff = w ^ expect;
+}
+
+// Gather the four 2-bit codes of a word into 8 bits, first byte most significant.
+__device__ __forceinline__ uint32_t pack_codes4(uint32_t code) { return (code * 0x40100401u) >> 24; }
+
+template <typename IdT> struct IdPair;
+template <> struct IdPair<int64_t> { using type = longlong2; };
+template <> struct IdPair<int32_t> { using type = int2; };
+
+template <typename T, typename F>
+__device__ __forceinline__ void warp_write_run(T* dst, int64_t m, int lane, F f) {
+    constexpr int N = Vec16<T>::N;
+    if (m <= 0) return;
+    int64_t head = (N - (int64_t)((reinterpret_cast<uintptr_t>(dst) / sizeof(T)) % N)) % N;
+    if (head > m) head = m;
+    for (int64_t j = lane; j < head; j += 32) dst[j] = f(j);
+    const int64_t nv = (m - head) / N;
+    for (int64_t v = lane; v < nv; v += 32) {
+        T vals[N];
+        const int64_t j0 = head + v * N;
+#pragma unroll
+        for (int e = 0; e < N; ++e) vals[e] = f(j0 + e);
+        store_vec<T>(dst + j0, vals);
+    }
+    for (int64_t j = head + nv * N + lane; j < m; j += 32) dst[j] = f(j);
+}
+
+template <typename M>
+__device__ __forceinline__ void warp_mask_row(M* row, int64_t stride, int64_t lo, int64_t hi, int lane) {
+    warp_write_run<M>(row, stride, lane, [=](int64_t j) { return (M)((j >= lo && j < hi) ? 1 : 0); });
+}
+
+template <typename IdT, int K>
+__global__ void __launch_bounds__(KW_WARPS * 32)
+kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                      int64_t total_bytes, const int32_t* __restrict__ kmer_ids,
+                      const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
+                      void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
+                      int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
+                      int32_t* __restrict__ status) {
+    constexpr int NW = (2 * K + 3 + 3) / 4;            // aligned words covering 2K bytes at any byte offset
+    constexpr uint32_t IDX_MASK = (1u << (2 * K)) - 1u;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const bool has_cls = f.cls_id >= 0, has_sep = f.sep_id >= 0;
+    const int n_special = (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
+    const bool ragged = f.out_stride == 0;
+    const int64_t off = offsets[row];
+    const int64_t len = offsets[row + 1] - off;
+    const int64_t n_win = (len + K - 1) / K;
+    const int64_t cap = f.cap_content;
+    const uint8_t* src = bytes + off;
+
+    IdT* orow = ragged ? ids + out_offsets[row] : ids + row * f.out_stride;
+    int64_t shift = 0;
+    if (!ragged && f.pad_left) shift = f.out_stride - lengths_in[row];
+    IdT* dst = orow + shift + (has_cls ? 1 : 0);
+    const bool pair_aligned = (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(IdT))) == 0;
+
+    int64_t base = 0;          // content tokens placed so far (uncapped)
+    int64_t w0 = 0;
+    for (; w0 < n_win && base < cap; w0 += 64) {
+        const int64_t wa = w0 + 2 * lane;               // this lane's first window
+        const int64_t p = wa * K;                       // its first byte within the row
+        // bytes of this lane's two windows that exist
+        int64_t have = len - p;
+        have = have < 0 ? 0 : (have > 2 * K ? 2 * K : have);
+        int lenA = (int)(have < K ? have : K), lenB = (int)have - lenA;
+        uint32_t idxA = 0, idxB = 0;
+        bool cleanA = false, cleanB = false;
+        const bool wide_ok = (off + p + 4 * NW <= total_bytes) && have == 2 * K;   // the aligned words stay inside the buffer
+        if (wide_ok) {
+            const uint8_t* g = src + p;
+            const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
+            uint32_t w[NW];
+#pragma unroll
+            for (int i = 0; i < NW; ++i) w[i] = __ldg(gw + i);
+            uint32_t P = 0, dA = 0, dB = 0;
+#pragma unroll
+            for (int i = 0; i < NW - 1; ++i) {
+                const uint32_t r = __funnelshift_r(w[i], w[i + 1], sh);     // bytes 4i .. 4i+3 of the pair
+                uint32_t c, d;
+                acgt_codes4(r, &c, &d);
+                if (i < 4) P |= pack_codes4(c) << (24 - 8 * i);
+                // byte b of this word belongs to window A when 4i+b < K, to window B when K <= 4i+b < 2K
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int pos = 4 * i + b;
+                    if (pos < K) dA |= d & (0xFFu << (8 * b));
+                    else if (pos < 2 * K) dB |= d & (0xFFu << (8 * b));
+                }
+            }
+            cleanA = dA == 0;
+            cleanB = dB == 0;
+            idxA = (P >> (32 - 2 * K)) & IDX_MASK;
+            idxB = (P >> (32 - 4 * K)) & IDX_MASK;
+        } else if (have > 0) {
+            // edge of the row or of the buffer: byte loads
+            bool okA = lenA == K, okB = lenB == K;
+            for (int i = 0; i < lenA; ++i) { const int c = kmer_code(__ldg(src + p + i)); okA &= c < 4; idxA = (idxA << 2) | (uint32_t)(c & 3); }
+            for (int i = 0; i < lenB; ++i) { const int c = kmer_code(__ldg(src + p + K + i)); okB &= c < 4; idxB = (idxB << 2) | (uint32_t)(c & 3); }
+            cleanA = okA; cleanB = okB;
+        }
+        const int cntA = lenA == 0 ? 0 : (cleanA ? 1 : lenA);
+        const int cntB = lenB == 0 ? 0 : (cleanB ? 1 : lenB);
+        const bool simple = (lenA == 0 || cleanA) && (lenB == 0 || cleanB);
+        if (__all_sync(0xffffffffu, simple)) {
+            // every window of the chunk is one token: lane's tokens sit at base + 2*lane (+1)
+            const int64_t pos = base + 2 * lane;
+            const IdT a = lenA ? (IdT)__ldg(kmer_ids + idxA) : (IdT)0;
+            const IdT b = lenB ? (IdT)__ldg(kmer_ids + idxB) : (IdT)0;
+            if (lenB && pos + 1 < cap && pair_aligned && ((pos & 1) == 0)) {
+                typename IdPair<IdT>::type v;
+                v.x = a; v.y = b;
+                *reinterpret_cast<typename IdPair<IdT>::type*>(dst + pos) = v;
+            } else {
+                if (lenA && pos < cap) dst[pos] = a;
+                if (lenB && pos + 1 < cap) dst[pos + 1] = b;
+            }
+            int64_t chunk = n_win - w0;
+            base += chunk < 64 ? chunk : 64;
+        } else {
+            int my = cntA + cntB, x = my;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, x, d);
+                if (lane >= d) x += y;
+            }
+            const int total = __shfl_sync(0xffffffffu, x, 31);
+            int64_t pos = base + x - my;
+            if (lenA) {
+                if (cleanA) { if (pos < cap) dst[pos] = (IdT)__ldg(kmer_ids + idxA); ++pos; }
+                else for (int i = 0; i < lenA; ++i, ++pos) if (pos < cap) dst[pos] = (IdT)__ldg(single_ids + __ldg(src + p + i));
+            }
+            if (lenB) {
+                if (cleanB) { if (pos < cap) dst[pos] = (IdT)__ldg(kmer_ids + idxB); ++pos; }
+                else for (int i = 0; i < lenB; ++i, ++pos) if (pos < cap) dst[pos] = (IdT)__ldg(single_ids + __ldg(src + p + K + i));
+            }
+            base += total;
+        }
+    }
+
+    const int64_t n = base < cap ? base : cap;
+    const int64_t T = n + n_special;
+    if (lane == 0) {
+        if (lengths_out) lengths_out[row] = (int32_t)T;
+        if (status && f.clip_is_error && (base > cap || w0 < n_win)) atomicOr(status + row, 4);
+        if (has_cls) orow[shift] = (IdT)f.cls_id;
+        if (has_sep) orow[shift + T - 1] = (IdT)f.sep_id;
+    }
+    if (!ragged) {
+        const IdT pad = (IdT)f.pad_id;
+        if (f.pad_left) warp_write_run<IdT>(orow, shift, lane, [=](int64_t) { return pad; });
+        else warp_write_run<IdT>(orow + T, f.out_stride - T, lane, [=](int64_t) { return pad; });
+        if (f.mask_bits == 64) warp_mask_row<int64_t>((int64_t*)mask + row * f.out_stride, f.out_stride, shift, shift + T, lane);
+        else if (f.mask_bits == 32) warp_mask_row<int32_t>((int32_t*)mask + row * f.out_stride, f.out_stride, shift, shift + T, lane);
+        else if (f.mask_bits == 8) warp_mask_row<uint8_t>((uint8_t*)mask + row * f.out_stride, f.out_stride, shift, shift + T, lane);
+    } else if (mask && f.mask_bits) {
+        const int64_t o = out_offsets[row];
+        if (f.mask_bits == 64) warp_write_run<int64_t>((int64_t*)mask + o, T, lane, [](int64_t) { return (int64_t)1; });
+        else if (f.mask_bits == 32) warp_write_run<int32_t>((int32_t*)mask + o, T, lane, [](int64_t) { return (int32_t)1; });
+        else warp_write_run<uint8_t>((uint8_t*)mask + o, T, lane, [](int64_t) { return (uint8_t)1; });
+    }
+}
+
+}  // namespace dnatok

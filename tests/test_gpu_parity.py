@@ -200,3 +200,62 @@ def test_bpe_backend_dropin(toks):
     kid = kids.cpu().numpy()
     for i, n in enumerate(lens):
         assert np.array_equal(kid[i, :n], want["input_ids"][i, :n]) and not kid[i, n:].any()
+
+
+def _kmer_spec(k):
+    """A synthetic k-mer vocabulary laid out like the 6-mer one: specials, 4**k k-mers, then A C G T N."""
+    from dnatok_b200.tables import Specials, TokenizerSpec
+    lut = np.full(256, 1, np.int32)
+    for i, c in enumerate("ACGTN"):
+        lut[ord(c)] = 5 + 4 ** k + i
+    rng = np.random.default_rng(k)
+    return TokenizerSpec("kmer", Specials(0, 1, 2, 3), 10 + 4 ** k, lut, k=k,
+                         kmer_ids=(5 + rng.permutation(4 ** k)).astype(np.int32))
+
+
+@pytest.mark.parametrize("k", [1, 2, 3, 4, 5, 7, 8])
+def test_kmer_other_k(k):
+    """Every window width the kernel is instantiated for, ragged rows, odd byte alignments."""
+    from dnatok_b200.tokenizer import B200Tokenizer
+    from oracle import oracle
+    spec = _kmer_spec(k)
+    tok = B200Tokenizer(spec, device=0)
+    rng = np.random.default_rng(100 + k)
+    B = 61
+    lens = rng.integers(0, 1500, size=B)
+    lens[:5] = [0, 1, k - 1 if k > 1 else 1, k, k + 1]
+    a = synth.config1(batch=B, length=1500, seed=k)
+    a[3, :] = np.frombuffer(b"ACGT", np.uint8)[rng.integers(0, 4, 1500)]           # an all-clean row
+    a[7, 100:160] |= 0x20                                                          # lower-case stretch
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat = np.concatenate([a[i, :lens[i]] for i in range(B)])
+    ids, counts = oracle.encode_ragged("kmer", flat, offs, lut256=spec.lut256, k=k, kmer_ids=spec.kmer_ids)
+    rows = oracle.rows(ids, offs, counts)
+    for kw in (dict(padding="longest"), dict(padding="max_length", max_length=97, truncation=True),
+               dict(padding="longest", add_special_tokens=False, ids_dtype=torch.int32)):
+        enc = run_device(tok, flat, offs, **kw)
+        want_ids, want_mask = oracle.assemble(rows, pad_id=0, cls_id=2, sep_id=3,
+                                              add_special=kw.get("add_special_tokens", True),
+                                              max_length=kw.get("max_length", 0), truncation=kw.get("truncation", False),
+                                              padding=kw["padding"])
+        assert np.array_equal(enc["input_ids"].cpu().numpy(), want_ids), kw
+        assert np.array_equal(enc["attention_mask"].cpu().numpy(), want_mask), kw
+    enc = run_device(tok, flat, offs, padding=False)
+    got = enc["input_ids"].cpu().numpy()
+    oo = enc["offsets"].cpu().numpy()
+    want = oracle.assemble(rows, pad_id=0, cls_id=2, sep_id=3, padding=False)
+    for i in range(B):
+        assert np.array_equal(got[oo[i]:oo[i + 1]], want[i]), i
+
+
+def test_kmer_very_long_rows_use_block_kernel(toks):
+    """Average row length above the warp-per-row limit: the block-per-row kernel."""
+    a = synth.config2(batch=3, length=100003, seed=77)
+    flat, offs = synth.pack_rows(a)
+    for kw in (dict(padding="longest", add_special_tokens=False), dict(padding="max_length", max_length=9000, truncation=True)):
+        enc = run_device(toks["kmer6"], flat, offs, **kw)
+        okw = dict(kw)
+        okw["add_special"] = okw.pop("add_special_tokens", True)
+        o_ids, o_mask = H.oracle_batch("kmer6", flat, offs, **okw)
+        assert np.array_equal(enc["input_ids"].cpu().numpy(), o_ids)
+        assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
