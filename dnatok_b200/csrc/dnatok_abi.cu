@@ -76,6 +76,7 @@ struct dnatok_handle {
     std::vector<int32_t> lut256;
     int k = 0;
     std::vector<int32_t> kmer_ids;
+    int32_t kmer_affine_base = -1;     // >= 0 when kmer_ids[i] == base + i for every i
     BpeHostTable bpe;
     std::mutex mu;
     std::map<int, DeviceTables> dev;
@@ -270,20 +271,30 @@ int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, 
 }
 
 template <typename IdT, int K>
-void launch_kmer_warp_k(const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets, int64_t n_rows,
-                        int64_t total_bytes, const RowFormat& rf, void* ids, void* mask, const int32_t* lengths_in,
-                        int32_t* lengths_out, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
+void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_t* bytes, const int64_t* offsets,
+                        int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
+                        const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets, int32_t* status,
+                        cudaStream_t st) {
     const unsigned grid = (unsigned)((n_rows + KW_WARPS - 1) / KW_WARPS);
-    kmer_warp_rows_kernel<IdT, K><<<grid, KW_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, total_bytes, d.kmer_ids, d.lut256, rf,
-                                                                 (IdT*)ids, mask, lengths_in, lengths_out, out_offsets, status);
+    const bool fuse = mask && rf.mask_bits == (int)sizeof(IdT) * 8;
+    const bool affine = affine_base >= 0;
+#define KLAUNCH(A, F) kmer_warp_rows_kernel<IdT, K, A, F><<<grid, KW_WARPS * 32, 0, st>>>(                          \
+        bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
+        lengths_out, out_offsets, status)
+    if (affine && fuse) KLAUNCH(true, true);
+    else if (affine) KLAUNCH(true, false);
+    else if (fuse) KLAUNCH(false, true);
+    else KLAUNCH(false, false);
+#undef KLAUNCH
 }
 
 template <typename IdT>
-void launch_kmer_warp(int k, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets, int64_t n_rows,
-                      int64_t total_bytes, const RowFormat& rf, void* ids, void* mask, const int32_t* lengths_in,
-                      int32_t* lengths_out, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
-#define KCASE(KK) case KK: launch_kmer_warp_k<IdT, KK>(d, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in, \
-                                                       lengths_out, out_offsets, status, st); break;
+void launch_kmer_warp(int k, const DeviceTables& d, int32_t affine_base, const uint8_t* bytes, const int64_t* offsets,
+                      int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
+                      const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets, int32_t* status,
+                      cudaStream_t st) {
+#define KCASE(KK) case KK: launch_kmer_warp_k<IdT, KK>(d, affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, \
+                                                       lengths_in, lengths_out, out_offsets, status, st); break;
     switch (k) { KCASE(1) KCASE(2) KCASE(3) KCASE(4) KCASE(5) KCASE(6) KCASE(7) KCASE(8) }
 #undef KCASE
 }
@@ -299,9 +310,9 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
     if (n_rows == 0) return 0;
     const int k = h->k;
     if (!COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
-        if (id_bits == 64) launch_kmer_warp<int64_t>(k, d, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
+        if (id_bits == 64) launch_kmer_warp<int64_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
                                                      lengths_out, out_offsets, status, st);
-        else launch_kmer_warp<int32_t>(k, d, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
+        else launch_kmer_warp<int32_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
                                        lengths_out, out_offsets, status, st);
         LAUNCH_CHECK("kmer_warp_rows_kernel");
         return 0;
@@ -370,6 +381,9 @@ int dnatok_create_kmer(int k, const int32_t* kmer_ids, const int32_t single_ids[
     h->kind = DNATOK_KIND_KMER; h->sp = *sp; h->k = k;
     h->lut256.assign(single_ids, single_ids + 256);
     h->kmer_ids.assign(kmer_ids, kmer_ids + ((size_t)1 << (2 * k)));
+    bool affine = kmer_ids[0] >= 0;
+    for (size_t i = 0; i < h->kmer_ids.size() && affine; ++i) affine = kmer_ids[i] == kmer_ids[0] + (int32_t)i;
+    h->kmer_affine_base = affine ? kmer_ids[0] : -1;
     *out = h;
     return DNATOK_OK;
 }

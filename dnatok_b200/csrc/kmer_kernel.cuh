@@ -232,16 +232,19 @@ __device__ __forceinline__ void warp_mask_row(M* row, int64_t stride, int64_t lo
     warp_write_run<M>(row, stride, lane, [=](int64_t j) { return (M)((j >= lo && j < hi) ? 1 : 0); });
 }
 
-template <typename IdT, int K>
+// AFFINE: the 4**K table is base + index (checked on the host), so no gather is needed.
+// FUSE_MASK: the mask has the ids' element type and is stored next to each id in the main loop.
+template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
 __global__ void __launch_bounds__(KW_WARPS * 32)
 kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
-                      int64_t total_bytes, const int32_t* __restrict__ kmer_ids,
+                      int64_t total_bytes, const int32_t* __restrict__ kmer_ids, int32_t affine_base,
                       const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
                       void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
                       int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
                       int32_t* __restrict__ status) {
     constexpr int NW = (2 * K + 3 + 3) / 4;            // aligned words covering 2K bytes at any byte offset
     constexpr uint32_t IDX_MASK = (1u << (2 * K)) - 1u;
+    using Pair = typename IdPair<IdT>::type;
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
     if (row >= n_rows) return;
@@ -249,31 +252,36 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
     const int n_special = (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
     const bool ragged = f.out_stride == 0;
     const int64_t off = offsets[row];
-    const int64_t len = offsets[row + 1] - off;
-    const int64_t n_win = (len + K - 1) / K;
-    const int64_t cap = f.cap_content;
+    const int64_t len64 = offsets[row + 1] - off;
+    const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);       // rows are < 2 GiB
+    const int n_win = (len + K - 1) / K;
+    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
     const uint8_t* src = bytes + off;
+    const int64_t room_total = total_bytes - off;      // bytes from the row start to the end of the buffer
 
     IdT* orow = ragged ? ids + out_offsets[row] : ids + row * f.out_stride;
-    int64_t shift = 0;
-    if (!ragged && f.pad_left) shift = f.out_stride - lengths_in[row];
+    int shift = 0;
+    if (!ragged && f.pad_left) shift = (int)f.out_stride - lengths_in[row];
     IdT* dst = orow + shift + (has_cls ? 1 : 0);
+    IdT* mdst = FUSE_MASK ? reinterpret_cast<IdT*>(mask) + (dst - ids) : nullptr;
     const bool pair_aligned = (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(IdT))) == 0;
 
-    int64_t base = 0;          // content tokens placed so far (uncapped)
-    int64_t w0 = 0;
-    for (; w0 < n_win && base < cap; w0 += 64) {
-        const int64_t wa = w0 + 2 * lane;               // this lane's first window
-        const int64_t p = wa * K;                       // its first byte within the row
-        // bytes of this lane's two windows that exist
-        int64_t have = len - p;
-        have = have < 0 ? 0 : (have > 2 * K ? 2 * K : have);
-        int lenA = (int)(have < K ? have : K), lenB = (int)have - lenA;
-        uint32_t idxA = 0, idxB = 0;
-        bool cleanA = false, cleanB = false;
-        const bool wide_ok = (off + p + 4 * NW <= total_bytes) && have == 2 * K;   // the aligned words stay inside the buffer
-        if (wide_ok) {
-            const uint8_t* g = src + p;
+    int base = 0;              // content tokens placed so far (uncapped)
+    const int n_chunks = (n_win + 63) >> 6;
+    const int n_full = len / K;                          // complete windows
+    bool clipped = false;
+
+    // Windows of one chunk for this lane: lengths, table indices, cleanliness.
+    struct Two { int lenA, lenB; uint32_t idxA, idxB; bool cleanA, cleanB; int p; };
+    auto decode = [&](int chunk) {
+        Two t;
+        const int wa = chunk * 64 + 2 * lane;
+        t.p = wa * K;
+        t.idxA = 0; t.idxB = 0;
+        // both windows complete and the aligned words inside the buffer: the wide route
+        if (wa + 2 <= n_full && (int64_t)t.p + 2 * K + 8 <= room_total) {
+            t.lenA = K; t.lenB = K;
+            const uint8_t* g = src + t.p;
             const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;
             const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
             uint32_t w[NW];
@@ -285,45 +293,55 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                 const uint32_t r = __funnelshift_r(w[i], w[i + 1], sh);     // bytes 4i .. 4i+3 of the pair
                 uint32_t c, d;
                 acgt_codes4(r, &c, &d);
-                if (i < 4) P |= pack_codes4(c) << (24 - 8 * i);
+                P |= pack_codes4(c) << (24 - 8 * i);
                 // byte b of this word belongs to window A when 4i+b < K, to window B when K <= 4i+b < 2K
+                uint32_t mA = 0, mB = 0;
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     const int pos = 4 * i + b;
-                    if (pos < K) dA |= d & (0xFFu << (8 * b));
-                    else if (pos < 2 * K) dB |= d & (0xFFu << (8 * b));
+                    if (pos < K) mA |= 0xFFu << (8 * b);
+                    else if (pos < 2 * K) mB |= 0xFFu << (8 * b);
                 }
+                dA |= d & mA;
+                dB |= d & mB;
             }
-            cleanA = dA == 0;
-            cleanB = dB == 0;
-            idxA = (P >> (32 - 2 * K)) & IDX_MASK;
-            idxB = (P >> (32 - 4 * K)) & IDX_MASK;
-        } else if (have > 0) {
-            // edge of the row or of the buffer: byte loads
-            bool okA = lenA == K, okB = lenB == K;
-            for (int i = 0; i < lenA; ++i) { const int c = kmer_code(__ldg(src + p + i)); okA &= c < 4; idxA = (idxA << 2) | (uint32_t)(c & 3); }
-            for (int i = 0; i < lenB; ++i) { const int c = kmer_code(__ldg(src + p + K + i)); okB &= c < 4; idxB = (idxB << 2) | (uint32_t)(c & 3); }
-            cleanA = okA; cleanB = okB;
-        }
-        const int cntA = lenA == 0 ? 0 : (cleanA ? 1 : lenA);
-        const int cntB = lenB == 0 ? 0 : (cleanB ? 1 : lenB);
-        const bool simple = (lenA == 0 || cleanA) && (lenB == 0 || cleanB);
-        if (__all_sync(0xffffffffu, simple)) {
-            // every window of the chunk is one token: lane's tokens sit at base + 2*lane (+1)
-            const int64_t pos = base + 2 * lane;
-            const IdT a = lenA ? (IdT)__ldg(kmer_ids + idxA) : (IdT)0;
-            const IdT b = lenB ? (IdT)__ldg(kmer_ids + idxB) : (IdT)0;
-            if (lenB && pos + 1 < cap && pair_aligned && ((pos & 1) == 0)) {
-                typename IdPair<IdT>::type v;
-                v.x = a; v.y = b;
-                *reinterpret_cast<typename IdPair<IdT>::type*>(dst + pos) = v;
-            } else {
-                if (lenA && pos < cap) dst[pos] = a;
-                if (lenB && pos + 1 < cap) dst[pos + 1] = b;
-            }
-            int64_t chunk = n_win - w0;
-            base += chunk < 64 ? chunk : 64;
+            t.cleanA = dA == 0;
+            t.cleanB = dB == 0;
+            t.idxA = (P >> (32 - 2 * K)) & IDX_MASK;
+            t.idxB = (P >> (32 - 4 * K)) & IDX_MASK;
         } else {
+            // edge of the row or of the buffer: byte loads
+            int have = len - t.p;
+            have = have < 0 ? 0 : (have > 2 * K ? 2 * K : have);
+            t.lenA = have < K ? have : K;
+            t.lenB = have - t.lenA;
+            bool okA = t.lenA == K, okB = t.lenB == K;
+            for (int i = 0; i < t.lenA; ++i) { const int c = kmer_code(__ldg(src + t.p + i)); okA &= c < 4; t.idxA = (t.idxA << 2) | (uint32_t)(c & 3); }
+            for (int i = 0; i < t.lenB; ++i) { const int c = kmer_code(__ldg(src + t.p + K + i)); okB &= c < 4; t.idxB = (t.idxB << 2) | (uint32_t)(c & 3); }
+            t.cleanA = okA; t.cleanB = okB;
+        }
+        return t;
+    };
+    auto emit = [&](int chunk, const Two& t) {
+        const bool simple = (t.lenA == 0 || t.cleanA) && (t.lenB == 0 || t.cleanB);
+        if (__all_sync(0xffffffffu, simple)) {
+            // every window of the chunk is one token: this lane's tokens sit at base + 2*lane (+1)
+            const int pos = base + 2 * lane;
+            const IdT a = t.lenA ? (IdT)(AFFINE ? affine_base + (int32_t)t.idxA : __ldg(kmer_ids + t.idxA)) : (IdT)0;
+            const IdT b = t.lenB ? (IdT)(AFFINE ? affine_base + (int32_t)t.idxB : __ldg(kmer_ids + t.idxB)) : (IdT)0;
+            if (t.lenB && pos + 1 < cap && pair_aligned && ((pos & 1) == 0)) {
+                Pair v; v.x = a; v.y = b;
+                *reinterpret_cast<Pair*>(dst + pos) = v;
+                if (FUSE_MASK) { Pair one; one.x = 1; one.y = 1; *reinterpret_cast<Pair*>(mdst + pos) = one; }
+            } else {
+                if (t.lenA && pos < cap) { dst[pos] = a; if (FUSE_MASK) mdst[pos] = 1; }
+                if (t.lenB && pos + 1 < cap) { dst[pos + 1] = b; if (FUSE_MASK) mdst[pos + 1] = 1; }
+            }
+            const int left = n_win - chunk * 64;
+            base += left < 64 ? left : 64;
+        } else {
+            const int cntA = t.lenA == 0 ? 0 : (t.cleanA ? 1 : t.lenA);
+            const int cntB = t.lenB == 0 ? 0 : (t.cleanB ? 1 : t.lenB);
             int my = cntA + cntB, x = my;
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
@@ -331,35 +349,111 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                 if (lane >= d) x += y;
             }
             const int total = __shfl_sync(0xffffffffu, x, 31);
-            int64_t pos = base + x - my;
-            if (lenA) {
-                if (cleanA) { if (pos < cap) dst[pos] = (IdT)__ldg(kmer_ids + idxA); ++pos; }
-                else for (int i = 0; i < lenA; ++i, ++pos) if (pos < cap) dst[pos] = (IdT)__ldg(single_ids + __ldg(src + p + i));
+            int pos = base + x - my;
+            if (t.lenA) {
+                if (t.cleanA) { if (pos < cap) { dst[pos] = (IdT)__ldg(kmer_ids + t.idxA); if (FUSE_MASK) mdst[pos] = 1; } ++pos; }
+                else for (int i = 0; i < t.lenA; ++i, ++pos) if (pos < cap) { dst[pos] = (IdT)__ldg(single_ids + __ldg(src + t.p + i)); if (FUSE_MASK) mdst[pos] = 1; }
             }
-            if (lenB) {
-                if (cleanB) { if (pos < cap) dst[pos] = (IdT)__ldg(kmer_ids + idxB); ++pos; }
-                else for (int i = 0; i < lenB; ++i, ++pos) if (pos < cap) dst[pos] = (IdT)__ldg(single_ids + __ldg(src + p + K + i));
+            if (t.lenB) {
+                if (t.cleanB) { if (pos < cap) { dst[pos] = (IdT)__ldg(kmer_ids + t.idxB); if (FUSE_MASK) mdst[pos] = 1; } ++pos; }
+                else for (int i = 0; i < t.lenB; ++i, ++pos) if (pos < cap) { dst[pos] = (IdT)__ldg(single_ids + __ldg(src + t.p + K + i)); if (FUSE_MASK) mdst[pos] = 1; }
             }
             base += total;
         }
-    }
+    };
 
-    const int64_t n = base < cap ? base : cap;
-    const int64_t T = n + n_special;
+    // Wide-route decode of the two windows at g (no bounds checks): table indices and a word that is
+    // non-zero when either window holds anything but ACGT.
+    auto decode_tight = [&](const uint32_t* gw, uint32_t sh, uint32_t* idxA, uint32_t* idxB) -> uint32_t {
+        uint32_t w[NW];
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[i] = __ldg(gw + i);
+        uint32_t P = 0, bad = 0;
+#pragma unroll
+        for (int i = 0; i < NW - 1; ++i) {
+            const uint32_t r = __funnelshift_r(w[i], w[i + 1], sh);
+            uint32_t c, d;
+            acgt_codes4(r, &c, &d);
+            P |= pack_codes4(c) << (24 - 8 * i);
+            uint32_t m = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) if (4 * i + b < 2 * K) m |= 0xFFu << (8 * b);
+            bad |= d & m;
+        }
+        *idxA = (P >> (32 - 2 * K)) & IDX_MASK;
+        *idxB = (P >> (32 - 4 * K)) & IDX_MASK;
+        return bad;
+    };
+    // chunks in which every lane owns two complete windows and the aligned words stay in the buffer
+    int n_tight = n_full >> 6;
+    {
+        const int64_t fit = (room_total - 8) / (64 * K);
+        if (fit < n_tight) n_tight = fit < 0 ? 0 : (int)fit;
+    }
+    const uint8_t* g0 = src + 2 * lane * K;
+    const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g0) & 3u) * 8u;     // the same for every chunk: 64K % 4 == 0
+    const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
+    Pair one; one.x = 1; one.y = 1;
+
+    int chunk = 0;
+    while (chunk < n_chunks && base < cap) {
+        // tight stretch: clean full chunks, no per-token checks
+        {
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(g0 - (sh >> 3)) + (size_t)chunk * (16 * K);
+            IdT* d = dst + base + 2 * lane;
+            const bool al = pair_aligned && ((base & 1) == 0);
+            while (chunk + 1 < n_tight && base + 128 <= cap) {
+                uint32_t a0, b0, a1, b1;
+                const uint32_t bad0 = decode_tight(gw, sh, &a0, &b0);
+                const uint32_t bad1 = decode_tight(gw + 16 * K, sh, &a1, &b1);
+                if (__any_sync(0xffffffffu, (bad0 | bad1) != 0)) break;
+                const IdT x0 = (IdT)(AFFINE ? affine_base + (int32_t)a0 : __ldg(kmer_ids + a0));
+                const IdT y0 = (IdT)(AFFINE ? affine_base + (int32_t)b0 : __ldg(kmer_ids + b0));
+                const IdT x1 = (IdT)(AFFINE ? affine_base + (int32_t)a1 : __ldg(kmer_ids + a1));
+                const IdT y1 = (IdT)(AFFINE ? affine_base + (int32_t)b1 : __ldg(kmer_ids + b1));
+                if (al) {
+                    Pair v0, v1; v0.x = x0; v0.y = y0; v1.x = x1; v1.y = y1;
+                    *reinterpret_cast<Pair*>(d) = v0;
+                    *reinterpret_cast<Pair*>(d + 64) = v1;
+                    if (FUSE_MASK) { *reinterpret_cast<Pair*>(d + mdelta) = one; *reinterpret_cast<Pair*>(d + mdelta + 64) = one; }
+                } else {
+                    d[0] = x0; d[1] = y0; d[64] = x1; d[65] = y1;
+                    if (FUSE_MASK) { d[mdelta] = 1; d[mdelta + 1] = 1; d[mdelta + 64] = 1; d[mdelta + 65] = 1; }
+                }
+                gw += 32 * K; d += 128; base += 128; chunk += 2;
+            }
+        }
+        if (chunk >= n_chunks) break;
+        if (base >= cap) { clipped = true; break; }
+        // one chunk by the general route (dirty windows, row edges, the last tokens before the cap)
+        const Two t0 = decode(chunk);
+        emit(chunk, t0);
+        ++chunk;
+    }
+    if (chunk < n_chunks) clipped = true;
+    if (base > cap) clipped = true;
+
+    const int n = base < cap ? base : cap;
+    const int T = n + n_special;
     if (lane == 0) {
         if (lengths_out) lengths_out[row] = (int32_t)T;
-        if (status && f.clip_is_error && (base > cap || w0 < n_win)) atomicOr(status + row, 4);
-        if (has_cls) orow[shift] = (IdT)f.cls_id;
-        if (has_sep) orow[shift + T - 1] = (IdT)f.sep_id;
+        if (status && f.clip_is_error && clipped) atomicOr(status + row, 4);
+        if (has_cls) { orow[shift] = (IdT)f.cls_id; if (FUSE_MASK) (reinterpret_cast<IdT*>(mask) + (orow - ids))[shift] = 1; }
+        if (has_sep) { orow[shift + T - 1] = (IdT)f.sep_id; if (FUSE_MASK) (reinterpret_cast<IdT*>(mask) + (orow - ids))[shift + T - 1] = 1; }
     }
     if (!ragged) {
+        const int stride = (int)f.out_stride;
         const IdT pad = (IdT)f.pad_id;
         if (f.pad_left) warp_write_run<IdT>(orow, shift, lane, [=](int64_t) { return pad; });
-        else warp_write_run<IdT>(orow + T, f.out_stride - T, lane, [=](int64_t) { return pad; });
-        if (f.mask_bits == 64) warp_mask_row<int64_t>((int64_t*)mask + row * f.out_stride, f.out_stride, shift, shift + T, lane);
-        else if (f.mask_bits == 32) warp_mask_row<int32_t>((int32_t*)mask + row * f.out_stride, f.out_stride, shift, shift + T, lane);
-        else if (f.mask_bits == 8) warp_mask_row<uint8_t>((uint8_t*)mask + row * f.out_stride, f.out_stride, shift, shift + T, lane);
-    } else if (mask && f.mask_bits) {
+        else warp_write_run<IdT>(orow + T, stride - T, lane, [=](int64_t) { return pad; });
+        if (FUSE_MASK) {
+            IdT* mrow = reinterpret_cast<IdT*>(mask) + row * f.out_stride;
+            if (f.pad_left) warp_write_run<IdT>(mrow, shift, lane, [](int64_t) { return (IdT)0; });
+            else warp_write_run<IdT>(mrow + T, stride - T, lane, [](int64_t) { return (IdT)0; });
+        } else if (f.mask_bits == 64) warp_mask_row<int64_t>((int64_t*)mask + row * f.out_stride, stride, shift, shift + T, lane);
+        else if (f.mask_bits == 32) warp_mask_row<int32_t>((int32_t*)mask + row * f.out_stride, stride, shift, shift + T, lane);
+        else if (f.mask_bits == 8) warp_mask_row<uint8_t>((uint8_t*)mask + row * f.out_stride, stride, shift, shift + T, lane);
+    } else if (mask && f.mask_bits && !FUSE_MASK) {
         const int64_t o = out_offsets[row];
         if (f.mask_bits == 64) warp_write_run<int64_t>((int64_t*)mask + o, T, lane, [](int64_t) { return (int64_t)1; });
         else if (f.mask_bits == 32) warp_write_run<int32_t>((int32_t*)mask + o, T, lane, [](int64_t) { return (int32_t)1; });
