@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(HERE, "csrc", "libdnatok_b200.so")
 OK = 0
 ROW_TOO_LONG, ROW_NOT_CONVERGED, ROW_CLIPPED = 1, 2, 4
 KIND_CHAR, KIND_KMER, KIND_BPE = 0, 1, 2
-BPE_MAX_WORD = 16384
+BPE_MAX_WORD = 49152
 
 EXPORTS = (
     "dnatok_version", "dnatok_last_error", "dnatok_create_char", "dnatok_create_kmer",

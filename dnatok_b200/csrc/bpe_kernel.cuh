@@ -1,41 +1,54 @@
-// BPE merge engine.  One warp owns one pre-tokenised word, held entirely in shared memory as
-// four 16-bit arrays over the word's original positions: the token at each live position, the
-// rank of the pair that starts there, and next / previous live position.  Every pass
-//   1. finds the lowest rank among all live pairs (128-bit shared-memory loads, packed 16-bit
-//      minima, one warp reduction),
-//   2. marks the positions holding that rank as merge sites; for a pair of equal tokens (x, x)
-//      only the first position of a run of such pairs is marked and its owner walks the run
-//      left to right taking every other pair, which is Hugging Face's leftmost-first rule,
-//   3. applies all sites (token replaced, right neighbour unlinked) and marks the positions
-//      whose pair changed,
-//   4. looks the changed pairs up again in the merge table,
-// until no pair has a rank.  Merging every occurrence of the lowest rank in one pass gives the
-// same result as Hugging Face's queue (one merge at a time, lowest rank then leftmost) when new
-// pairs always rank above the merge that created them; the host checks that property of the
-// table and otherwise selects one merge per pass (single_step).
+// BPE merge engine: exact Hugging Face merge order in a handful of data-parallel rounds.
 //
-// Words are binned by length into capacity classes so that short words do not pay for the
-// shared memory of long ones; each class is one persistent launch whose warps pull words from a
-// shared counter.  Merged tokens (uint16, Hugging Face ids) and per-row counts go to the
-// caller's scratch; the emit kernels turn them into the final ids / mask layout.
+// One warp owns one pre-tokenised word, kept as a COMPACT array of 16-bit tokens in shared memory
+// (no links, no tombstones).  A round:
+//   A. every adjacent pair is looked up in the merge table (perfect hash, two dependent loads);
+//      its rank is stored and B = min over the present ranks r of F[r] is reduced, where F[r] is
+//      the lowest rank of any pair that contains the token rank r creates;
+//   B. pairs with rank < B are candidates.  Hugging Face would take them in (rank, position)
+//      order, skipping a pair when an earlier one consumed one of its tokens.  On a path that
+//      greedy choice has a closed form: follow the strictly improving priorities to the left and to
+//      the right of a candidate down to the local optimum; the candidate is taken iff both walks
+//      have even length.  The two parities are segmented prefix-XORs, computed 32 positions at a
+//      time with carry-propagating bit tricks on ballot masks (one backward sweep, one forward);
+//   C. the forward sweep also applies the selected merges and compacts the array in place.
+// Everything created in a round contains a new token, so it ranks >= B, above every pair merged
+// in that round: the round equals the sequential queue run over the same ranks.  Rounds repeat
+// until no pair has a rank: 5-7 rounds for DNA words of any length, ~3.3 position visits per
+// input byte in total.  Equal ranks on neighbouring pairs (runs of one token) fall out of the same
+// rule, because priority is (rank, position): every other pair from the left.
 //
-// Same rule as the reference kernel states (src/dnatok_bpe_kernel/dnatok_bpe.cu:3-5,172-176),
-// different machinery: that kernel keeps per-rank bucket lists and the word itself in global
-// memory with one 256-thread block per sequence (:237-740).
+// A table whose merge operands may be created by later ranks has no usable F; for it the host
+// selects single_step: one merge per round, the leftmost pair of the lowest rank.
+//
+// Words are binned by length into capacity classes (shared memory per word = 4.125 bytes per
+// position); each class is one launch of resident warps that pull words from a shared counter.
+// Merged tokens (uint16, Hugging Face ids) and per-row counts go to the caller's scratch; the emit
+// kernels produce the final ids / mask layout.
+//
+// Same result as the rule the reference kernel states (src/dnatok_bpe_kernel/dnatok_bpe.cu:3-5,
+// 172-176); that kernel walks the ranks one by one with per-rank bucket lists in global memory
+// and one 256-thread block per sequence (:237-740).
 #pragma once
 #include "common.cuh"
 
 namespace dnatok {
 
-constexpr uint32_t BPE_NONE = 0xFFFFu;      // no rank / no position / dead token
-constexpr int BPE_N_CLASSES = 7;            // capacities 256 << c, c = 0..6
-constexpr int BPE_MIN_CAP = 256;
+constexpr uint32_t BPE_NONE = 0xFFFFu;          // no rank
+constexpr int BPE_N_CLASSES = 9;
+constexpr int BPE_WARPS = 8;                    // warps (= words in flight) per block
+
+__host__ __device__ constexpr int bpe_class_capacity(int c) {
+    return c < 8 ? (256 << c) : 49152;          // 256 ... 32768, 49152
+}
+__host__ __device__ constexpr int bpe_slot_bytes(int C) { return 4 * C + C / 8; }
 
 struct BpeDeviceTable {
-    const uint32_t* disp;
-    const uint32_t* slots;
-    const uint16_t* merge_out;
-    const uint16_t* byte_tok;
+    const uint32_t* disp;        // [n_tokens] row displacement of the left token
+    const uint32_t* slots;       // (left << 16) | rank, 0xFFFFFFFF when empty
+    const uint16_t* merge_out;   // [n_merges] token created by a rank
+    const uint16_t* future;      // [n_merges] F: lowest rank of a pair containing that token
+    const uint16_t* byte_tok;    // [256]
     int32_t single_step;
 };
 
@@ -44,10 +57,17 @@ __device__ __forceinline__ uint32_t bpe_rank(const BpeDeviceTable& t, uint32_t a
     return (s >> 16) == a ? (s & 0xFFFFu) : BPE_NONE;
 }
 
-// Bytes of shared memory one word slot of capacity C takes.
-__host__ __device__ constexpr int bpe_slot_bytes(int C) { return 8 * C + C / 8 + C / 8; }
+// odd(i) = c(i) & ~odd(i-1), odd(-1) = prev_odd: parity of the length of the run of set bits
+// ending at each bit, continued from the previous 32 positions.
+__device__ __forceinline__ uint32_t run_parity(uint32_t c, bool prev_odd) {
+    uint32_t se = c & ~(c << 1) & 0x55555555u;      // runs that start on an even bit
+    if (prev_odd) se &= ~1u;                        // a run continuing an odd position behaves as odd-started
+    const uint32_t fe = c & ~(c + se);              // all bits of those runs
+    const uint32_t fo = c & ~fe;
+    return (fe & 0x55555555u) | (fo & 0xAAAAAAAAu);
+}
 
-// Bin rows by length.  class_count[c] rows land in class_list[c * n_rows ...].
+// Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].
 __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t n_rows,
                                     int32_t* __restrict__ class_count, int32_t* __restrict__ class_list,
                                     int32_t* __restrict__ counts, int32_t* __restrict__ status) {
@@ -57,28 +77,26 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
     counts[i] = 0;
     if (n <= 0) return;
     int c = 0;
-    while (c < BPE_N_CLASSES && (int64_t)(BPE_MIN_CAP << c) < n) ++c;
+    while (c < BPE_N_CLASSES && (int64_t)bpe_class_capacity(c) < n) ++c;
     if (c >= BPE_N_CLASSES) { if (status) atomicOr(status + i, 1); return; }
     const int slot = atomicAdd(class_count + c, 1);
     class_list[(int64_t)c * n_rows + slot] = (int32_t)i;
 }
 
 template <int C>
-__global__ void bpe_merge_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
-                                 const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
-                                 int32_t* __restrict__ work_counter, BpeDeviceTable t,
-                                 uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
-                                 int32_t* __restrict__ status) {
+__global__ void __launch_bounds__(BPE_WARPS * 32)
+bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
+                  const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
+                  int32_t* __restrict__ work_counter, BpeDeviceTable t,
+                  uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ status) {
     extern __shared__ uint4 bpe_dyn[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lt = (1u << lane) - 1u;
     uint8_t* slot = reinterpret_cast<uint8_t*>(bpe_dyn) + (size_t)warp * bpe_slot_bytes(C);
-    uint16_t* rk = reinterpret_cast<uint16_t*>(slot);            // 16-byte aligned: slot size is a multiple of 16
-    uint16_t* tok = rk + C;
-    uint16_t* nxt = tok + C;
-    uint16_t* prv = nxt + C;
-    uint8_t* siteb = reinterpret_cast<uint8_t*>(prv + C);        // C/8 bytes: one flag byte per 8 positions
-    uint32_t* dirty = reinterpret_cast<uint32_t*>(siteb + C / 8);// C/32 words
-    const uint4* rk4 = reinterpret_cast<const uint4*>(rk);
+    uint16_t* tok = reinterpret_cast<uint16_t*>(slot);          // [C] live tokens, compact
+    uint16_t* rk = tok + C;                                     // [C] rank of the pair (i, i+1)
+    uint32_t* oddr = reinterpret_cast<uint32_t*>(rk + C);       // [C/32] right-walk parity bits per 32 positions
     const int n_words = *list_count;
 
     for (;;) {
@@ -88,120 +106,86 @@ __global__ void bpe_merge_kernel(const uint8_t* __restrict__ bytes, const int64_
         if (wi >= n_words) break;
         const int row = list[wi];
         const int64_t off = offsets[row];
-        const int n = (int)(offsets[row + 1] - off);          // 1 <= n <= C by classification
-        const int nvec = (n + 7) >> 3;
+        int n = (int)(offsets[row + 1] - off);               // 1 <= n <= C by classification
 
-        for (int i = lane; i < nvec * 8; i += 32) {
-            if (i < n) {
-                tok[i] = t.byte_tok[__ldg(bytes + off + i)];
-                nxt[i] = (uint16_t)(i + 1 < n ? i + 1 : BPE_NONE);
-                prv[i] = (uint16_t)(i ? i - 1 : BPE_NONE);
-            }
-            rk[i] = (uint16_t)BPE_NONE;
-        }
-        for (int i = lane; i < (nvec + 3) / 4; i += 32) dirty[i] = 0;
-        __syncwarp();
-        for (int i = lane; i + 1 < n; i += 32) rk[i] = (uint16_t)bpe_rank(t, tok[i], tok[i + 1]);
+        for (int i = lane; i < n; i += 32) tok[i] = __ldg(t.byte_tok + __ldg(bytes + off + i));
         __syncwarp();
 
-        int pass = 0;
-        for (; pass <= n; ++pass) {
-            // 1. lowest rank
-            uint32_t m = 0xFFFFFFFFu;
-            for (int j = lane; j < nvec; j += 32) {
-                const uint4 v = rk4[j];
-                m = __vminu2(m, __vminu2(__vminu2(v.x, v.y), __vminu2(v.z, v.w)));
-            }
-            const uint32_t g = __reduce_min_sync(0xffffffffu, min(m & 0xFFFFu, m >> 16));
-            if (g == BPE_NONE) break;
-            const uint16_t newtok = __ldg(t.merge_out + g);
-            const uint32_t gg = g | (g << 16);
-
-            // 2. sites (reads only)
-            uint32_t first_site = BPE_NONE;
-            for (int j = lane; j < nvec; j += 32) {
-                const uint4 v = rk4[j];
-                const uint32_t w[4] = { v.x, v.y, v.z, v.w };
-                uint32_t flags = 0;
-                if ((__vcmpeq2(w[0], gg) | __vcmpeq2(w[1], gg) | __vcmpeq2(w[2], gg) | __vcmpeq2(w[3], gg)) != 0) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const uint32_t r = (w[e >> 1] >> ((e & 1) * 16)) & 0xFFFFu;
-                        if (r == g) {
-                            const int p = j * 8 + e;
-                            bool site = true;
-                            if (tok[nxt[p]] == tok[p]) {              // pair (x, x): only a run start is a site
-                                const uint32_t l = prv[p];
-                                if (l != BPE_NONE && rk[l] == g) site = false;
-                            }
-                            if (site) { flags |= 1u << e; if (first_site == BPE_NONE) first_site = p; }
-                        }
-                    }
+        int round = 0;
+        const int max_rounds = n + 2;
+        for (; round < max_rounds; ++round) {
+            const int groups = (n + 31) >> 5;
+            // ---- A: ranks of all pairs, bound B, lowest rank
+            uint32_t bmin = BPE_NONE, gmin = BPE_NONE;
+            for (int g = 0; g < groups; ++g) {
+                const int i = g * 32 + lane;
+                uint32_t r = BPE_NONE;
+                if (i + 1 < n) r = bpe_rank(t, tok[i], tok[i + 1]);
+                if (i < n) rk[i] = (uint16_t)r;
+                if (r != BPE_NONE) {
+                    gmin = min(gmin, r);
+                    bmin = min(bmin, (uint32_t)__ldg(t.future + r));
                 }
-                siteb[j] = (uint8_t)flags;
             }
-            uint32_t only = BPE_NONE;
-            if (t.single_step) only = __reduce_min_sync(0xffffffffu, first_site);
+            gmin = __reduce_min_sync(0xffffffffu, gmin);
+            if (gmin == BPE_NONE) break;                       // no pair can merge: done
+            uint32_t B = __reduce_min_sync(0xffffffffu, bmin);
+            if (t.single_step) B = gmin + 1;
             __syncwarp();
 
-            // 3. apply
-            for (int j = lane; j < nvec; j += 32) {
-                uint32_t flags = siteb[j];
-                while (flags) {
-                    const int e = __ffs(flags) - 1;
-                    flags &= flags - 1;
-                    int p = j * 8 + e;
-                    if (t.single_step && (uint32_t)p != only) continue;
-                    const bool homo = tok[nxt[p]] == tok[p];
-                    for (int guard = 0; guard < C; ++guard) {
-                        const uint32_t q = nxt[p];
-                        const uint32_t r = nxt[q];
-                        tok[p] = newtok;
-                        tok[q] = (uint16_t)BPE_NONE;
-                        rk[q] = (uint16_t)BPE_NONE;
-                        nxt[p] = (uint16_t)r;
-                        if (r != BPE_NONE) prv[r] = (uint16_t)p;
-                        atomicOr(dirty + (p >> 5), 1u << (p & 31));
-                        const uint32_t l = prv[p];
-                        if (l != BPE_NONE) atomicOr(dirty + (l >> 5), 1u << (l & 31));
-                        if (!homo || t.single_step || r == BPE_NONE || rk[r] != g) break;
-                        p = (int)r;       // next pair of the run (x, x)(x, x)...
-                    }
-                }
+            // ---- B: parity of the improving walk to the right, last group first
+            bool carry = false;                                // parity bit of position 32(g+1)
+            for (int g = groups - 1; g >= 0; --g) {
+                const int i = g * 32 + lane;
+                const uint32_t r = i < n ? (uint32_t)rk[i] : BPE_NONE;
+                const uint32_t rn = i + 1 < n ? (uint32_t)rk[i + 1] : BPE_NONE;
+                const bool link = r < B && rn < r;             // the right neighbour is a candidate with better priority
+                const uint32_t c = __brev(__ballot_sync(0xffffffffu, link));
+                const uint32_t odd = __brev(run_parity(c, carry));
+                if (lane == 0) oddr[g] = odd;
+                carry = odd & 1u;
             }
             __syncwarp();
 
-            // 4. re-rank the pairs that changed
-            for (int i = lane; i < (nvec + 3) / 4; i += 32) {
-                uint32_t d = dirty[i];
-                if (d) {
-                    dirty[i] = 0;
-                    while (d) {
-                        const int p = i * 32 + __ffs(d) - 1;
-                        d &= d - 1;
-                        const uint32_t a = tok[p];
-                        if (a != BPE_NONE) {
-                            const uint32_t r = nxt[p];
-                            rk[p] = (uint16_t)(r == BPE_NONE ? BPE_NONE : bpe_rank(t, a, tok[r]));
-                        }
-                    }
+            // ---- C: left-walk parity, selection, merge and in-place compaction, first group first
+            carry = false;                                     // left parity bit of position 32g - 1
+            uint32_t prev_sel = 0;                             // was position 32g - 1 selected (its partner is dropped)
+            int out = 0;
+            bool took_one = false;
+            for (int g = 0; g < groups; ++g) {
+                const int i = g * 32 + lane;
+                const uint32_t r = i < n ? (uint32_t)rk[i] : BPE_NONE;
+                const uint32_t rp = i > 0 && i < n ? (uint32_t)rk[i - 1] : BPE_NONE;
+                const uint32_t tk = i < n ? (uint32_t)tok[i] : 0u;
+                const bool cand = r < B;
+                const bool link = cand && rp <= r;             // rp <= r < B: the left neighbour is a candidate and goes first
+                const uint32_t candm = __ballot_sync(0xffffffffu, cand);
+                const uint32_t oddl = run_parity(__ballot_sync(0xffffffffu, link), carry);
+                carry = oddl >> 31;
+                uint32_t sel = candm & ~oddl & ~oddr[g];
+                if (t.single_step) {                           // only the leftmost pair of the lowest rank
+                    sel = took_one ? 0u : (sel & (0u - sel));
+                    took_one = took_one || sel != 0;
                 }
+                const uint32_t valid = (i < n ? 1u : 0u);
+                const uint32_t validm = __ballot_sync(0xffffffffu, valid);
+                const uint32_t dropped = (sel << 1) | prev_sel;          // positions consumed as the right half of a pair
+                const uint32_t kept = validm & ~dropped;
+                uint32_t v = tk;
+                if ((sel >> lane) & 1u) v = __ldg(t.merge_out + r);
+                __syncwarp();                                  // every lane has read this group's tokens
+                if ((kept >> lane) & 1u) tok[out + __popc(kept & lt)] = (uint16_t)v;
+                out += __popc(kept);
+                prev_sel = sel >> 31;
             }
+            n = out;
             __syncwarp();
         }
 
-        // compact the live tokens, in order, to out_tok[off ...]
-        int base = 0;
-        for (int i0 = 0; i0 < n; i0 += 32) {
-            const int i = i0 + lane;
-            const bool live = i < n && tok[i] != BPE_NONE;
-            const uint32_t bal = __ballot_sync(0xffffffffu, live);
-            if (live) out_tok[off + base + __popc(bal & ((1u << lane) - 1))] = tok[i];
-            base += __popc(bal);
-        }
+        for (int i = lane; i < n; i += 32) out_tok[off + i] = tok[i];
         if (lane == 0) {
-            counts[row] = base;
-            if (pass > n && status) atomicOr(status + row, 2);
+            counts[row] = n;
+            if (round >= max_rounds && status) atomicOr(status + row, 2);
         }
         __syncwarp();
     }

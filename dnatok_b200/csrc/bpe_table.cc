@@ -73,6 +73,13 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
     t->slots.swap(slots);
     t->merge_out.resize(n);
     for (int32_t r = 0; r < n; ++r) t->merge_out[r] = (uint16_t)o[r];
+    t->future.assign(n, 0xFFFFu);
+    for (int32_t r = 0; r < n; ++r) {
+        for (int32_t x : {a[r], b[r]}) {
+            const int32_t c = created[x];
+            if (c >= 0 && (uint32_t)r < t->future[c]) t->future[c] = (uint16_t)r;
+        }
+    }
     t->byte_tok.resize(256);
     for (int i = 0; i < 256; ++i) t->byte_tok[i] = (uint16_t)byte_ids[i];
     t->n_tokens = n_tokens;

@@ -18,13 +18,14 @@ struct BpeHostTable {
     std::vector<uint32_t> disp;        // [n_tokens]
     std::vector<uint32_t> slots;       // [max disp + n_tokens], 0xFFFFFFFF when empty
     std::vector<uint16_t> merge_out;   // [n_merges] id created by each rank
+    std::vector<uint16_t> future;      // [n_merges] lowest rank of any pair containing that id, 0xFFFF if none
     std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
     uint32_t n_tokens = 0;
     uint32_t n_merges = 0;
     // True when every merge's operands are created by lower ranks (or are initial symbols).
     // Then a pair that contains a freshly created token always ranks above the merge that
-    // created it, and all non-overlapping occurrences of the lowest rank can be merged in
-    // one pass.  Otherwise the kernel merges one occurrence per pass.
+    // created it, `future` bounds what a round may create, and many ranks can be merged in one
+    // round.  Otherwise the kernel merges one pair per round.
     bool batch_safe = false;
 };
 

@@ -54,6 +54,7 @@ struct DeviceTables {
     uint32_t* disp = nullptr;
     uint32_t* slots = nullptr;
     uint16_t* merge_out = nullptr;
+    uint16_t* future = nullptr;
     uint16_t* byte_tok = nullptr;
     int sm_count = 0;
     // host-pipeline staging (grow only)
@@ -109,6 +110,7 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
             if ((rc = upload(&d.disp, h->bpe.disp))) return rc;
             if ((rc = upload(&d.slots, h->bpe.slots))) return rc;
             if ((rc = upload(&d.merge_out, h->bpe.merge_out))) return rc;
+            if ((rc = upload(&d.future, h->bpe.future))) return rc;
             if ((rc = upload(&d.byte_tok, h->bpe.byte_tok))) return rc;
         }
         it = h->dev.emplace(dev, d).first;
@@ -157,8 +159,8 @@ int resolve(const dnatok_handle* h, const dnatok_format* f, int64_t stride, RowF
 struct BpeScratch {
     uint16_t* tokens;       // [total_bytes] merged tokens at the input offsets
     int32_t* counts;        // [n_rows] content tokens per row
-    int32_t* class_count;   // [8]
-    int32_t* work;          // [8]
+    int32_t* class_count;   // [16]
+    int32_t* work;          // [16]
     int32_t* class_list;    // [BPE_N_CLASSES * n_rows]
     size_t bytes;
 };
@@ -169,25 +171,25 @@ BpeScratch bpe_scratch_layout(void* base, int64_t n_rows, int64_t total_bytes) {
     uint8_t* b = (uint8_t*)base;
     s.tokens = (uint16_t*)(b + o);      o += align_up((size_t)total_bytes * 2 + 16, 256);
     s.counts = (int32_t*)(b + o);       o += align_up((size_t)n_rows * 4 + 4, 256);
-    s.class_count = (int32_t*)(b + o);  o += 32;
-    s.work = (int32_t*)(b + o);         o += 32;
+    s.class_count = (int32_t*)(b + o);  o += 64;
+    s.work = (int32_t*)(b + o);         o += 64;
     o = align_up(o, 256);
     s.class_list = (int32_t*)(b + o);   o += align_up((size_t)n_rows * 4 * BPE_N_CLASSES + 4, 256);
     s.bytes = o;
     return s;
 }
 
-template <int C>
-int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, int cls, const uint8_t* bytes,
-                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status,
-                     cudaStream_t st) {
-    const int slot = bpe_slot_bytes(C);
-    int warps = (200 * 1024) / slot;
-    if (warps > 32) warps = 32;
+template <int CLS>
+int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
+                     int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+    constexpr int C = bpe_class_capacity(CLS);
+    constexpr int slot = bpe_slot_bytes(C);
+    int warps = (100 * 1024) / slot;                 // words in flight per block
+    if (warps > BPE_WARPS) warps = BPE_WARPS;
     if (warps < 1) warps = 1;
     const size_t smem = (size_t)warps * slot;
     static std::mutex mu;
-    static std::map<int, int> blocks_per_sm;     // device -> resident blocks (also marks the attribute as set)
+    static std::map<int, int> blocks_per_sm;         // device -> resident blocks (also marks the attribute as set)
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
     int bps = 0;
@@ -195,8 +197,8 @@ int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, int cls, co
         std::lock_guard<std::mutex> lock(mu);
         auto it = blocks_per_sm.find(dev);
         if (it == blocks_per_sm.end()) {
-            CUDA_TRY(cudaFuncSetAttribute(bpe_merge_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_merge_kernel<C>, warps * 32, smem));
+            CUDA_TRY(cudaFuncSetAttribute(bpe_rounds_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_rounds_kernel<C>, warps * 32, smem));
             if (bps < 1) bps = 1;
             blocks_per_sm[dev] = bps;
         } else bps = it->second;
@@ -206,10 +208,10 @@ int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, int cls, co
     const int64_t need = (n_rows + warps - 1) / warps;
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
-    bpe_merge_kernel<C><<<(unsigned)grid, warps * 32, smem, st>>>(
-        bytes, offsets, s.class_list + (int64_t)cls * n_rows, s.class_count + cls, s.work + cls, t,
+    bpe_rounds_kernel<C><<<(unsigned)grid, warps * 32, smem, st>>>(
+        bytes, offsets, s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
         s.tokens, s.counts, status);
-    LAUNCH_CHECK("bpe_merge_kernel");
+    LAUNCH_CHECK("bpe_rounds_kernel");
     return 0;
 }
 
@@ -221,20 +223,20 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     BpeScratch s = bpe_scratch_layout(scratch, n_rows, total_bytes);
     if (s.bytes > scratch_bytes) return fail(DNATOK_ERR_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, s.bytes);
     if (n_rows == 0) return 0;
-    CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 64, st));   // class_count and work are adjacent
+    CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 128, st));   // class_count and work are adjacent
     bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
                                                                        s.class_list, s.counts, status);
     LAUNCH_CHECK("bpe_classify_kernel");
-    BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
+    BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.future, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
+    // Classes that cannot hold a row of this batch are skipped: the longest row is at most total_bytes.
     int rc;
+#define BPE_CLASS(CLS)                                                                                         \
+    if ((CLS == 0 || total_bytes > bpe_class_capacity(CLS == 0 ? 0 : CLS - 1)) &&                                \
+        (rc = launch_bpe_class<CLS>(d, t, bytes, offsets, n_rows, s, status, st)))                               \
+        return rc;
     // longest class first: its few, slow words start while nothing else competes for the SMs
-    if ((rc = launch_bpe_class<16384>(d, t, 6, bytes, offsets, n_rows, s, status, st))) return rc;
-    if ((rc = launch_bpe_class<8192>(d, t, 5, bytes, offsets, n_rows, s, status, st))) return rc;
-    if ((rc = launch_bpe_class<4096>(d, t, 4, bytes, offsets, n_rows, s, status, st))) return rc;
-    if ((rc = launch_bpe_class<2048>(d, t, 3, bytes, offsets, n_rows, s, status, st))) return rc;
-    if ((rc = launch_bpe_class<1024>(d, t, 2, bytes, offsets, n_rows, s, status, st))) return rc;
-    if ((rc = launch_bpe_class<512>(d, t, 1, bytes, offsets, n_rows, s, status, st))) return rc;
-    if ((rc = launch_bpe_class<256>(d, t, 0, bytes, offsets, n_rows, s, status, st))) return rc;
+    BPE_CLASS(8) BPE_CLASS(7) BPE_CLASS(6) BPE_CLASS(5) BPE_CLASS(4) BPE_CLASS(3) BPE_CLASS(2) BPE_CLASS(1) BPE_CLASS(0)
+#undef BPE_CLASS
     return 0;
 }
 
@@ -413,7 +415,7 @@ void dnatok_destroy(dnatok_handle* h) {
         DeviceTables& d = kv.second;
         if (cudaSetDevice(kv.first) != cudaSuccess) continue;
         if (d.stream) cudaStreamSynchronize(d.stream);
-        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.byte_tok, d.st_bytes, d.st_offsets,
+        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.future, d.byte_tok, d.st_bytes, d.st_offsets,
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);

@@ -54,7 +54,7 @@ extern "C" {
 #define DNATOK_KIND_KMER 1
 #define DNATOK_KIND_BPE  2
 
-#define DNATOK_BPE_MAX_WORD 16384     /* longest BPE word (bytes) the merge kernel accepts */
+#define DNATOK_BPE_MAX_WORD 49152     /* longest BPE word (bytes) the merge kernel accepts */
 
 typedef struct dnatok_handle dnatok_handle;
 typedef void* dnatok_stream;          /* a cudaStream_t */

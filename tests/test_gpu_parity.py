@@ -127,7 +127,7 @@ def test_ragged_lengths_truncation_dtypes(toks, name, ids_dtype, mask_dtype):
 def test_bpe_homopolymers_and_long_words(toks, name):
     words = [b"A" * n for n in (1, 2, 3, 4, 5, 8, 9, 31, 32, 33, 64, 100, 255, 256, 257, 1024, 4097)]
     words += [b"AC" * 300, b"ACG" * 333, b"T" * 511 + b"A", b"N" * 70, b"ACGTNNNACGTnnacgt" * 40]
-    words += [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (255, 256, 257, 511, 513, 2047, 2049, 8191, 8193, 16384)]
+    words += [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (255, 256, 257, 511, 513, 2047, 2049, 8191, 8193, 16384, 16385, 32769, 49152)]
     flat, offs = H.pack_strs(words)
     enc = run_device(toks[name], flat, offs, padding=False, add_special_tokens=False)
     ids = enc["input_ids"].cpu().numpy()
@@ -138,7 +138,7 @@ def test_bpe_homopolymers_and_long_words(toks, name):
 
 
 def test_bpe_word_over_limit_raises(toks):
-    flat, offs = H.pack_strs([b"ACGT" * 5000])          # 20,000 bytes > 16,384
+    flat, offs = H.pack_strs([b"ACGT" * 13000])         # 52,000 bytes > 49,152
     with pytest.raises(RuntimeError, match="word limit"):
         run_device(toks["bpe4096"], flat, offs, padding=False)
 
@@ -259,3 +259,30 @@ def test_kmer_very_long_rows_use_block_kernel(toks):
         o_ids, o_mask = H.oracle_batch("kmer6", flat, offs, **okw)
         assert np.array_equal(enc["input_ids"].cpu().numpy(), o_ids)
         assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
+
+
+def test_bpe_table_with_late_created_operands_single_step():
+    """A merge list whose operands are created by LATER ranks (not what BpeTrainer emits): the kernel
+    must fall back to one merge per round and still equal the queue semantics of the checker."""
+    from dnatok_b200.tables import Specials, TokenizerSpec
+    from dnatok_b200.tokenizer import B200Tokenizer
+    from oracle import oracle
+    lut = np.full(256, 1, np.int32)
+    for i, c in enumerate("ACGT"):
+        lut[ord(c)] = 5 + i
+    # rank 0 names token 10 ("AC"), which only rank 1 creates; rank 4 names 14, created by rank 5
+    a = np.array([10, 5, 7, 12, 14, 8, 6, 9], np.int32)
+    b = np.array([8, 6, 7, 12, 5, 8, 7, 9], np.int32)
+    o = np.array([11, 10, 12, 13, 15, 14, 9, 16], np.int32)
+    spec = TokenizerSpec("bpe", Specials(0, 1, 2, 3), 32, lut, merge_a=a, merge_b=b, merge_out=o)
+    tok = B200Tokenizer(spec, device=0)
+    table = oracle.BpeTable(a, b, o)
+    rng = np.random.default_rng(5)
+    words = [bytes(np.frombuffer(b"ACGT", np.uint8)[rng.integers(0, 4, int(n))]) for n in rng.integers(1, 400, 40)]
+    words += [b"ACT" * 50, b"GGGGGGGGGGGGGGGGG", b"TTA" * 33, b"ACTTTTACGGGG" * 20, b"CGCGCGCGCG" * 9]
+    flat, offs = H.pack_strs(words)
+    enc = run_device(tok, flat, offs, padding=False, add_special_tokens=False)
+    ids = enc["input_ids"].cpu().numpy()
+    oo = enc["offsets"].cpu().numpy()
+    for i, w in enumerate(words):
+        assert ids[oo[i]:oo[i + 1]].tolist() == oracle.bpe_word(table, w, lut), i
