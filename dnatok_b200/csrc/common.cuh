@@ -58,6 +58,30 @@ __device__ __forceinline__ void block_write_mask_row(M* row, int64_t stride, int
     block_write_run<M>(row, stride, [=](int64_t j) { return (M)((j >= lo && j < hi) ? 1 : 0); });
 }
 
+// Warp-level variants: the 32 lanes of one warp write dst[0..m).
+template <typename T, typename F>
+__device__ __forceinline__ void warp_write_run(T* dst, int64_t m, int lane, F f) {
+    constexpr int N = Vec16<T>::N;
+    if (m <= 0) return;
+    int64_t head = (N - (int64_t)((reinterpret_cast<uintptr_t>(dst) / sizeof(T)) % N)) % N;
+    if (head > m) head = m;
+    for (int64_t j = lane; j < head; j += 32) dst[j] = f(j);
+    const int64_t nv = (m - head) / N;
+    for (int64_t v = lane; v < nv; v += 32) {
+        T vals[N];
+        const int64_t j0 = head + v * N;
+#pragma unroll
+        for (int e = 0; e < N; ++e) vals[e] = f(j0 + e);
+        store_vec<T>(dst + j0, vals);
+    }
+    for (int64_t j = head + nv * N + lane; j < m; j += 32) dst[j] = f(j);
+}
+
+template <typename M>
+__device__ __forceinline__ void warp_mask_row(M* row, int64_t stride, int64_t lo, int64_t hi, int lane) {
+    warp_write_run<M>(row, stride, lane, [=](int64_t j) { return (M)((j >= lo && j < hi) ? 1 : 0); });
+}
+
 __device__ __forceinline__ void block_write_mask_any(void* mask, int mask_bits, int64_t row,
                                                      int64_t stride, int64_t lo, int64_t hi) {
     if (mask_bits == 64) block_write_mask_row<int64_t>((int64_t*)mask + row * stride, stride, lo, hi);

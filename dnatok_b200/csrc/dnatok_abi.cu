@@ -78,6 +78,7 @@ struct dnatok_handle {
     int k = 0;
     std::vector<int32_t> kmer_ids;
     int32_t kmer_affine_base = -1;     // >= 0 when kmer_ids[i] == base + i for every i
+    bool lut_identity = false;         // char: id == byte value for every byte (byte-level tokenizers)
     BpeHostTable bpe;
     std::mutex mu;
     std::map<int, DeviceTables> dev;
@@ -246,15 +247,18 @@ int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, 
                 int32_t* lengths, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
     if (n_rows == 0) return 0;
     if (rf.out_stride > 0) {
-        const int64_t tpr = (rf.out_stride + EMIT_TILE - 1) / EMIT_TILE;
-        const int64_t n_tiles = tpr * n_rows;
-        const unsigned grid = (unsigned)(n_tiles < (int64_t)d.sm_count * 64 ? n_tiles : (int64_t)d.sm_count * 64);
+        const int64_t spr = (rf.out_stride + EMIT_SPAN - 1) / EMIT_SPAN;
+        const int64_t n_spans = spr * n_rows;
+        const int64_t blocks = (n_spans + EMIT_WARPS - 1) / EMIT_WARPS;
+        const unsigned grid = (unsigned)(blocks < (int64_t)d.sm_count * 32 ? blocks : (int64_t)d.sm_count * 32);
+        const uint8_t* sb = reinterpret_cast<const uint8_t*>(src);
+        const uint8_t* se = sb + (size_t)total_bytes * sizeof(SrcT);
         if (id_bits == 64)
-            emit_padded_kernel<SrcT, int64_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, offsets, counts, n_rows, d.lut256, rf,
-                                                                                  (int64_t*)ids, mask, lengths, status, tpr, n_tiles);
+            emit_padded_kernel<SrcT, int64_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
+                                                                                  (int64_t*)ids, mask, lengths, status, spr, n_spans);
         else
-            emit_padded_kernel<SrcT, int32_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, offsets, counts, n_rows, d.lut256, rf,
-                                                                                  (int32_t*)ids, mask, lengths, status, tpr, n_tiles);
+            emit_padded_kernel<SrcT, int32_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
+                                                                                  (int32_t*)ids, mask, lengths, status, spr, n_spans);
         LAUNCH_CHECK("emit_padded_kernel");
     } else {
         const int64_t bound = total_bytes + 2 * n_rows;
@@ -369,6 +373,8 @@ int dnatok_create_char(const int32_t lut[256], const dnatok_specials* sp, dnatok
     if (!h) return fail(DNATOK_ERR_INVALID, "out of memory");
     h->kind = DNATOK_KIND_CHAR; h->sp = *sp;
     h->lut256.assign(lut, lut + 256);
+    h->lut_identity = true;
+    for (int i = 0; i < 256; ++i) h->lut_identity = h->lut_identity && lut[i] == i;
     *out = h;
     return DNATOK_OK;
 }
@@ -486,6 +492,9 @@ int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
     if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
     switch (h->kind) {
         case DNATOK_KIND_CHAR:
+            if (h->lut_identity)
+                return launch_emit<uint8_t, false>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits,
+                                                   d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
             return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits,
                                               d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
         case DNATOK_KIND_KMER:
@@ -535,9 +544,13 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
     if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
     if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
-    if (h->kind == DNATOK_KIND_CHAR)
+    if (h->kind == DNATOK_KIND_CHAR) {
+        if (h->lut_identity)
+            return launch_emit<uint8_t, false>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits, d_ids,
+                                               d_mask, d_lengths, nullptr, d_status, st);
         return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits, d_ids,
                                           d_mask, d_lengths, nullptr, d_status, st);
+    }
     return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
                               nullptr, d_status, st);
 }

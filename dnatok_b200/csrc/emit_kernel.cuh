@@ -15,69 +15,136 @@ __device__ __forceinline__ int32_t emit_load(const SrcT* __restrict__ p, const i
     return (int32_t)__ldg(p);
 }
 
+constexpr int EMIT_WARPS = EMIT_THREADS / 32;
+constexpr int EMIT_SPAN = 512;           // output columns one warp produces per trip
+
 // Padded output [n_rows, out_stride].  counts == nullptr: a row's content is its byte span.
+//
+// A warp takes 512 consecutive columns of one row.  The source elements under those columns are
+// fetched as aligned 16-byte chunks (one or two per lane) into a per-warp shared-memory window,
+// whatever the row's byte alignment and the one-column shift a leading special token causes; each
+// lane then reads the N = 16/sizeof(IdT) elements of its output vector back as aligned words plus a
+// funnel shift, maps them (LUT or identity) and issues one 16-byte store, so both the global loads
+// and the global stores of a warp are contiguous.  Vectors that touch a special token, the
+// truncation point or the padding take a per-column route.
 template <typename SrcT, typename IdT, bool USE_LUT>
 __global__ void __launch_bounds__(EMIT_THREADS)
-emit_padded_kernel(const SrcT* __restrict__ src, const int64_t* __restrict__ offsets,
+emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src_begin,
+                   const uint8_t* __restrict__ src_end, const int64_t* __restrict__ offsets,
                    const int32_t* __restrict__ counts, int64_t n_rows,
                    const int32_t* __restrict__ lut, RowFormat f, IdT* __restrict__ ids,
                    void* __restrict__ mask, int32_t* __restrict__ lengths_out,
-                   int32_t* __restrict__ status, int64_t tiles_per_row, int64_t n_tiles) {
+                   int32_t* __restrict__ status, int64_t spans_per_row, int64_t n_spans) {
+    constexpr int N = Vec16<IdT>::N;
+    constexpr int SZ = (int)sizeof(SrcT);
+    constexpr int CHUNKS = EMIT_SPAN * SZ / 16 + 1;          // 16-byte chunks covering a span at any alignment
+    constexpr int VB = N * SZ;                                // source bytes under one output vector: 2, 4 or 8
     __shared__ int32_t s_lut[256];
+    __shared__ uint4 s_win[EMIT_WARPS][CHUNKS + 1];
     if (USE_LUT) {
         for (int i = threadIdx.x; i < 256; i += EMIT_THREADS) s_lut[i] = lut[i];
         __syncthreads();
     }
-    constexpr int N = Vec16<IdT>::N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t* win = reinterpret_cast<const uint32_t*>(s_win[warp]);
     const bool has_cls = f.cls_id >= 0, has_sep = f.sep_id >= 0;
     const int64_t stride = f.out_stride;
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t row = tile / tiles_per_row;
-        const int64_t c0 = (tile - row * tiles_per_row) * EMIT_TILE;
+    const bool small = n_spans <= 0x7fffffff;
+
+    for (int64_t span = (int64_t)blockIdx.x * EMIT_WARPS + warp; span < n_spans; span += (int64_t)gridDim.x * EMIT_WARPS) {
+        int64_t row;
+        int64_t cs;
+        if (small) {
+            const uint32_t r32 = (uint32_t)span / (uint32_t)spans_per_row;
+            row = r32;
+            cs = (int64_t)((uint32_t)span - r32 * (uint32_t)spans_per_row) * EMIT_SPAN;
+        } else {
+            row = span / spans_per_row;
+            cs = (span - row * spans_per_row) * EMIT_SPAN;
+        }
         const int64_t off = offsets[row];
         const int64_t n_in = counts ? (int64_t)counts[row] : offsets[row + 1] - off;
         const int64_t n = n_in < f.cap_content ? n_in : f.cap_content;
         const int64_t T = n + (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
         const int64_t shift = f.pad_left ? stride - T : 0;
-        if (c0 == 0 && threadIdx.x == 0) {
+        const int64_t first = shift + (has_cls ? 1 : 0);      // column of content element 0
+        if (cs == 0 && lane == 0) {
             if (lengths_out) lengths_out[row] = (int32_t)T;
             if (status && f.clip_is_error && n_in > n) atomicOr(status + row, 4);
         }
-        const SrcT* srow = src + off - (has_cls ? 1 : 0);
-        IdT* orow = ids + row * stride;
-        const bool aligned = ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
-        int64_t c_end = c0 + EMIT_TILE < stride ? c0 + EMIT_TILE : stride;
-        for (int64_t c = c0 + (int64_t)threadIdx.x * N; c < c_end; c += (int64_t)EMIT_THREADS * N) {
-            IdT vals[N];
+        const int ncol = (int)(stride - cs < EMIT_SPAN ? stride - cs : EMIT_SPAN);   // columns of this span
+        IdT* orow = ids + row * stride + cs;
+        const bool aligned = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
+
+        // ---- stage the source window: element (cs - first + j) for j in [0, 512)
+        const int64_t t_lo = cs - first;
+        const uint8_t* wptr = reinterpret_cast<const uint8_t*>(src + off) + t_lo * SZ;
+        const int a = (int)(reinterpret_cast<uintptr_t>(wptr) & 15);
+        const uint8_t* wbase = wptr - a;
+        // only chunks that can hold content of this row are fetched
+        const int64_t t_hi = t_lo + ncol;                     // one past the last element wanted
+        const bool any_content = t_hi > 0 && t_lo < n;
+        __syncwarp();
+        if (any_content) {
+            for (int k = lane; k < CHUNKS; k += 32) {
+                const uint8_t* g = wbase + 16 * k;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (g >= src_begin && g + 16 <= src_end) v = __ldg(reinterpret_cast<const uint4*>(g));
+                else {
+                    uint8_t tmp[16];
 #pragma unroll
-            for (int e = 0; e < N; ++e) {
-                const int64_t t = c + e - shift;
-                int32_t v = f.pad_id;
-                if (t >= 0 && t < T && c + e < stride) {
-                    if (has_cls && t == 0) v = f.cls_id;
-                    else if (has_sep && t == T - 1) v = f.sep_id;
-                    else v = emit_load<SrcT, USE_LUT>(srow + t, s_lut);
+                    for (int b = 0; b < 16; ++b) tmp[b] = (g + b >= src_begin && g + b < src_end) ? __ldg(g + b) : (uint8_t)0;
+                    v = *reinterpret_cast<uint4*>(tmp);
                 }
-                vals[e] = (IdT)v;
-            }
-            if (aligned && c + N <= stride) store_vec<IdT>(orow + c, vals);
-            else {
-#pragma unroll
-                for (int e = 0; e < N; ++e) if (c + e < stride) orow[c + e] = vals[e];
+                s_win[warp][k] = v;
             }
         }
+        __syncwarp();
+
+        // ---- ids
+        for (int v = lane; v * N < ncol; v += 32) {
+            const int c0 = v * N;                              // column within the span
+            const int boff = a + c0 * SZ;                      // byte offset of the vector's source in the window
+            const uint32_t sh = (uint32_t)(boff & 3) * 8u;
+            const uint32_t* wp = win + (boff >> 2);
+            uint32_t lo = 0, hi = 0;
+            if (any_content) {
+                const uint32_t w0 = wp[0], w1 = wp[1];
+                lo = __funnelshift_r(w0, w1, sh);
+                if (VB > 4) hi = __funnelshift_r(w1, wp[2], sh);
+            }
+            IdT vals[N];
+            const int64_t t0 = t_lo + c0;
+            const bool interior = t0 >= 0 && t0 + N <= n && c0 + N <= ncol;
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                uint32_t word = (e * SZ < 4) ? lo : hi;
+                uint32_t x = SZ == 1 ? (word >> (8 * (e & 3))) & 0xFFu : (word >> (16 * (e & 1))) & 0xFFFFu;
+                int32_t val = USE_LUT ? s_lut[x & 0xFFu] : (int32_t)x;
+                if (!interior) {
+                    const int64_t t = t0 + e;                  // content index of this column
+                    const int64_t col = cs + c0 + e - shift;   // token index within the row
+                    if (t < 0 || t >= n) {
+                        val = f.pad_id;
+                        if (has_cls && col == 0) val = f.cls_id;
+                        else if (has_sep && col == T - 1 && col >= 0) val = f.sep_id;
+                    }
+                }
+                vals[e] = (IdT)val;
+            }
+            if (aligned && c0 + N <= ncol) store_vec<IdT>(orow + c0, vals);
+            else {
+#pragma unroll
+                for (int e = 0; e < N; ++e) if (c0 + e < ncol) orow[c0 + e] = vals[e];
+            }
+        }
+
+        // ---- mask: ones on [shift, shift + T)
         if (f.mask_bits) {
-            // this tile's slice of the mask row
-            const int64_t lo = shift - c0, hi = shift + T - c0, m = c_end - c0;
-            if (f.mask_bits == 64)
-                block_write_run<int64_t>((int64_t*)mask + row * stride + c0, m,
-                                         [=](int64_t j) { return (int64_t)((j >= lo && j < hi) ? 1 : 0); });
-            else if (f.mask_bits == 32)
-                block_write_run<int32_t>((int32_t*)mask + row * stride + c0, m,
-                                         [=](int64_t j) { return (int32_t)((j >= lo && j < hi) ? 1 : 0); });
-            else
-                block_write_run<uint8_t>((uint8_t*)mask + row * stride + c0, m,
-                                         [=](int64_t j) { return (uint8_t)((j >= lo && j < hi) ? 1 : 0); });
+            const int64_t lo = shift - cs, hi = shift + T - cs;
+            if (f.mask_bits == 64) warp_mask_row<int64_t>((int64_t*)mask + row * stride + cs, ncol, lo, hi, lane);
+            else if (f.mask_bits == 32) warp_mask_row<int32_t>((int32_t*)mask + row * stride + cs, ncol, lo, hi, lane);
+            else warp_mask_row<uint8_t>((uint8_t*)mask + row * stride + cs, ncol, lo, hi, lane);
         }
     }
 }

@@ -209,29 +209,6 @@ template <typename IdT> struct IdPair;
 template <> struct IdPair<int64_t> { using type = longlong2; };
 template <> struct IdPair<int32_t> { using type = int2; };
 
-template <typename T, typename F>
-__device__ __forceinline__ void warp_write_run(T* dst, int64_t m, int lane, F f) {
-    constexpr int N = Vec16<T>::N;
-    if (m <= 0) return;
-    int64_t head = (N - (int64_t)((reinterpret_cast<uintptr_t>(dst) / sizeof(T)) % N)) % N;
-    if (head > m) head = m;
-    for (int64_t j = lane; j < head; j += 32) dst[j] = f(j);
-    const int64_t nv = (m - head) / N;
-    for (int64_t v = lane; v < nv; v += 32) {
-        T vals[N];
-        const int64_t j0 = head + v * N;
-#pragma unroll
-        for (int e = 0; e < N; ++e) vals[e] = f(j0 + e);
-        store_vec<T>(dst + j0, vals);
-    }
-    for (int64_t j = head + nv * N + lane; j < m; j += 32) dst[j] = f(j);
-}
-
-template <typename M>
-__device__ __forceinline__ void warp_mask_row(M* row, int64_t stride, int64_t lo, int64_t hi, int lane) {
-    warp_write_run<M>(row, stride, lane, [=](int64_t j) { return (M)((j >= lo && j < hi) ? 1 : 0); });
-}
-
 // AFFINE: the 4**K table is base + index (checked on the host), so no gather is needed.
 // FUSE_MASK: the mask has the ids' element type and is stored next to each id in the main loop.
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
