@@ -7,6 +7,7 @@
 #include <climits>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -24,6 +25,8 @@ namespace {
 
 thread_local std::string g_err;
 std::atomic<int64_t> g_launches{0};
+std::atomic<int64_t> g_host_chunk_bytes{256ll << 20};        // bytes (in + out) per chunk of the host pipeline
+std::atomic<int64_t> g_host_chunk_threshold{4ll << 30};      // batches below this size are not chunked
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -67,6 +70,17 @@ struct DeviceTables {
     int64_t* st_out_offsets = nullptr;
     void* st_scratch = nullptr;   size_t st_scratch_cap = 0;
     cudaStream_t stream = nullptr;
+    // chunked host pipeline: three independent slots (buffers + stream), grow only
+    struct PipeSlot {
+        cudaStream_t stream = nullptr;
+        void* bytes = nullptr;   size_t bytes_cap = 0;
+        void* offsets = nullptr; size_t offsets_cap = 0;
+        void* ids = nullptr;     size_t ids_cap = 0;
+        void* mask = nullptr;    size_t mask_cap = 0;
+        void* rows = nullptr;    size_t rows_cap = 0;      // lengths then status, int32 each
+        void* scratch = nullptr; size_t scratch_cap = 0;
+        int64_t* h_offsets = nullptr; size_t h_offsets_cap = 0;   // pinned, chunk-local offsets
+    } pipe[3];
 };
 
 }  // namespace
@@ -360,6 +374,13 @@ int dnatok_version(void) { return DNATOK_ABI_VERSION; }
 const char* dnatok_last_error(void) { return g_err.c_str(); }
 int64_t dnatok_launch_count(void) { return g_launches.load(); }
 
+int dnatok_set_option(const char* name, int64_t value) {
+    if (!name || value < 0) return fail(DNATOK_ERR_INVALID, "bad option");
+    if (!strcmp(name, "host_chunk_bytes")) { g_host_chunk_bytes = value; return DNATOK_OK; }
+    if (!strcmp(name, "host_chunk_threshold")) { g_host_chunk_threshold = value; return DNATOK_OK; }
+    return fail(DNATOK_ERR_INVALID, "unknown option %s", name);
+}
+
 static int check_specials(const dnatok_specials* sp) {
     if (!sp) return fail(DNATOK_ERR_INVALID, "specials is NULL");
     if (sp->pad_id < 0) return fail(DNATOK_ERR_INVALID, "pad_id < 0");
@@ -425,6 +446,11 @@ void dnatok_destroy(dnatok_handle* h) {
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);
+        for (auto& ps : d.pipe) {
+            if (ps.stream) { cudaStreamSynchronize(ps.stream); cudaStreamDestroy(ps.stream); }
+            for (void* p : {ps.bytes, ps.offsets, ps.ids, ps.mask, ps.rows, ps.scratch}) if (p) cudaFree(p);
+            if (ps.h_offsets) cudaFreeHost(ps.h_offsets);
+        }
     }
     if (!h->dev.empty()) cudaSetDevice(cur);
     delete h;
@@ -619,6 +645,59 @@ static int grow(void** p, size_t* cap, size_t need) {
     return 0;
 }
 
+// Fixed-stride output in row chunks over three slots: while chunk c is being encoded, chunk c+1 is
+// on its way in and chunk c-1 on its way out, so the two PCIe directions and the kernels overlap.
+// Every chunk is an independent sub-batch with chunk-local offsets, which also bounds the staging
+// memory by the chunk size instead of the batch size.
+static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, const uint8_t* h_bytes, const int64_t* h_offsets,
+                                 int64_t n_rows, const dnatok_format* f, int64_t rows_per_chunk, void* h_ids,
+                                 void* h_mask, int32_t* h_lengths, int32_t* h_status) {
+    const size_t id_sz = f->id_bits / 8, mask_sz = (f->mask_bits && h_mask) ? f->mask_bits / 8 : 0;
+    const int64_t stride = f->out_stride;
+    dnatok_format cf = *f;
+    if (!mask_sz) cf.mask_bits = 0;
+    int64_t chunk = 0;
+    for (int64_t r0 = 0; r0 < n_rows; r0 += rows_per_chunk, ++chunk) {
+        const int64_t r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
+        const int64_t rows = r1 - r0;
+        const int64_t b0 = h_offsets[r0], nbytes = h_offsets[r1] - b0;
+        DeviceTables::PipeSlot& ps = d->pipe[chunk % 3];
+        if (!ps.stream) CUDA_TRY(cudaStreamCreateWithFlags(&ps.stream, cudaStreamNonBlocking));
+        CUDA_TRY(cudaStreamSynchronize(ps.stream));           // the slot's previous chunk has left
+        if (int rc = grow(&ps.bytes, &ps.bytes_cap, (size_t)nbytes + 64)) return rc;
+        if (int rc = grow(&ps.offsets, &ps.offsets_cap, (size_t)(rows + 1) * 8)) return rc;
+        if (int rc = grow(&ps.ids, &ps.ids_cap, (size_t)(rows * stride) * id_sz + 64)) return rc;
+        if (mask_sz) if (int rc = grow(&ps.mask, &ps.mask_cap, (size_t)(rows * stride) * mask_sz + 64)) return rc;
+        if (int rc = grow(&ps.rows, &ps.rows_cap, (size_t)rows * 8 + 64)) return rc;
+        const size_t sneed = dnatok_scratch_bytes(h, rows, nbytes);
+        if (sneed) if (int rc = grow(&ps.scratch, &ps.scratch_cap, sneed)) return rc;
+        if ((size_t)(rows + 1) * 8 > ps.h_offsets_cap) {
+            if (ps.h_offsets) CUDA_TRY(cudaFreeHost(ps.h_offsets));
+            ps.h_offsets = nullptr; ps.h_offsets_cap = 0;
+            const size_t cap = (size_t)(rows + 1) * 8 + 4096;
+            CUDA_TRY(cudaMallocHost((void**)&ps.h_offsets, cap));
+            ps.h_offsets_cap = cap;
+        }
+        for (int64_t i = 0; i <= rows; ++i) ps.h_offsets[i] = h_offsets[r0 + i] - b0;
+        int32_t* d_len = (int32_t*)ps.rows;
+        int32_t* d_st = d_len + rows;
+        if (nbytes) CUDA_TRY(cudaMemcpyAsync(ps.bytes, h_bytes + b0, (size_t)nbytes, cudaMemcpyHostToDevice, ps.stream));
+        CUDA_TRY(cudaMemcpyAsync(ps.offsets, ps.h_offsets, (size_t)(rows + 1) * 8, cudaMemcpyHostToDevice, ps.stream));
+        if (int rc = dnatok_encode(h, (const uint8_t*)ps.bytes, (const int64_t*)ps.offsets, rows, nbytes, &cf, ps.ids,
+                                   mask_sz ? ps.mask : nullptr, d_len, nullptr, d_st, ps.scratch, ps.scratch_cap, ps.stream))
+            return rc;
+        CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_ids + (size_t)(r0 * stride) * id_sz, ps.ids, (size_t)(rows * stride) * id_sz,
+                                 cudaMemcpyDeviceToHost, ps.stream));
+        if (mask_sz)
+            CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_mask + (size_t)(r0 * stride) * mask_sz, ps.mask,
+                                     (size_t)(rows * stride) * mask_sz, cudaMemcpyDeviceToHost, ps.stream));
+        if (h_lengths) CUDA_TRY(cudaMemcpyAsync(h_lengths + r0, d_len, (size_t)rows * 4, cudaMemcpyDeviceToHost, ps.stream));
+        if (h_status) CUDA_TRY(cudaMemcpyAsync(h_status + r0, d_st, (size_t)rows * 4, cudaMemcpyDeviceToHost, ps.stream));
+    }
+    for (auto& ps : d->pipe) if (ps.stream) CUDA_TRY(cudaStreamSynchronize(ps.stream));
+    return DNATOK_OK;
+}
+
 int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, const int64_t* h_offsets,
                        int64_t n_rows, const dnatok_format* fmt, void* h_ids, int64_t ids_capacity, void* h_mask,
                        int32_t* h_lengths, int64_t* h_out_offsets, int32_t* h_status, int64_t* out_stride_used) {
@@ -636,6 +715,42 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
     const int ns = n_special(h, fmt);
     const size_t id_sz = fmt->id_bits / 8, mask_sz = fmt->mask_bits / 8;
 
+    {
+        // Fixed stride known up front (given, or char rows padded to the longest): chunked pipeline
+        // when the batch is large enough to split.
+        int64_t pstride = fmt->out_stride;
+        if (pstride < 0 && h->kind == DNATOK_KIND_CHAR) {
+            const int64_t cap = fmt->max_tokens > 0 ? fmt->max_tokens - ns : INT64_MAX;
+            pstride = 0;
+            for (int64_t i = 0; i < n_rows; ++i) {
+                int64_t n = h_offsets[i + 1] - h_offsets[i];
+                if (n > cap) n = cap;
+                if (n + ns > pstride) pstride = n + ns;
+            }
+        }
+        if (pstride > 0 && n_rows >= 2) {
+            const size_t row_out = (size_t)pstride * (id_sz + ((mask_sz && h_mask) ? mask_sz : 0));
+            const size_t out_total = row_out * (size_t)n_rows;
+            // Chunking bounds the staging memory; on a link whose two directions share one budget it
+            // does not shorten the call, so by default only batches of 4 GiB and more are split.
+            const size_t CHUNK_BYTES = (size_t)g_host_chunk_bytes.load();
+            const size_t threshold = (size_t)g_host_chunk_threshold.load();
+            if (CHUNK_BYTES && out_total + (size_t)total >= threshold && out_total + (size_t)total >= 2 * CHUNK_BYTES) {
+                if ((int64_t)(out_total / (id_sz + ((mask_sz && h_mask) ? mask_sz : 0))) > ids_capacity)
+                    return fail(DNATOK_ERR_CAPACITY, "ids buffer holds %lld elements, %lld needed", (long long)ids_capacity,
+                                (long long)(n_rows * pstride));
+                const size_t per_row = row_out + (size_t)(total / n_rows) + 1;
+                int64_t rpc = (int64_t)(CHUNK_BYTES / per_row);
+                if (rpc < 1) rpc = 1;
+                dnatok_format pf = *fmt;
+                pf.out_stride = pstride;
+                if (int rc = encode_host_pipelined(h, d, h_bytes, h_offsets, n_rows, &pf, rpc, h_ids, h_mask, h_lengths, h_status))
+                    return rc;
+                if (out_stride_used) *out_stride_used = pstride;
+                return DNATOK_OK;
+            }
+        }
+    }
     if (int rc = grow((void**)&d->st_bytes, &d->st_bytes_cap, (size_t)total + 64)) return rc;
     if (int rc = grow((void**)&d->st_offsets, &d->st_offsets_cap, (size_t)(n_rows + 1) * 8)) return rc;
     if ((size_t)n_rows + 1 > d->st_rows_cap) {

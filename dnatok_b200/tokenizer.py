@@ -327,8 +327,13 @@ class B200Tokenizer:
                            max_tokens=max_tokens, out_stride=stride)
         if stride > 0:
             cap = B * stride
-        else:
+        elif ragged:
             cap = int(offsets[-1]) + ns * B
+        else:                                     # padded to the longest row: no row has more tokens than bytes
+            longest = int(np.diff(offsets).max()) if B else 0
+            if max_tokens:
+                longest = min(longest, max_tokens - ns)
+            cap = B * (longest + ns)
         if out_ids is None or out_ids.size < cap:
             out_ids = np.empty(max(cap, 1), dtype=ids_dtype)
         if mask_bits and (out_mask is None or out_mask.size < cap):

@@ -163,6 +163,12 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes,
                        void* h_ids, int64_t ids_capacity, void* h_mask, int32_t* h_lengths,
                        int64_t* h_out_offsets, int32_t* h_status, int64_t* out_stride_used);
 
+/* Process-wide tuning knobs (no reference counterpart):
+ *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
+ *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)
+ *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB) */
+int dnatok_set_option(const char* name, int64_t value);
+
 /* Number of kernels this library has launched from the calling process (for accounting). */
 int64_t dnatok_launch_count(void);
 

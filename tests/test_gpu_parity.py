@@ -286,3 +286,35 @@ def test_bpe_table_with_late_created_operands_single_step():
     oo = enc["offsets"].cpu().numpy()
     for i, w in enumerate(words):
         assert ids[oo[i]:oo[i + 1]].tolist() == oracle.bpe_word(table, w, lut), i
+
+
+@pytest.mark.parametrize("name,rows,length,kw", [
+    ("char", 8192, 1024, dict(padding="longest")),
+    ("kmer6", 4096, 6000, dict(padding="max_length", max_length=1000, truncation=True, add_special_tokens=False)),
+    ("bpe4096", 6144, 1024, dict(padding="max_length", max_length=768)),
+])
+def test_host_entry_chunked_pipeline(toks, name, rows, length, kw):
+    """Batches large enough for dnatok_encode_host to split into overlapping chunks (several slots reused)."""
+    gen = {"char": synth.config1, "kmer6": synth.config2, "bpe4096": synth.config3}[name]
+    flat, offs = synth.pack_rows(gen(batch=rows, length=length, seed=1234))
+    # ragged tail so the chunks differ in size
+    lens = np.diff(offs)
+    lens[-7:] = [0, 1, 5, length // 2, 17, length - 1, 3]
+    offs2 = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat2 = np.concatenate([flat[offs[i]:offs[i] + lens[i]] for i in range(rows - 7, rows)])
+    flat = np.concatenate([flat[:offs[rows - 7]], flat2])
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 16 << 20))
+    _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 0))
+    try:
+        enc = toks[name].encode_host((flat, offs2), **kw)
+    finally:
+        _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 256 << 20))
+        _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 4 << 30))
+    okw = dict(kw)
+    okw["add_special"] = okw.pop("add_special_tokens", True)
+    o_ids, o_mask = H.oracle_batch(name, flat, offs2, **okw)
+    assert np.array_equal(enc["input_ids"], o_ids)
+    assert np.array_equal(enc["attention_mask"], o_mask)
+    assert np.array_equal(enc["lengths"], o_mask.sum(axis=1))
