@@ -67,20 +67,32 @@ __device__ __forceinline__ uint32_t run_parity(uint32_t c, bool prev_odd) {
     return (fe & 0x55555555u) | (fo & 0xAAAAAAAAu);
 }
 
-// Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].
+// Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].  One atomic per
+// warp and class (rows of a batch mostly share a class).
 __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t n_rows,
                                     int32_t* __restrict__ class_count, int32_t* __restrict__ class_list,
                                     int32_t* __restrict__ counts, int32_t* __restrict__ status) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_rows) return;
-    const int64_t n = offsets[i + 1] - offsets[i];
-    counts[i] = 0;
-    if (n <= 0) return;
-    int c = 0;
-    while (c < BPE_N_CLASSES && (int64_t)bpe_class_capacity(c) < n) ++c;
-    if (c >= BPE_N_CLASSES) { if (status) atomicOr(status + i, 1); return; }
-    const int slot = atomicAdd(class_count + c, 1);
-    class_list[(int64_t)c * n_rows + slot] = (int32_t)i;
+    const int lane = threadIdx.x & 31;
+    int c = -1;
+    if (i < n_rows) {
+        const int64_t n = offsets[i + 1] - offsets[i];
+        counts[i] = 0;
+        if (n > 0) {
+            c = 0;
+            while (c < BPE_N_CLASSES && (int64_t)bpe_class_capacity(c) < n) ++c;
+            if (c >= BPE_N_CLASSES) { if (status) atomicOr(status + i, 1); c = -1; }
+        }
+    }
+    for (int k = 0; k < BPE_N_CLASSES; ++k) {
+        const uint32_t m = __ballot_sync(0xffffffffu, c == k);
+        if (m == 0) continue;
+        const int leader = __ffs(m) - 1;
+        int base = 0;
+        if (lane == leader) base = atomicAdd(class_count + k, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (c == k) class_list[(int64_t)k * n_rows + base + __popc(m & ((1u << lane) - 1u))] = (int32_t)i;
+    }
 }
 
 template <int C>
