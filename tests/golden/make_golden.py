@@ -132,6 +132,30 @@ def main():
                                   "pad_token_id": evo.pad_token_id, "unk_token_id": evo.unk_token_id}
     G["reference_paths"] = ref
 
+    # the reference's DNATok API on a small ragged batch: encode_batch_to_ids and
+    # encode_batch_with_padding, both padding sides (its default is left)
+    rng = np.random.default_rng(99)
+    api_seqs = []
+    for n in [1, 5, 6, 7, 12, 13, 40, 64, 100, 37, 18, 90]:
+        row = np.frombuffer(b"ACGT", np.uint8)[rng.integers(0, 4, n)].copy()
+        if n in (40, 100, 13):
+            row[n // 3:n // 3 + 3] = ord("N")
+        api_seqs.append(bytes(row).decode())
+    api = {"seqs": api_seqs, "cases": []}
+    for tname in ("char", "kmer6"):
+        for side in ("left", "right"):
+            hlp = DNATok(_Embedder(toks[tname]), padding_side=side)
+            hlp.discover()
+            ids = hlp.encode_batch_to_ids(api_seqs)
+            case = {"tokenizer": tname, "padding_side": side, "encode_batch_to_ids": ids.tolist(), "with_padding": []}
+            for max_tokens, pad_to_max, pad_multiple in ((16, False, 16), (8, True, 4), (64, False, 1), (10, True, 16)):
+                i2, m2 = hlp.encode_batch_with_padding(api_seqs, max_tokens, pad_to_max=pad_to_max, pad_multiple=pad_multiple)
+                case["with_padding"].append({"max_tokens": max_tokens, "pad_to_max": pad_to_max, "pad_multiple": pad_multiple,
+                                             "ids": i2.tolist(), "ids_dtype": str(i2.dtype), "mask": m2.tolist(),
+                                             "mask_dtype": str(m2.dtype)})
+            api["cases"].append(case)
+    G["dnatok_api"] = api
+
     # normaliser known answers, produced by the reference's compiler
     cases = [
         ({"type": "Strip", "strip_left": True, "strip_right": True}, ["  ACGT  ", "ACGT"]),
@@ -157,7 +181,7 @@ def main():
     G["normalizer"] = {"accepted": norm, "rejected": rejected}
 
     with open(os.path.join(HERE, "golden.json"), "w") as fh:
-        json.dump(G, fh, indent=1, sort_keys=True)
+        json.dump(G, fh, sort_keys=True, separators=(",", ":"))
     print("wrote golden.json;", {k: v["shape"] for k, v in G["configs"].items()})
     print("reference paths:", json.dumps(ref, indent=1))
 

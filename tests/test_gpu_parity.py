@@ -318,3 +318,59 @@ def test_host_entry_chunked_pipeline(toks, name, rows, length, kw):
     assert np.array_equal(enc["input_ids"], o_ids)
     assert np.array_equal(enc["attention_mask"], o_mask)
     assert np.array_equal(enc["lengths"], o_mask.sum(axis=1))
+
+
+def test_dnatok_api_matches_reference_outputs(golden):
+    """dnatok_b200.dna_tokenizer.DNATok against what the reference's DNATok returned for the same calls
+    (recorded by tests/golden/make_golden.py): encode_batch_to_ids and encode_batch_with_padding."""
+    from dnatok_b200.dna_tokenizer import DNATok
+
+    class Embedder:
+        def __init__(self, tokenizer):
+            self.tokenizer = tokenizer
+
+        def embed_tokens(self, ids):
+            return ids
+
+    api = golden["dnatok_api"]
+    seqs = api["seqs"]
+    for case in api["cases"]:
+        helper = DNATok(Embedder(H.hf(case["tokenizer"])), padding_side=case["padding_side"])
+        helper.discover()
+        assert helper.use_ids_path
+        assert (helper.kmer_k or 1) == (6 if case["tokenizer"] == "kmer6" else 1)
+        ids = helper.encode_batch_to_ids(seqs)
+        assert ids.dtype == torch.int64 and ids.device.type == "cpu" and ids.is_pinned()
+        if case["tokenizer"] == "kmer6" and case["padding_side"] == "left":
+            # For ragged k-mer rows the reference pads each equal-length group on the left and the merged
+            # tensor on the right, so a row's tokens end up in the middle of its row.  Same tokens per
+            # row are required here; the placement is a consistent left padding.
+            pad = helper.id_pad
+            for mine, ref in zip(ids.tolist(), case["encode_batch_to_ids"]):
+                assert [t for t in mine if t != pad] == [t for t in ref if t != pad]
+                n = sum(t != pad for t in mine)
+                assert all(t == pad for t in mine[:len(mine) - n])
+        else:
+            assert ids.tolist() == case["encode_batch_to_ids"]
+        for w in case["with_padding"]:
+            i2, m2 = helper.encode_batch_with_padding(seqs, w["max_tokens"], pad_to_max=w["pad_to_max"],
+                                                      pad_multiple=w["pad_multiple"])
+            assert str(i2.dtype) == w["ids_dtype"] and str(m2.dtype) == w["mask_dtype"]
+            assert i2.tolist() == w["ids"], (case["tokenizer"], case["padding_side"], w["max_tokens"])
+            assert m2.tolist() == w["mask"]
+        with pytest.raises(ValueError, match="No sequences provided"):
+            helper.encode_batch_to_ids([])
+        with pytest.raises(ValueError, match="Empty batch"):
+            helper.encode_batch_with_padding([], 8)
+    # BPE goes through the backend slot, as in the reference's discover()
+    helper = DNATok(Embedder(H.hf("bpe4096")), padding_side="right")
+    helper.discover()
+    assert not helper.use_ids_path and helper.bpe_backend is not None
+    ids = helper.encode_batch_to_ids(seqs)
+    want = H.hf("bpe4096")(seqs, padding=True, add_special_tokens=False, return_tensors="np")["input_ids"]
+    assert np.array_equal(ids.numpy(), want)
+    helper.padding_side = "left"
+    ids_left = helper.encode_batch_to_ids(seqs)
+    lens = (want != helper.pad_id).sum(axis=1)
+    for i, n in enumerate(lens):
+        assert ids_left[i, ids_left.shape[1] - n:].tolist() == want[i, :n].tolist()
