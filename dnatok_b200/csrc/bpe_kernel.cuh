@@ -1,28 +1,34 @@
 // BPE merge engine: exact Hugging Face merge order in a handful of data-parallel rounds.
 //
-// One warp owns one pre-tokenised word, kept as a COMPACT array of 16-bit tokens in shared memory
-// (no links, no tombstones).  A round:
-//   A. every adjacent pair is looked up in the merge table (perfect hash, two dependent loads);
-//      its rank is stored and B = min over the present ranks r of F[r] is reduced, where F[r] is
-//      the lowest rank of any pair that contains the token rank r creates;
-//   B. pairs with rank < B are candidates.  Hugging Face would take them in (rank, position)
-//      order, skipping a pair when an earlier one consumed one of its tokens.  On a path that
-//      greedy choice has a closed form: follow the strictly improving priorities to the left and to
-//      the right of a candidate down to the local optimum; the candidate is taken iff both walks
-//      have even length.  The two parities are segmented prefix-XORs, computed 32 positions at a
-//      time with carry-propagating bit tricks on ballot masks (one backward sweep, one forward);
-//   C. the forward sweep also applies the selected merges and compacts the array in place.
-// Everything created in a round contains a new token, so it ranks >= B, above every pair merged
-// in that round: the round equals the sequential queue run over the same ranks.  Rounds repeat
-// until no pair has a rank: 5-7 rounds for DNA words of any length, ~3.3 position visits per
-// input byte in total.  Equal ranks on neighbouring pairs (runs of one token) fall out of the same
-// rule, because priority is (rank, position): every other pair from the left.
+// A word (one pre-tokenised row) is kept as a COMPACT array of 16-bit tokens in shared memory (no
+// links, no tombstones) and is owned by a team of W warps (W = 1 for short words, up to 8 for long
+// ones).  A round:
+//   1. every adjacent pair is looked up in the merge table (perfect hash, two dependent loads); its
+//      rank is stored, a bit "rank(i-1) <= rank(i)" goes into a per-32-positions mask, and
+//      B = min over the present ranks r of F[r] is reduced, where F[r] is the lowest rank of any
+//      pair that contains the token rank r creates;
+//   2. pairs with rank < B are candidates (one ballot mask per 32 positions).  Hugging Face would
+//      take them in (rank, position) order, skipping a pair when an earlier one consumed one of its
+//      tokens.  On a path that greedy choice has a closed form: follow the strictly improving
+//      priorities to the left and to the right of a candidate down to the local optimum; the
+//      candidate is taken iff both walks have even length;
+//   3. the two parities are prefix-XORs along runs of set bits in the masks.  They are computed on
+//      the masks themselves, one lane per 32 positions: carry-propagating bit tricks inside a mask,
+//      and a warp scan over the four possible carry functions (constant 0, constant 1, identity,
+//      negation) across masks.  The same step gives the selected pairs, the surviving positions
+//      and, by a warp prefix sum, where each group of 32 positions lands after compaction;
+//   4. selected merges are applied and the array is compacted in place, tile by tile.
+// Everything created in a round contains a new token, so it ranks >= B, above every pair merged in
+// that round: the round equals the sequential queue run over the same ranks.  Rounds repeat until no
+// pair has a rank: 5-7 rounds for DNA words of any length, ~3.3 position visits per input byte in
+// total.  Equal ranks on neighbouring pairs (runs of one token) fall out of the same rule, because
+// priority is (rank, position): every other pair from the left.
 //
 // A table whose merge operands may be created by later ranks has no usable F; for it the host
 // selects single_step: one merge per round, the leftmost pair of the lowest rank.
 //
-// Words are binned by length into capacity classes (shared memory per word = 4.125 bytes per
-// position); each class is one launch of resident warps that pull words from a shared counter.
+// Words are binned by length into capacity classes (shared memory per word = 4.375 bytes per
+// position); each class is one launch of resident teams that pull words from a shared counter.
 // Merged tokens (uint16, Hugging Face ids) and per-row counts go to the caller's scratch; the emit
 // kernels produce the final ids / mask layout.
 //
@@ -36,12 +42,17 @@ namespace dnatok {
 
 constexpr uint32_t BPE_NONE = 0xFFFFu;          // no rank
 constexpr int BPE_N_CLASSES = 9;
-constexpr int BPE_WARPS = 8;                    // warps (= words in flight) per block
+constexpr int BPE_BLOCK_WARPS = 8;              // warps per block; a block holds 8 / W words
 
 __host__ __device__ constexpr int bpe_class_capacity(int c) {
     return c < 8 ? (256 << c) : 49152;          // 256 ... 32768, 49152
 }
-__host__ __device__ constexpr int bpe_slot_bytes(int C) { return 4 * C + C / 8; }
+// warps that share one word of a class
+__host__ __device__ constexpr int bpe_class_team(int c) {
+    return c <= 2 ? 1 : c == 3 ? 2 : c == 4 ? 4 : 8;
+}
+// tokens + ranks (2 bytes each) + three 32-bit words per 32 positions
+__host__ __device__ constexpr int bpe_slot_bytes(int C) { return 4 * C + 3 * (C / 32) * 4; }
 
 struct BpeDeviceTable {
     const uint32_t* disp;        // [n_tokens] row displacement of the left token
@@ -65,6 +76,16 @@ __device__ __forceinline__ uint32_t run_parity(uint32_t c, bool prev_odd) {
     const uint32_t fe = c & ~(c + se);              // all bits of those runs
     const uint32_t fo = c & ~fe;
     return (fe & 0x55555555u) | (fo & 0xAAAAAAAAu);
+}
+
+// Carry functions {0,1} -> {0,1} as two bits: bit 0 = f(0), bit 1 = f(1).
+__device__ __forceinline__ uint32_t carry_fn(uint32_t c) {
+    return (run_parity(c, false) >> 31) | ((run_parity(c, true) >> 31) << 1);
+}
+__device__ __forceinline__ uint32_t carry_apply(uint32_t f, bool x) { return (f >> (x ? 1 : 0)) & 1u; }
+// first a, then b
+__device__ __forceinline__ uint32_t carry_then(uint32_t a, uint32_t b) {
+    return carry_apply(b, a & 1u) | (carry_apply(b, (a >> 1) & 1u) << 1);
 }
 
 // Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].  One atomic per
@@ -95,111 +116,202 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
     }
 }
 
-template <int C>
-__global__ void __launch_bounds__(BPE_WARPS * 32)
+// Barrier over the W warps of one team (team index `team` within the block).
+template <int W>
+__device__ __forceinline__ void team_sync(int team) {
+    if (W == 1) __syncwarp();
+    else if (W == BPE_BLOCK_WARPS) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(W * 32) : "memory");
+}
+
+// C: capacity in positions; W: warps per word.
+template <int C, int W>
+__global__ void __launch_bounds__(BPE_BLOCK_WARPS * 32)
 bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
                   const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
                   int32_t* __restrict__ work_counter, BpeDeviceTable t,
                   uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
                   int32_t* __restrict__ status) {
+    constexpr int TEAMS = BPE_BLOCK_WARPS / W;
+    constexpr int G = C / 32;
     extern __shared__ uint4 bpe_dyn[];
+    __shared__ uint32_t s_red[BPE_BLOCK_WARPS][2];            // per-warp partial minima
+    __shared__ int32_t s_word[TEAMS][2];                      // claimed word index, new length
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int team = warp / W, tw = warp % W;                 // team, warp within team
+    const int tt = tw * 32 + lane;                            // thread within team
     const uint32_t lt = (1u << lane) - 1u;
-    uint8_t* slot = reinterpret_cast<uint8_t*>(bpe_dyn) + (size_t)warp * bpe_slot_bytes(C);
+    uint8_t* slot = reinterpret_cast<uint8_t*>(bpe_dyn) + (size_t)team * bpe_slot_bytes(C);
     uint16_t* tok = reinterpret_cast<uint16_t*>(slot);          // [C] live tokens, compact
     uint16_t* rk = tok + C;                                     // [C] rank of the pair (i, i+1)
-    uint32_t* oddr = reinterpret_cast<uint32_t*>(rk + C);       // [C/32] right-walk parity bits per 32 positions
+    uint32_t* m_leq = reinterpret_cast<uint32_t*>(rk + C);      // [G] bit i: rank(i-1) <= rank(i)
+    uint32_t* m_cs = m_leq + G;                                 // [G] candidates, then selected pairs
+    uint32_t* g_aux = m_cs + G;                                 // [G] right-walk parity, then output base
     const int n_words = *list_count;
 
     for (;;) {
-        int wi = 0;
-        if (lane == 0) wi = atomicAdd(work_counter, 1);
-        wi = __shfl_sync(0xffffffffu, wi, 0);
+        if (tt == 0) s_word[team][0] = atomicAdd(work_counter, 1);
+        team_sync<W>(team);
+        const int wi = s_word[team][0];
         if (wi >= n_words) break;
         const int row = list[wi];
         const int64_t off = offsets[row];
         int n = (int)(offsets[row + 1] - off);               // 1 <= n <= C by classification
 
-        for (int i = lane; i < n; i += 32) tok[i] = __ldg(t.byte_tok + __ldg(bytes + off + i));
-        __syncwarp();
+        for (int i = tt; i < n; i += W * 32) tok[i] = __ldg(t.byte_tok + __ldg(bytes + off + i));
+        team_sync<W>(team);
 
         int round = 0;
         const int max_rounds = n + 2;
         for (; round < max_rounds; ++round) {
             const int groups = (n + 31) >> 5;
-            // ---- A: ranks of all pairs, bound B, lowest rank
+            // ---- 1: ranks of all pairs, "not worse than my left neighbour" masks, bound B, lowest rank
             uint32_t bmin = BPE_NONE, gmin = BPE_NONE;
-            for (int g = 0; g < groups; ++g) {
+            for (int g = tw; g < groups; g += W) {
                 const int i = g * 32 + lane;
                 uint32_t r = BPE_NONE;
                 if (i + 1 < n) r = bpe_rank(t, tok[i], tok[i + 1]);
+                uint32_t rp = __shfl_up_sync(0xffffffffu, r, 1);
+                if (lane == 0) rp = i > 0 ? bpe_rank(t, tok[i - 1], tok[i]) : BPE_NONE;   // i < n holds for lane 0
                 if (i < n) rk[i] = (uint16_t)r;
+                const uint32_t leq = __ballot_sync(0xffffffffu, rp <= r);
+                if (lane == 0) m_leq[g] = leq;
                 if (r != BPE_NONE) {
                     gmin = min(gmin, r);
                     bmin = min(bmin, (uint32_t)__ldg(t.future + r));
                 }
             }
             gmin = __reduce_min_sync(0xffffffffu, gmin);
-            if (gmin == BPE_NONE) break;                       // no pair can merge: done
-            uint32_t B = __reduce_min_sync(0xffffffffu, bmin);
-            if (t.single_step) B = gmin + 1;
-            __syncwarp();
-
-            // ---- B: parity of the improving walk to the right, last group first
-            bool carry = false;                                // parity bit of position 32(g+1)
-            for (int g = groups - 1; g >= 0; --g) {
-                const int i = g * 32 + lane;
-                const uint32_t r = i < n ? (uint32_t)rk[i] : BPE_NONE;
-                const uint32_t rn = i + 1 < n ? (uint32_t)rk[i + 1] : BPE_NONE;
-                const bool link = r < B && rn < r;             // the right neighbour is a candidate with better priority
-                const uint32_t c = __brev(__ballot_sync(0xffffffffu, link));
-                const uint32_t odd = __brev(run_parity(c, carry));
-                if (lane == 0) oddr[g] = odd;
-                carry = odd & 1u;
-            }
-            __syncwarp();
-
-            // ---- C: left-walk parity, selection, merge and in-place compaction, first group first
-            carry = false;                                     // left parity bit of position 32g - 1
-            uint32_t prev_sel = 0;                             // was position 32g - 1 selected (its partner is dropped)
-            int out = 0;
-            bool took_one = false;
-            for (int g = 0; g < groups; ++g) {
-                const int i = g * 32 + lane;
-                const uint32_t r = i < n ? (uint32_t)rk[i] : BPE_NONE;
-                const uint32_t rp = i > 0 && i < n ? (uint32_t)rk[i - 1] : BPE_NONE;
-                const uint32_t tk = i < n ? (uint32_t)tok[i] : 0u;
-                const bool cand = r < B;
-                const bool link = cand && rp <= r;             // rp <= r < B: the left neighbour is a candidate and goes first
-                const uint32_t candm = __ballot_sync(0xffffffffu, cand);
-                const uint32_t oddl = run_parity(__ballot_sync(0xffffffffu, link), carry);
-                carry = oddl >> 31;
-                uint32_t sel = candm & ~oddl & ~oddr[g];
-                if (t.single_step) {                           // only the leftmost pair of the lowest rank
-                    sel = took_one ? 0u : (sel & (0u - sel));
-                    took_one = took_one || sel != 0;
+            bmin = __reduce_min_sync(0xffffffffu, bmin);
+            if (W > 1) {
+                if (lane == 0) { s_red[warp][0] = gmin; s_red[warp][1] = bmin; }
+                team_sync<W>(team);
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    gmin = min(gmin, s_red[team * W + k][0]);
+                    bmin = min(bmin, s_red[team * W + k][1]);
                 }
-                const uint32_t valid = (i < n ? 1u : 0u);
-                const uint32_t validm = __ballot_sync(0xffffffffu, valid);
-                const uint32_t dropped = (sel << 1) | prev_sel;          // positions consumed as the right half of a pair
-                const uint32_t kept = validm & ~dropped;
-                uint32_t v = tk;
-                if ((sel >> lane) & 1u) v = __ldg(t.merge_out + r);
-                __syncwarp();                                  // every lane has read this group's tokens
-                if ((kept >> lane) & 1u) tok[out + __popc(kept & lt)] = (uint16_t)v;
-                out += __popc(kept);
-                prev_sel = sel >> 31;
+            } else {
+                __syncwarp();
             }
-            n = out;
-            __syncwarp();
+            if (gmin == BPE_NONE) break;                       // no pair can merge: done (uniform over the team)
+            const uint32_t B = t.single_step ? gmin + 1 : bmin;
+
+            // ---- 2: candidate masks
+            for (int g = tw; g < groups; g += W) {
+                const int i = g * 32 + lane;
+                const uint32_t r = i < n ? (uint32_t)rk[i] : BPE_NONE;
+                const uint32_t cand = __ballot_sync(0xffffffffu, r < B);
+                if (lane == 0) m_cs[g] = cand;
+            }
+            team_sync<W>(team);
+
+            // ---- 3: on the masks, one lane per 32 positions (first warp of the team)
+            if (tw == 0) {
+                const int blocks = (groups + 31) >> 5;
+                // 3a. right-walk parity, last block first
+                bool carry = false;                            // parity bit of the position after the block
+                for (int b = blocks - 1; b >= 0; --b) {
+                    const int g = b * 32 + lane;
+                    const bool live = g < groups;
+                    const uint32_t cand = live ? m_cs[g] : 0u;
+                    const uint32_t leq = live ? m_leq[g] : 0xFFFFFFFFu;
+                    const uint32_t leq_next = g + 1 < groups ? m_leq[g + 1] : 0xFFFFFFFFu;
+                    // bit i: the right neighbour ranks strictly better: not (rank(i) <= rank(i+1))
+                    const uint32_t link = cand & ~((leq >> 1) | (leq_next << 31));
+                    const uint32_t c = __brev(link);           // walk from the high positions down
+                    // carry functions compose from the highest group of the block to the lowest
+                    uint32_t f = carry_fn(c);
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const uint32_t other = __shfl_down_sync(0xffffffffu, f, d);   // groups above, applied first
+                        if (lane + d < 32) f = carry_then(other, f);
+                    }
+                    // f now maps the block's incoming carry to the carry leaving this group downwards
+                    const uint32_t above = __shfl_down_sync(0xffffffffu, f, 1);
+                    const bool cin = lane == 31 ? carry : (carry_apply(above, carry) != 0);
+                    const uint32_t odd = __brev(run_parity(c, cin));
+                    if (live) g_aux[g] = odd;
+                    carry = carry_apply(__shfl_sync(0xffffffffu, f, 0), carry) != 0;
+                }
+                __syncwarp();
+                // 3b. left-walk parity, selection, survivors, output bases, first block first
+                carry = false;                                 // left parity bit of the position before the block
+                uint32_t sel_carry = 0;                        // was the position before the block selected
+                int base = 0;
+                bool took = false;
+                for (int b = 0; b < blocks; ++b) {
+                    const int g = b * 32 + lane;
+                    const bool live = g < groups;
+                    const uint32_t cand = live ? m_cs[g] : 0u;
+                    const uint32_t leq = live ? m_leq[g] : 0u;
+                    const uint32_t link = cand & leq;          // the left neighbour is a candidate that goes first
+                    uint32_t f = carry_fn(link);
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const uint32_t other = __shfl_up_sync(0xffffffffu, f, d);     // groups below, applied first
+                        if (lane >= d) f = carry_then(other, f);
+                    }
+                    const uint32_t below = __shfl_up_sync(0xffffffffu, f, 1);
+                    const bool cin = lane == 0 ? carry : (carry_apply(below, carry) != 0);
+                    const uint32_t oddl = run_parity(link, cin);
+                    uint32_t sel = live ? (cand & ~oddl & ~g_aux[g]) : 0u;
+                    carry = carry_apply(__shfl_sync(0xffffffffu, f, 31), carry) != 0;
+                    if (t.single_step) {                       // only the leftmost pair of the lowest rank
+                        const uint32_t any = __ballot_sync(0xffffffffu, sel != 0);
+                        const int first = __ffs(any) - 1;
+                        sel = (!took && lane == first) ? (sel & (0u - sel)) : 0u;
+                        took = took || any != 0;
+                    }
+                    uint32_t prev = __shfl_up_sync(0xffffffffu, sel, 1) >> 31;
+                    if (lane == 0) prev = sel_carry;
+                    sel_carry = __shfl_sync(0xffffffffu, sel, 31) >> 31;
+                    const int cnt_pos = n - g * 32;            // positions of this group
+                    const uint32_t valid = !live ? 0u : (cnt_pos >= 32 ? 0xFFFFFFFFu : ((1u << cnt_pos) - 1u));
+                    const uint32_t kept = valid & ~((sel << 1) | prev);
+                    int x = __popc(kept), incl = x;
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int y = __shfl_up_sync(0xffffffffu, incl, d);
+                        if (lane >= d) incl += y;
+                    }
+                    if (live) { m_cs[g] = sel; g_aux[g] = (uint32_t)(base + incl - x); }
+                    base += __shfl_sync(0xffffffffu, incl, 31);
+                }
+                if (lane == 0) s_word[team][1] = base;
+            }
+            team_sync<W>(team);
+
+            // ---- 4: merge and compact in place, W groups at a time
+            const int n_new = s_word[team][1];
+            for (int g0 = 0; g0 < groups; g0 += W) {
+                const int g = g0 + tw;
+                const int i = g * 32 + lane;
+                uint32_t v = 0, kept = 0;
+                int base = 0;
+                if (g < groups) {
+                    const uint32_t sel = m_cs[g];
+                    const uint32_t prev = g > 0 ? (m_cs[g - 1] >> 31) : 0u;
+                    const int cnt_pos = n - g * 32;
+                    const uint32_t valid = cnt_pos >= 32 ? 0xFFFFFFFFu : ((1u << cnt_pos) - 1u);
+                    kept = valid & ~((sel << 1) | prev);
+                    base = (int)g_aux[g];
+                    if (i < n) v = tok[i];
+                    if ((sel >> lane) & 1u) v = __ldg(t.merge_out + rk[i]);
+                }
+                team_sync<W>(team);                            // every warp has read its tokens of this tile
+                if ((kept >> lane) & 1u) tok[base + __popc(kept & lt)] = (uint16_t)v;
+            }
+            team_sync<W>(team);
+            n = n_new;
         }
 
-        for (int i = lane; i < n; i += 32) out_tok[off + i] = tok[i];
-        if (lane == 0) {
+        for (int i = tt; i < n; i += W * 32) out_tok[off + i] = tok[i];
+        if (tt == 0) {
             counts[row] = n;
             if (round >= max_rounds && status) atomicOr(status + row, 2);
         }
-        __syncwarp();
+        team_sync<W>(team);
     }
 }
 

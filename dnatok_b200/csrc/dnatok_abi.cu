@@ -198,11 +198,9 @@ template <int CLS>
 int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
                      int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
     constexpr int C = bpe_class_capacity(CLS);
-    constexpr int slot = bpe_slot_bytes(C);
-    int warps = (100 * 1024) / slot;                 // words in flight per block
-    if (warps > BPE_WARPS) warps = BPE_WARPS;
-    if (warps < 1) warps = 1;
-    const size_t smem = (size_t)warps * slot;
+    constexpr int W = bpe_class_team(CLS);
+    constexpr int TEAMS = BPE_BLOCK_WARPS / W;                 // words in flight per block
+    const size_t smem = (size_t)TEAMS * bpe_slot_bytes(C);
     static std::mutex mu;
     static std::map<int, int> blocks_per_sm;         // device -> resident blocks (also marks the attribute as set)
     int dev = 0;
@@ -212,18 +210,18 @@ int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8
         std::lock_guard<std::mutex> lock(mu);
         auto it = blocks_per_sm.find(dev);
         if (it == blocks_per_sm.end()) {
-            CUDA_TRY(cudaFuncSetAttribute(bpe_rounds_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_rounds_kernel<C>, warps * 32, smem));
+            CUDA_TRY(cudaFuncSetAttribute(bpe_rounds_kernel<C, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_rounds_kernel<C, W>, BPE_BLOCK_WARPS * 32, smem));
             if (bps < 1) bps = 1;
             blocks_per_sm[dev] = bps;
         } else bps = it->second;
     }
-    // Resident-size grid: every warp pulls words from the class's shared counter.
+    // Resident-size grid: every team pulls words from the class's shared counter.
     int64_t grid = (int64_t)d.sm_count * bps;
-    const int64_t need = (n_rows + warps - 1) / warps;
+    const int64_t need = (n_rows + TEAMS - 1) / TEAMS;
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
-    bpe_rounds_kernel<C><<<(unsigned)grid, warps * 32, smem, st>>>(
+    bpe_rounds_kernel<C, W><<<(unsigned)grid, BPE_BLOCK_WARPS * 32, smem, st>>>(
         bytes, offsets, s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
         s.tokens, s.counts, status);
     LAUNCH_CHECK("bpe_rounds_kernel");
