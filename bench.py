@@ -337,7 +337,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
                      "kernel": {"kmer6": "kmer_warp_rows_kernel", "char": "emit_padded_kernel", "byte": "emit_padded_kernel",
-                                "bpe4k": "bpe_merge_kernel", "bpe32k": "bpe_merge_kernel"}[kind],
+                                "bpe4k": "bpe_rounds_kernel", "bpe32k": "bpe_rounds_kernel"}[kind],
                      "algorithmic_bytes_per_launch": abytes, "kernel_ms": round(kernel_ms, 5)},
         "e2e": {"value": round(world * total_bp / e2e_s / 1e6, 1), "unit": "Mbp/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),

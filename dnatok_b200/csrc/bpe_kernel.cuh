@@ -4,12 +4,11 @@
 // links, no tombstones) and is owned by a team of W warps (W = 1 for short words, up to 8 for long
 // ones).  A round:
 //   1. every adjacent pair is looked up in the merge table (perfect hash, two dependent loads); its
-//      rank is stored, a bit "rank(i-1) <= rank(i)" goes into a per-32-positions mask, and
-//      B = min over the present ranks r of F[r] is reduced, where F[r] is the lowest rank of any
-//      pair that contains the token rank r creates;
-//   2. pairs with rank < B are candidates (one ballot mask per 32 positions).  Hugging Face would
-//      take them in (rank, position) order, skipping a pair when an earlier one consumed one of its
-//      tokens.  On a path that greedy choice has a closed form: follow the strictly improving
+//      rank is stored and B = min over the present ranks r of F[r] is reduced, where F[r] is the
+//      lowest rank of any pair that contains the token rank r creates;
+//   2. pairs with rank < B are candidates: one ballot mask per 32 positions, and one more for
+//      "rank(i-1) <= rank(i)".  Hugging Face would take the candidates in (rank, position) order,
+//      skipping a pair when an earlier one consumed one of its tokens.  On a path that greedy choice has a closed form: follow the strictly improving
 //      priorities to the left and to the right of a candidate down to the local optimum; the
 //      candidate is taken iff both walks have even length;
 //   3. the two parities are prefix-XORs along runs of set bits in the masks.  They are computed on
@@ -165,17 +164,13 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
         const int max_rounds = n + 2;
         for (; round < max_rounds; ++round) {
             const int groups = (n + 31) >> 5;
-            // ---- 1: ranks of all pairs, "not worse than my left neighbour" masks, bound B, lowest rank
+            // ---- 1: ranks of all pairs, bound B, lowest rank
             uint32_t bmin = BPE_NONE, gmin = BPE_NONE;
             for (int g = tw; g < groups; g += W) {
                 const int i = g * 32 + lane;
                 uint32_t r = BPE_NONE;
                 if (i + 1 < n) r = bpe_rank(t, tok[i], tok[i + 1]);
-                uint32_t rp = __shfl_up_sync(0xffffffffu, r, 1);
-                if (lane == 0) rp = i > 0 ? bpe_rank(t, tok[i - 1], tok[i]) : BPE_NONE;   // i < n holds for lane 0
                 if (i < n) rk[i] = (uint16_t)r;
-                const uint32_t leq = __ballot_sync(0xffffffffu, rp <= r);
-                if (lane == 0) m_leq[g] = leq;
                 if (r != BPE_NONE) {
                     gmin = min(gmin, r);
                     bmin = min(bmin, (uint32_t)__ldg(t.future + r));
@@ -197,12 +192,15 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
             if (gmin == BPE_NONE) break;                       // no pair can merge: done (uniform over the team)
             const uint32_t B = t.single_step ? gmin + 1 : bmin;
 
-            // ---- 2: candidate masks
+            // ---- 2: candidate masks and "not worse than my left neighbour" masks
             for (int g = tw; g < groups; g += W) {
                 const int i = g * 32 + lane;
                 const uint32_t r = i < n ? (uint32_t)rk[i] : BPE_NONE;
+                uint32_t rp = __shfl_up_sync(0xffffffffu, r, 1);
+                if (lane == 0) rp = i > 0 ? (uint32_t)rk[i - 1] : BPE_NONE;
                 const uint32_t cand = __ballot_sync(0xffffffffu, r < B);
-                if (lane == 0) m_cs[g] = cand;
+                const uint32_t leq = __ballot_sync(0xffffffffu, rp <= r);
+                if (lane == 0) { m_cs[g] = cand; m_leq[g] = leq; }
             }
             team_sync<W>(team);
 
