@@ -58,6 +58,7 @@ struct BpeDeviceTable {
     const uint32_t* slots;       // (left << 16) | rank, 0xFFFFFFFF when empty
     const uint16_t* merge_out;   // [n_merges] token created by a rank
     const uint16_t* future;      // [n_merges] F: lowest rank of a pair containing that token
+    const uint32_t* hot;         // [32 * 32] pairs of ids < 32: rank | F << 16 (0xFFFFFFFF: no merge)
     const uint16_t* byte_tok;    // [256]
     int32_t single_step;
 };
@@ -135,6 +136,9 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
     constexpr int G = C / 32;
     extern __shared__ uint4 bpe_dyn[];
     __shared__ uint32_t s_red[BPE_BLOCK_WARPS][2];            // per-warp partial minima
+    __shared__ uint32_t s_hot[32 * 32];                       // direct table for pairs of small ids
+    for (int i = threadIdx.x; i < 32 * 32; i += BPE_BLOCK_WARPS * 32) s_hot[i] = __ldg(t.hot + i);
+    __syncthreads();
     __shared__ int32_t s_word[TEAMS][2];                      // claimed word index, new length
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int team = warp / W, tw = warp % W;                 // team, warp within team
@@ -168,13 +172,20 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
             uint32_t bmin = BPE_NONE, gmin = BPE_NONE;
             for (int g = tw; g < groups; g += W) {
                 const int i = g * 32 + lane;
-                uint32_t r = BPE_NONE;
-                if (i + 1 < n) r = bpe_rank(t, tok[i], tok[i + 1]);
-                if (i < n) rk[i] = (uint16_t)r;
-                if (r != BPE_NONE) {
-                    gmin = min(gmin, r);
-                    bmin = min(bmin, (uint32_t)__ldg(t.future + r));
+                uint32_t r = BPE_NONE, fut = BPE_NONE;
+                if (i + 1 < n) {
+                    const uint32_t a = tok[i], b = tok[i + 1];
+                    if ((a | b) < 32u) {                        // early rounds: both tokens are among the first ids
+                        const uint32_t e = s_hot[a * 32u + b];
+                        r = e & 0xFFFFu; fut = e >> 16;
+                    } else {
+                        r = bpe_rank(t, a, b);
+                        if (r != BPE_NONE) fut = __ldg(t.future + r);
+                    }
                 }
+                if (i < n) rk[i] = (uint16_t)r;
+                gmin = min(gmin, r);
+                bmin = min(bmin, fut);
             }
             gmin = __reduce_min_sync(0xffffffffu, gmin);
             bmin = __reduce_min_sync(0xffffffffu, bmin);

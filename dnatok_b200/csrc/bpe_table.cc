@@ -80,6 +80,11 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
             if (c >= 0 && (uint32_t)r < t->future[c]) t->future[c] = (uint16_t)r;
         }
     }
+    // direct table for pairs of small ids (the initial symbols and the first merges of a trained
+    // vocabulary): one shared-memory load answers rank and future rank
+    t->hot.assign(32 * 32, 0xFFFFFFFFu);
+    for (int32_t r = 0; r < n; ++r)
+        if (a[r] < 32 && b[r] < 32) t->hot[a[r] * 32 + b[r]] = (uint32_t)r | ((uint32_t)t->future[r] << 16);
     t->byte_tok.resize(256);
     for (int i = 0; i < 256; ++i) t->byte_tok[i] = (uint16_t)byte_ids[i];
     t->n_tokens = n_tokens;

@@ -19,6 +19,7 @@ struct BpeHostTable {
     std::vector<uint32_t> slots;       // [max disp + n_tokens], 0xFFFFFFFF when empty
     std::vector<uint16_t> merge_out;   // [n_merges] id created by each rank
     std::vector<uint16_t> future;      // [n_merges] lowest rank of any pair containing that id, 0xFFFF if none
+    std::vector<uint32_t> hot;         // [32 * 32] pairs of ids < 32: rank | future << 16, 0xFFFFFFFF if no merge
     std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
     uint32_t n_tokens = 0;
     uint32_t n_merges = 0;

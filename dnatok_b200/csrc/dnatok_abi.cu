@@ -58,6 +58,7 @@ struct DeviceTables {
     uint32_t* slots = nullptr;
     uint16_t* merge_out = nullptr;
     uint16_t* future = nullptr;
+    uint32_t* hot = nullptr;
     uint16_t* byte_tok = nullptr;
     int sm_count = 0;
     // host-pipeline staging (grow only)
@@ -126,6 +127,7 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
             if ((rc = upload(&d.slots, h->bpe.slots))) return rc;
             if ((rc = upload(&d.merge_out, h->bpe.merge_out))) return rc;
             if ((rc = upload(&d.future, h->bpe.future))) return rc;
+            if ((rc = upload(&d.hot, h->bpe.hot))) return rc;
             if ((rc = upload(&d.byte_tok, h->bpe.byte_tok))) return rc;
         }
         it = h->dev.emplace(dev, d).first;
@@ -240,7 +242,7 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
                                                                        s.class_list, s.counts, status);
     LAUNCH_CHECK("bpe_classify_kernel");
-    BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.future, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
+    BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.future, d.hot, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
     // Classes that cannot hold a row of this batch are skipped: the longest row is at most total_bytes.
     int rc;
 #define BPE_CLASS(CLS)                                                                                         \
@@ -327,6 +329,15 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
                 int32_t* status, cudaStream_t st) {
     if (n_rows == 0) return 0;
     const int k = h->k;
+    if (COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
+        const unsigned grid = (unsigned)((n_rows + KW_WARPS - 1) / KW_WARPS);
+#define KCASE(KK) case KK: kmer_warp_count_kernel<KK><<<grid, KW_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, total_bytes, rf, \
+                                                                                  lengths_out, status); break;
+        switch (k) { KCASE(1) KCASE(2) KCASE(3) KCASE(4) KCASE(5) KCASE(6) KCASE(7) KCASE(8) }
+#undef KCASE
+        LAUNCH_CHECK("kmer_warp_count_kernel");
+        return 0;
+    }
     if (!COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
         if (id_bits == 64) launch_kmer_warp<int64_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
                                                      lengths_out, out_offsets, status, st);
@@ -440,7 +451,7 @@ void dnatok_destroy(dnatok_handle* h) {
         DeviceTables& d = kv.second;
         if (cudaSetDevice(kv.first) != cudaSuccess) continue;
         if (d.stream) cudaStreamSynchronize(d.stream);
-        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.future, d.byte_tok, d.st_bytes, d.st_offsets,
+        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.future, d.hot, d.byte_tok, d.st_bytes, d.st_offsets,
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);

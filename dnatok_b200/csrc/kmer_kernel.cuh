@@ -209,6 +209,74 @@ template <typename IdT> struct IdPair;
 template <> struct IdPair<int64_t> { using type = longlong2; };
 template <> struct IdPair<int32_t> { using type = int2; };
 
+// Token counts only (the sizing pass for 'longest' padding and for ragged output): one warp per row,
+// same window decoding as the encoder, no stores except lengths_out.
+template <int K>
+__global__ void __launch_bounds__(KW_WARPS * 32)
+kmer_warp_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                       int64_t total_bytes, RowFormat f, int32_t* __restrict__ lengths_out,
+                       int32_t* __restrict__ status) {
+    constexpr int NW = (2 * K + 3 + 3) / 4;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int n_special = (f.cls_id >= 0 ? 1 : 0) + (f.sep_id >= 0 ? 1 : 0);
+    const int64_t off = offsets[row];
+    const int64_t len64 = offsets[row + 1] - off;
+    const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);
+    const int n_win = (len + K - 1) / K;
+    const int n_full = len / K;
+    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
+    const uint8_t* src = bytes + off;
+    const int64_t room_total = total_bytes - off;
+    const int n_chunks = (n_win + 63) >> 6;
+    int base = 0, chunk = 0;
+    for (; chunk < n_chunks && base < cap; ++chunk) {
+        const int wa = chunk * 64 + 2 * lane;
+        const int p = wa * K;
+        int cnt = 0;
+        if (wa + 2 <= n_full && (int64_t)p + 2 * K + 8 <= room_total) {
+            const uint8_t* g = src + p;
+            const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
+            uint32_t w[NW];
+#pragma unroll
+            for (int i = 0; i < NW; ++i) w[i] = __ldg(gw + i);
+            uint32_t dA = 0, dB = 0;
+#pragma unroll
+            for (int i = 0; i < NW - 1; ++i) {
+                const uint32_t r = __funnelshift_r(w[i], w[i + 1], sh);
+                uint32_t c, d;
+                acgt_codes4(r, &c, &d);
+                uint32_t mA = 0, mB = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int pos = 4 * i + b;
+                    if (pos < K) mA |= 0xFFu << (8 * b);
+                    else if (pos < 2 * K) mB |= 0xFFu << (8 * b);
+                }
+                dA |= d & mA;
+                dB |= d & mB;
+            }
+            cnt = (dA == 0 ? 1 : K) + (dB == 0 ? 1 : K);
+        } else {
+            int have = len - p;
+            have = have < 0 ? 0 : (have > 2 * K ? 2 * K : have);
+            const int lenA = have < K ? have : K, lenB = have - lenA;
+            bool okA = lenA == K, okB = lenB == K;
+            for (int i = 0; i < lenA; ++i) okA &= kmer_code(__ldg(src + p + i)) < 4;
+            for (int i = 0; i < lenB; ++i) okB &= kmer_code(__ldg(src + p + K + i)) < 4;
+            cnt = (lenA == 0 ? 0 : (okA ? 1 : lenA)) + (lenB == 0 ? 0 : (okB ? 1 : lenB));
+        }
+        base += __reduce_add_sync(0xffffffffu, cnt);
+    }
+    if (lane == 0) {
+        const int n = base < cap ? base : cap;
+        lengths_out[row] = n + n_special;
+        if (status && f.clip_is_error && (base > cap || chunk < n_chunks)) atomicOr(status + row, 4);
+    }
+}
+
 // AFFINE: the 4**K table is base + index (checked on the host), so no gather is needed.
 // FUSE_MASK: the mask has the ids' element type and is stored next to each id in the main loop.
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
