@@ -221,7 +221,37 @@ def time_device(tok, d_bytes, d_off, offsets, call, steps, warmup, barrier=None)
         barrier()
     per = np.array([a.elapsed_time(b) for a, b in ev])
     total_ms = ev[0][0].elapsed_time(ev[-1][1])
+    time_device.last_run = run
     return enc, per, total_ms, launches
+
+
+def time_graph(run, reps=20, replays=10):
+    """Kernel-only time of a launch-latency-bound shape: `reps` encodes captured in one CUDA graph,
+    replayed `replays` times; returns ms per encode, or None when capture is not possible."""
+    import torch
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                run()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (reps * replays)
+    except Exception:
+        torch.cuda.synchronize()
+        return None
 
 
 def make_ragged_runner(tok, d_bytes, d_off, offsets, kw, scratch, enc):
@@ -385,7 +415,10 @@ def per_config(local, peak, args):
             else:
                 ab = algorithmic_bytes(int(offsets[-1]), len(offsets) - 1, enc, False)
             ms = total_ms / steps
+            gms = time_graph(time_device.last_run) if label == "literal" else None
             out["%s/%s" % (kind, label)] = {
+                "graph_replay_ms_per_step": None if gms is None else round(gms, 5),
+                "graph_replay_Mbp/s": None if gms is None else round(int(offsets[-1]) / gms / 1e3, 1),
                 "workload": desc, "ms_per_step": round(ms, 5), "Mbp/s": round(int(offsets[-1]) / ms / 1e3, 1),
                 "algorithmic_GB/s": round(ab / ms / 1e6, 1), "frac_of_hbm_peak": round(ab / ms / 1e6 / peak, 4),
                 "launches_per_step": launches // steps}

@@ -27,6 +27,7 @@ thread_local std::string g_err;
 std::atomic<int64_t> g_launches{0};
 std::atomic<int64_t> g_host_chunk_bytes{256ll << 20};        // bytes (in + out) per chunk of the host pipeline
 std::atomic<int64_t> g_host_chunk_threshold{4ll << 30};      // batches below this size are not chunked
+std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -196,11 +197,10 @@ BpeScratch bpe_scratch_layout(void* base, int64_t n_rows, int64_t total_bytes) {
     return s;
 }
 
-template <int CLS>
-int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
-                     int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+template <int CLS, int W>
+int launch_bpe_team(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
+                    int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
     constexpr int C = bpe_class_capacity(CLS);
-    constexpr int W = bpe_class_team(CLS);
     constexpr int TEAMS = BPE_BLOCK_WARPS / W;                 // words in flight per block
     const size_t smem = (size_t)TEAMS * bpe_slot_bytes(C);
     static std::mutex mu;
@@ -228,6 +228,18 @@ int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8
         s.tokens, s.counts, status);
     LAUNCH_CHECK("bpe_rounds_kernel");
     return 0;
+}
+
+// A small batch cannot fill the GPU with one warp per word: give every word a whole block then, which
+// shortens each word's rounds instead.
+template <int CLS>
+int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
+                     int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+    constexpr int W = bpe_class_team(CLS);
+    const int64_t lim = g_bpe_block_team_rows.load();
+    if (W < BPE_BLOCK_WARPS && n_rows <= (lim < 0 ? (int64_t)d.sm_count * 8 : lim))
+        return launch_bpe_team<CLS, BPE_BLOCK_WARPS>(d, t, bytes, offsets, n_rows, s, status, st);
+    return launch_bpe_team<CLS, W>(d, t, bytes, offsets, n_rows, s, status, st);
 }
 
 int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
@@ -384,7 +396,9 @@ const char* dnatok_last_error(void) { return g_err.c_str(); }
 int64_t dnatok_launch_count(void) { return g_launches.load(); }
 
 int dnatok_set_option(const char* name, int64_t value) {
-    if (!name || value < 0) return fail(DNATOK_ERR_INVALID, "bad option");
+    if (!name) return fail(DNATOK_ERR_INVALID, "bad option");
+    if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
+    if (value < 0) return fail(DNATOK_ERR_INVALID, "bad option value");
     if (!strcmp(name, "host_chunk_bytes")) { g_host_chunk_bytes = value; return DNATOK_OK; }
     if (!strcmp(name, "host_chunk_threshold")) { g_host_chunk_threshold = value; return DNATOK_OK; }
     return fail(DNATOK_ERR_INVALID, "unknown option %s", name);

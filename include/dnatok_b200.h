@@ -166,7 +166,10 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes,
 /* Process-wide tuning knobs (no reference counterpart):
  *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
  *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)
- *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB) */
+ *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB)
+ *   "bpe_block_team_rows"   BPE batches of at most this many rows give every word a whole thread block
+ *                           instead of one warp (lower latency when the batch cannot fill the GPU);
+ *                           -1 (default): 8 rows per SM */
 int dnatok_set_option(const char* name, int64_t value);
 
 /* Number of kernels this library has launched from the calling process (for accounting). */

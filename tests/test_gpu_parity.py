@@ -12,6 +12,18 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
+@pytest.fixture(params=["auto", "warp_teams", "block_teams"])
+def bpe_team_mode(request):
+    """Run a BPE test under each way of assigning warps to words (small batches would otherwise only
+    ever see the block-per-word kernels)."""
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    value = {"auto": -1, "warp_teams": 0, "block_teams": 1 << 40}[request.param]
+    _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", value))
+    yield request.param
+    _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", -1))
+
+
 @pytest.fixture(scope="module")
 def toks():
     if not torch.cuda.is_available():
@@ -33,7 +45,9 @@ def run_device(tok, flat, offs, **kw):
 
 
 @pytest.mark.parametrize("cfg", H.ALL_CONFIGS)
-def test_golden_configs_device(golden, toks, cfg):
+def test_golden_configs_device(golden, toks, cfg, bpe_team_mode):
+    if bpe_team_mode != "auto" and "bpe" not in cfg:
+        pytest.skip("team mode only concerns BPE")
     g = golden["configs"][cfg]
     name, flat, offs = H.config_inputs(cfg)
     kw = H.call_to_kwargs(g["call"])
@@ -59,7 +73,7 @@ def test_golden_configs_host_entry(golden, toks, cfg):
     assert H.sha(enc["attention_mask"]) == g["mask_sha256"]
 
 
-def test_ragged_output_config5(golden, toks):
+def test_ragged_output_config5(golden, toks, bpe_team_mode):
     g = golden["configs"]["cfg5_bpe32000_512reads"]
     name, flat, offs = H.config_inputs("cfg5_bpe32000_512reads")
     enc = run_device(toks[name], flat, offs, padding=False)
@@ -124,7 +138,7 @@ def test_ragged_lengths_truncation_dtypes(toks, name, ids_dtype, mask_dtype):
 
 
 @pytest.mark.parametrize("name", ["bpe4096", "bpe32000"])
-def test_bpe_homopolymers_and_long_words(toks, name):
+def test_bpe_homopolymers_and_long_words(toks, name, bpe_team_mode):
     words = [b"A" * n for n in (1, 2, 3, 4, 5, 8, 9, 31, 32, 33, 64, 100, 255, 256, 257, 1024, 4097)]
     words += [b"AC" * 300, b"ACG" * 333, b"T" * 511 + b"A", b"N" * 70, b"ACGTNNNACGTnnacgt" * 40]
     words += [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (255, 256, 257, 511, 513, 2047, 2049, 8191, 8193, 16384, 16385, 32769, 49152)]
@@ -261,7 +275,7 @@ def test_kmer_very_long_rows_use_block_kernel(toks):
         assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
 
 
-def test_bpe_table_with_late_created_operands_single_step():
+def test_bpe_table_with_late_created_operands_single_step(bpe_team_mode):
     """A merge list whose operands are created by LATER ranks (not what BpeTrainer emits): the kernel
     must fall back to one merge per round and still equal the queue semantics of the checker."""
     from dnatok_b200.tables import Specials, TokenizerSpec
