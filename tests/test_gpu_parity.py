@@ -388,3 +388,53 @@ def test_dnatok_api_matches_reference_outputs(golden):
     lens = (want != helper.pad_id).sum(axis=1)
     for i, n in enumerate(lens):
         assert ids_left[i, ids_left.shape[1] - n:].tolist() == want[i, :n].tolist()
+
+
+def test_full_size_config4_byte_level(toks):
+    """Benchmark shape 4 at its full size (8 x 1,048,576 bp, int32 ids): byte-level ids are the bytes themselves."""
+    flat, offs = synth.pack_rows(synth.config4())
+    enc = run_device(toks["byte"], flat, offs, ids_dtype=torch.int32, return_attention_mask=False)
+    ids = enc["input_ids"]
+    assert tuple(ids.shape) == (8, 1048576) and ids.dtype == torch.int32
+    assert torch.equal(ids.reshape(-1), torch.from_numpy(flat).cuda().to(torch.int32))
+    assert int(enc["lengths"].min()) == 1048576
+
+
+def test_full_size_config5_reads(toks):
+    """Benchmark shape 5 at its full size (16,384 reads, ~38 Mbp, ragged output): equal to the CPU checker on
+    every read, and decoding the ids through the vocabulary gives back the input bytes."""
+    flat, offs = synth.config5()
+    enc = run_device(toks["bpe32000"], flat, offs, padding=False, add_special_tokens=False)
+    ids = enc["input_ids"].cpu().numpy()
+    oo = enc["offsets"].cpu().numpy()
+    want = H.oracle_rows("bpe32000", flat, offs, threads=8)
+    assert np.array_equal(np.diff(oo), np.array([len(r) for r in want]))
+    assert np.array_equal(ids, np.concatenate(want))
+    spec = H.spec("bpe32000")
+    inv = {v: k for k, v in spec.vocab.items()}
+    tok_len = np.zeros(max(inv) + 1, dtype=np.int64)
+    for i, t in inv.items():
+        tok_len[i] = len(t)
+    assert int(tok_len[ids].sum()) == int(offs[-1])            # every base is covered exactly once
+    for r in (0, 1, 4097, 16383):
+        text = "".join(inv[int(t)] for t in ids[oo[r]:oo[r + 1]])
+        assert text.encode() == bytes(flat[offs[r]:offs[r + 1]])
+
+
+def test_full_size_config3_property(toks):
+    """Shape 3 scaled 16x (16,384 words): same ids as the checker on a sample, and the padded tensor is
+    consistent with its lengths (mask sum, [CLS] first, [SEP] last, pad after)."""
+    flat, offs = synth.pack_rows(synth.config3(batch=16384, seed=31))
+    enc = run_device(toks["bpe4096"], flat, offs, padding="longest")
+    ids, mask, lens = enc["input_ids"], enc["attention_mask"], enc["lengths"].long()
+    assert torch.equal(mask.sum(dim=1), lens)
+    assert bool((ids[:, 0] == 2).all()) and bool((ids.gather(1, (lens - 1).unsqueeze(1)) == 3).all())
+    assert bool(((ids == 0) == (mask == 0)).all())
+    sample = np.arange(0, 16384, 257)
+    from dnatok_b200.shard import take_rows
+    f2, o2 = take_rows(flat, offs, sample)
+    want = H.oracle_rows("bpe4096", f2, o2)
+    got = ids.cpu().numpy()
+    for j, r in enumerate(sample):
+        n = int(lens[r]) - 2
+        assert got[r, 1:1 + n].tolist() == want[j].tolist()
