@@ -51,44 +51,49 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
     const int64_t stride = f.out_stride;
     const bool small = n_spans <= 0x7fffffff;
 
-    for (int64_t span = (int64_t)blockIdx.x * EMIT_WARPS + warp; span < n_spans; span += (int64_t)gridDim.x * EMIT_WARPS) {
-        int64_t row;
-        int64_t cs;
+    constexpr int R = (CHUNKS + 31) / 32;                     // window chunks per lane
+
+    struct Span {
+        int64_t row, cs, n, T, shift, t_lo;
+        const uint8_t* wbase;
+        int ncol, a;
+        bool any_content;
+    };
+    auto describe = [&](int64_t span) {
+        Span p;
         if (small) {
             const uint32_t r32 = (uint32_t)span / (uint32_t)spans_per_row;
-            row = r32;
-            cs = (int64_t)((uint32_t)span - r32 * (uint32_t)spans_per_row) * EMIT_SPAN;
+            p.row = r32;
+            p.cs = (int64_t)((uint32_t)span - r32 * (uint32_t)spans_per_row) * EMIT_SPAN;
         } else {
-            row = span / spans_per_row;
-            cs = (span - row * spans_per_row) * EMIT_SPAN;
+            p.row = span / spans_per_row;
+            p.cs = (span - p.row * spans_per_row) * EMIT_SPAN;
         }
-        const int64_t off = offsets[row];
-        const int64_t n_in = counts ? (int64_t)counts[row] : offsets[row + 1] - off;
-        const int64_t n = n_in < f.cap_content ? n_in : f.cap_content;
-        const int64_t T = n + (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
-        const int64_t shift = f.pad_left ? stride - T : 0;
-        const int64_t first = shift + (has_cls ? 1 : 0);      // column of content element 0
-        if (cs == 0 && lane == 0) {
-            if (lengths_out) lengths_out[row] = (int32_t)T;
-            if (status && f.clip_is_error && n_in > n) atomicOr(status + row, 4);
+        const int64_t off = offsets[p.row];
+        const int64_t n_in = counts ? (int64_t)counts[p.row] : offsets[p.row + 1] - off;
+        p.n = n_in < f.cap_content ? n_in : f.cap_content;
+        p.T = p.n + (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
+        p.shift = f.pad_left ? stride - p.T : 0;
+        if (p.cs == 0 && lane == 0) {
+            if (lengths_out) lengths_out[p.row] = (int32_t)p.T;
+            if (status && f.clip_is_error && n_in > p.n) atomicOr(status + p.row, 4);
         }
-        const int ncol = (int)(stride - cs < EMIT_SPAN ? stride - cs : EMIT_SPAN);   // columns of this span
-        IdT* orow = ids + row * stride + cs;
-        const bool aligned = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
-
-        // ---- stage the source window: element (cs - first + j) for j in [0, 512)
-        const int64_t t_lo = cs - first;
-        const uint8_t* wptr = reinterpret_cast<const uint8_t*>(src + off) + t_lo * SZ;
-        const int a = (int)(reinterpret_cast<uintptr_t>(wptr) & 15);
-        const uint8_t* wbase = wptr - a;
-        // only chunks that can hold content of this row are fetched
-        const int64_t t_hi = t_lo + ncol;                     // one past the last element wanted
-        const bool any_content = t_hi > 0 && t_lo < n;
-        __syncwarp();
-        if (any_content) {
-            for (int k = lane; k < CHUNKS; k += 32) {
-                const uint8_t* g = wbase + 16 * k;
-                uint4 v = make_uint4(0, 0, 0, 0);
+        p.ncol = (int)(stride - p.cs < EMIT_SPAN ? stride - p.cs : EMIT_SPAN);
+        p.t_lo = p.cs - (p.shift + (has_cls ? 1 : 0));        // content index under the span's first column
+        const uint8_t* wptr = reinterpret_cast<const uint8_t*>(src + off) + p.t_lo * SZ;
+        p.a = (int)(reinterpret_cast<uintptr_t>(wptr) & 15);
+        p.wbase = wptr - p.a;
+        p.any_content = p.t_lo + p.ncol > 0 && p.t_lo < p.n;  // else the span is specials and padding only
+        return p;
+    };
+    // the span's source window as aligned 16-byte chunks, into registers
+    auto fetch = [&](const Span& p, uint4* regs) {
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int k = lane + 32 * q;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (p.any_content && k < CHUNKS) {
+                const uint8_t* g = p.wbase + 16 * k;
                 if (g >= src_begin && g + 16 <= src_end) v = __ldg(reinterpret_cast<const uint4*>(g));
                 else {
                     uint8_t tmp[16];
@@ -96,10 +101,33 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
                     for (int b = 0; b < 16; ++b) tmp[b] = (g + b >= src_begin && g + b < src_end) ? __ldg(g + b) : (uint8_t)0;
                     v = *reinterpret_cast<uint4*>(tmp);
                 }
-                s_win[warp][k] = v;
             }
+            regs[q] = v;
         }
+    };
+
+    const int64_t span_step = (int64_t)gridDim.x * EMIT_WARPS;
+    int64_t span = (int64_t)blockIdx.x * EMIT_WARPS + warp;
+    if (span >= n_spans) return;
+    Span cur = describe(span);
+    uint4 pre[R];
+    fetch(cur, pre);
+    for (;;) {
+        // the window of this span goes to shared memory; the next span's window is requested right away
         __syncwarp();
+#pragma unroll
+        for (int q = 0; q < R; ++q) if (lane + 32 * q < CHUNKS) s_win[warp][lane + 32 * q] = pre[q];
+        __syncwarp();
+        const int64_t next = span + span_step;
+        const bool more = next < n_spans;
+        Span nxt = cur;
+        if (more) { nxt = describe(next); fetch(nxt, pre); }
+
+        const int64_t row = cur.row, cs = cur.cs, n = cur.n, T = cur.T, shift = cur.shift, t_lo = cur.t_lo;
+        const int ncol = cur.ncol, a = cur.a;
+        const bool any_content = cur.any_content;
+        IdT* orow = ids + row * stride + cs;
+        const bool aligned = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
 
         // ---- ids
         for (int v = lane; v * N < ncol; v += 32) {
@@ -146,6 +174,9 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
             else if (f.mask_bits == 32) warp_mask_row<int32_t>((int32_t*)mask + row * stride + cs, ncol, lo, hi, lane);
             else warp_mask_row<uint8_t>((uint8_t*)mask + row * stride + cs, ncol, lo, hi, lane);
         }
+        if (!more) break;
+        span = next;
+        cur = nxt;
     }
 }
 
