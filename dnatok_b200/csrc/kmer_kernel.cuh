@@ -280,7 +280,7 @@ kmer_warp_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restr
 // AFFINE: the 4**K table is base + index (checked on the host), so no gather is needed.
 // FUSE_MASK: the mask has the ids' element type and is stored next to each id in the main loop.
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
-__global__ void __launch_bounds__(KW_WARPS * 32)
+__global__ void __launch_bounds__(KW_WARPS * 32, 6)
 kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
                       int64_t total_bytes, const int32_t* __restrict__ kmer_ids, int32_t affine_base,
                       const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,

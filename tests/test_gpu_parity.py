@@ -438,3 +438,42 @@ def test_full_size_config3_property(toks):
     for j, r in enumerate(sample):
         n = int(lens[r]) - 2
         assert got[r, 1:1 + n].tolist() == want[j].tolist()
+
+
+@pytest.mark.parametrize("name", H.TOKENIZERS)
+def test_seeded_fuzz_against_live_hf(toks, name):
+    """Random batches over a dirty alphabet, random lengths and call options, against the live Hugging Face
+    tokenizer (not the checker): ids, mask, padding side."""
+    import zlib
+    rng = np.random.default_rng(zlib.crc32(name.encode()) % 1000 + 17)
+    alphabet = np.frombuffer(b"ACGTACGTACGTACGTNNacgtnRYKM-_0xX", np.uint8)
+    hf, mine = H.hf(name), toks[name]
+    for trial in range(25):
+        B = int(rng.integers(1, 24))
+        lens = rng.integers(0, 260, size=B)
+        if trial % 5 == 0:
+            lens[rng.integers(0, B)] = int(rng.integers(1000, 5000))
+        strs = [bytes(alphabet[rng.integers(0, len(alphabet), int(n))]).decode() for n in lens]
+        if trial % 7 == 3:
+            strs[0] = "A" * int(rng.integers(1, 700))
+        special = bool(rng.integers(0, 2))
+        mode = int(rng.integers(0, 3))
+        if mode == 0:
+            kw = dict(padding=True)
+        elif mode == 1:
+            kw = dict(padding="max_length", max_length=int(rng.integers(2, 300)), truncation=True)
+        else:
+            kw = dict(padding=True, max_length=int(rng.integers(2, 120)), truncation=True)
+        for side in ("right", "left"):
+            hf.padding_side = side
+            mine.padding_side = side
+            try:
+                want = hf(strs, add_special_tokens=special, return_tensors="np", **kw)
+                got = mine(strs, add_special_tokens=special, return_tensors="pt", **kw)
+            finally:
+                hf.padding_side = "right"
+                mine.padding_side = "right"
+            assert np.array_equal(got["input_ids"].cpu().numpy(), want["input_ids"]), (name, trial, side, kw, special)
+            assert np.array_equal(got["attention_mask"].cpu().numpy(), want["attention_mask"]), (name, trial, side, kw)
+        rows = hf(strs, add_special_tokens=special)["input_ids"]
+        assert mine(strs, add_special_tokens=special)["input_ids"] == [list(r) for r in rows]
