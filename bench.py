@@ -358,7 +358,7 @@ def run_ours(args):
     line = {
         "metric": "Mbp/s encoded (bit-exact vs HF)", "value": round(value, 1), "unit": "Mbp/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8->int64",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
         "data": "synthetic (seeded; stands in for genomic reads and the NT-v2 tokenizer)",
         "config": {"workload": desc, "rows_per_gpu": len(offsets) - 1, "bp_per_gpu": total_bp,
                    "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" % (abytes / 1e6)
@@ -518,7 +518,7 @@ def run_reference(args):
         "impl": "reference", "metric": "Mbp/s encoded (bit-exact vs HF)", "value": round(value, 2), "unit": "Mbp/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8->int64", "data": "synthetic (seeded)",
+        "dtype": "u8", "data": "synthetic (seeded)",
         "config": {"workload": desc, "note": "CPU arm runs a bounded sample of the GPU arm's workload per step"},
         "cpu_baseline": cpu,
         "e2e": {"value": round(value, 2), "unit": "Mbp/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -1,11 +1,11 @@
-"""Generate the committed golden vectors.  Run where ``/root/reference`` and Hugging Face
-``tokenizers`` are available:
+"""Generate the committed golden vectors.  Needs a checkout of eniktab/DNAtok and Hugging Face
+``tokenizers``:
 
-    python tests/golden/make_golden.py
+    DNATOK_REFERENCE_SRC=<checkout>/src python tests/golden/make_golden.py
 
 Writes ``tests/golden/golden.json`` (hashes + small literal cases) from three sources:
   * live Hugging Face tokenizers built by ``oracle/hf_oracle.py`` - the parity target;
-  * the reference's own CPU paths imported from ``/root/reference/src``: ``DNATok`` (numpy LUT and
+  * the reference's own CPU paths imported from that checkout: ``DNATok`` (numpy LUT and
     k-mer paths) wrapped around those tokenizers, and ``dnatok_compat.Evo2ByteTokenizer``;
   * the reference's normaliser known answers (``tests/test_gputok_bpe_backend.py:319-425``),
     re-derived by calling its ``_compile_normalizer_step``.
@@ -27,7 +27,7 @@ import torch  # noqa: E402
 from dnatok_b200 import synth  # noqa: E402
 from oracle import hf_oracle  # noqa: E402
 
-REF_SRC = "/root/reference/src"
+REF_SRC = os.environ.get("DNATOK_REFERENCE_SRC", "")
 
 
 def sha(a) -> str:
@@ -60,6 +60,8 @@ class _Embedder(torch.nn.Module):
 
 
 def main():
+    if not os.path.isdir(REF_SRC):
+        raise SystemExit("set DNATOK_REFERENCE_SRC to the src/ directory of an eniktab/DNAtok checkout")
     sys.path.insert(0, REF_SRC)
     from dna_tokenizer import DNATok                      # reference, CPU numpy paths
     import gputok_bpe_backend as ref_backend              # reference normaliser compiler
