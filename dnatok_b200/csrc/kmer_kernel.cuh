@@ -312,30 +312,33 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
     const bool pair_aligned = (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(IdT))) == 0;
 
     int base = 0;              // content tokens placed so far (uncapped)
-    const int n_chunks = (n_win + 63) >> 6;
+    int w = 0;                 // next window of the row
     const int n_full = len / K;                          // complete windows
     bool clipped = false;
 
-    // Windows of one chunk for this lane: lengths, table indices, cleanliness.
+    // The two windows of this lane in the chunk of `nwin` windows starting at window w0:
+    // lengths, table indices, cleanliness.
     struct Two { int lenA, lenB; uint32_t idxA, idxB; bool cleanA, cleanB; int p; };
-    auto decode = [&](int chunk) {
+    auto decode = [&](int w0, int nwin) {
         Two t;
-        const int wa = chunk * 64 + 2 * lane;
+        const int wa = w0 + 2 * lane;
+        int lim = w0 + nwin;                              // one past the chunk's last window
+        if (lim > n_win) lim = n_win;
         t.p = wa * K;
         t.idxA = 0; t.idxB = 0;
-        // both windows complete and the aligned words inside the buffer: the wide route
-        if (wa + 2 <= n_full && (int64_t)t.p + 2 * K + 8 <= room_total) {
+        // both windows complete, inside the chunk, and the aligned words inside the buffer: the wide route
+        if (wa + 2 <= lim && wa + 2 <= n_full && (int64_t)t.p + 2 * K + 8 <= room_total) {
             t.lenA = K; t.lenB = K;
             const uint8_t* g = src + t.p;
             const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;
             const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
-            uint32_t w[NW];
+            uint32_t wd[NW];
 #pragma unroll
-            for (int i = 0; i < NW; ++i) w[i] = __ldg(gw + i);
+            for (int i = 0; i < NW; ++i) wd[i] = __ldg(gw + i);
             uint32_t P = 0, dA = 0, dB = 0;
 #pragma unroll
             for (int i = 0; i < NW - 1; ++i) {
-                const uint32_t r = __funnelshift_r(w[i], w[i + 1], sh);     // bytes 4i .. 4i+3 of the pair
+                const uint32_t r = __funnelshift_r(wd[i], wd[i + 1], sh);     // bytes 4i .. 4i+3 of the pair
                 uint32_t c, d;
                 acgt_codes4(r, &c, &d);
                 P |= pack_codes4(c) << (24 - 8 * i);
@@ -355,11 +358,10 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
             t.idxA = (P >> (32 - 2 * K)) & IDX_MASK;
             t.idxB = (P >> (32 - 4 * K)) & IDX_MASK;
         } else {
-            // edge of the row or of the buffer: byte loads
-            int have = len - t.p;
-            have = have < 0 ? 0 : (have > 2 * K ? 2 * K : have);
-            t.lenA = have < K ? have : K;
-            t.lenB = have - t.lenA;
+            // edge of the chunk, of the row or of the buffer: byte loads
+            t.lenA = 0; t.lenB = 0;
+            if (wa < lim) { const int h = len - t.p; t.lenA = h < K ? h : K; }
+            if (wa + 1 < lim) { const int h = len - t.p - K; t.lenB = h < K ? h : K; }
             bool okA = t.lenA == K, okB = t.lenB == K;
             for (int i = 0; i < t.lenA; ++i) { const int c = kmer_code(__ldg(src + t.p + i)); okA &= c < 4; t.idxA = (t.idxA << 2) | (uint32_t)(c & 3); }
             for (int i = 0; i < t.lenB; ++i) { const int c = kmer_code(__ldg(src + t.p + K + i)); okB &= c < 4; t.idxB = (t.idxB << 2) | (uint32_t)(c & 3); }
@@ -367,14 +369,14 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
         }
         return t;
     };
-    auto emit = [&](int chunk, const Two& t) {
+    auto emit = [&](int w0, int nwin, const Two& t) {
         const bool simple = (t.lenA == 0 || t.cleanA) && (t.lenB == 0 || t.cleanB);
         if (__all_sync(0xffffffffu, simple)) {
             // every window of the chunk is one token: this lane's tokens sit at base + 2*lane (+1)
             const int pos = base + 2 * lane;
             const IdT a = t.lenA ? (IdT)(AFFINE ? affine_base + (int32_t)t.idxA : __ldg(kmer_ids + t.idxA)) : (IdT)0;
             const IdT b = t.lenB ? (IdT)(AFFINE ? affine_base + (int32_t)t.idxB : __ldg(kmer_ids + t.idxB)) : (IdT)0;
-            if (t.lenB && pos + 1 < cap && pair_aligned && ((pos & 1) == 0)) {
+            if (t.lenB && pos + 1 < cap && (reinterpret_cast<uintptr_t>(dst + pos) % (2 * sizeof(IdT))) == 0) {
                 Pair v; v.x = a; v.y = b;
                 *reinterpret_cast<Pair*>(dst + pos) = v;
                 if (FUSE_MASK) { Pair one; one.x = 1; one.y = 1; *reinterpret_cast<Pair*>(mdst + pos) = one; }
@@ -382,8 +384,8 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                 if (t.lenA && pos < cap) { dst[pos] = a; if (FUSE_MASK) mdst[pos] = 1; }
                 if (t.lenB && pos + 1 < cap) { dst[pos + 1] = b; if (FUSE_MASK) mdst[pos + 1] = 1; }
             }
-            const int left = n_win - chunk * 64;
-            base += left < 64 ? left : 64;
+            const int left = n_win - w0;
+            base += left < nwin ? left : nwin;
         } else {
             const int cntA = t.lenA == 0 ? 0 : (t.cleanA ? 1 : t.lenA);
             const int cntB = t.lenB == 0 ? 0 : (t.cleanB ? 1 : t.lenB);
@@ -410,13 +412,13 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
     // Wide-route decode of the two windows at g (no bounds checks): table indices and a word that is
     // non-zero when either window holds anything but ACGT.
     auto decode_tight = [&](const uint32_t* gw, uint32_t sh, uint32_t* idxA, uint32_t* idxB) -> uint32_t {
-        uint32_t w[NW];
+        uint32_t wd[NW];
 #pragma unroll
-        for (int i = 0; i < NW; ++i) w[i] = __ldg(gw + i);
+        for (int i = 0; i < NW; ++i) wd[i] = __ldg(gw + i);
         uint32_t P = 0, bad = 0;
 #pragma unroll
         for (int i = 0; i < NW - 1; ++i) {
-            const uint32_t r = __funnelshift_r(w[i], w[i + 1], sh);
+            const uint32_t r = __funnelshift_r(wd[i], wd[i + 1], sh);
             uint32_t c, d;
             acgt_codes4(r, &c, &d);
             P |= pack_codes4(c) << (24 - 8 * i);
@@ -429,53 +431,50 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
         *idxB = (P >> (32 - 4 * K)) & IDX_MASK;
         return bad;
     };
-    // chunks in which every lane owns two complete windows and the aligned words stay in the buffer
-    int n_tight = n_full >> 6;
+    // windows [0, n_tight) are complete and their aligned words stay in the buffer
+    int n_tight = n_full;
     {
-        const int64_t fit = (room_total - 8) / (64 * K);
+        const int64_t fit = (room_total - 8) / K;
         if (fit < n_tight) n_tight = fit < 0 ? 0 : (int)fit;
     }
-    const uint8_t* g0 = src + 2 * lane * K;
-    const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g0) & 3u) * 8u;     // the same for every chunk: 64K % 4 == 0
     const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
     Pair one; one.x = 1; one.y = 1;
 
-    int chunk = 0;
-    while (chunk < n_chunks && base < cap) {
-        // tight stretch: clean full chunks, no per-token checks
-        {
-            const uint32_t* gw = reinterpret_cast<const uint32_t*>(g0 - (sh >> 3)) + (size_t)chunk * (16 * K);
+    while (w < n_win && base < cap) {
+        // 16-byte stores need an even element offset; after an odd number of tokens (a chunk with
+        // single-base fallbacks) one chunk of 63 windows puts the row back in step
+        const bool al = (reinterpret_cast<uintptr_t>(dst + base) % (2 * sizeof(IdT))) == 0;
+        if (al) {
+            // tight stretch: clean full chunks, two per trip, no per-token checks
+            const uint8_t* g = src + (w + 2 * lane) * K;
+            const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;   // constant while w moves by 64: 64K % 4 == 0
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
             IdT* d = dst + base + 2 * lane;
-            const bool al = pair_aligned && ((base & 1) == 0);
-            while (chunk + 1 < n_tight && base + 128 <= cap) {
+            while (w + 128 <= n_tight && base + 128 <= cap) {
                 uint32_t a0, b0, a1, b1;
                 const uint32_t bad0 = decode_tight(gw, sh, &a0, &b0);
                 const uint32_t bad1 = decode_tight(gw + 16 * K, sh, &a1, &b1);
                 if (__any_sync(0xffffffffu, (bad0 | bad1) != 0)) break;
-                const IdT x0 = (IdT)(AFFINE ? affine_base + (int32_t)a0 : __ldg(kmer_ids + a0));
-                const IdT y0 = (IdT)(AFFINE ? affine_base + (int32_t)b0 : __ldg(kmer_ids + b0));
-                const IdT x1 = (IdT)(AFFINE ? affine_base + (int32_t)a1 : __ldg(kmer_ids + a1));
-                const IdT y1 = (IdT)(AFFINE ? affine_base + (int32_t)b1 : __ldg(kmer_ids + b1));
-                if (al) {
-                    Pair v0, v1; v0.x = x0; v0.y = y0; v1.x = x1; v1.y = y1;
-                    *reinterpret_cast<Pair*>(d) = v0;
-                    *reinterpret_cast<Pair*>(d + 64) = v1;
-                    if (FUSE_MASK) { *reinterpret_cast<Pair*>(d + mdelta) = one; *reinterpret_cast<Pair*>(d + mdelta + 64) = one; }
-                } else {
-                    d[0] = x0; d[1] = y0; d[64] = x1; d[65] = y1;
-                    if (FUSE_MASK) { d[mdelta] = 1; d[mdelta + 1] = 1; d[mdelta + 64] = 1; d[mdelta + 65] = 1; }
-                }
-                gw += 32 * K; d += 128; base += 128; chunk += 2;
+                Pair v0, v1;
+                v0.x = (IdT)(AFFINE ? affine_base + (int32_t)a0 : __ldg(kmer_ids + a0));
+                v0.y = (IdT)(AFFINE ? affine_base + (int32_t)b0 : __ldg(kmer_ids + b0));
+                v1.x = (IdT)(AFFINE ? affine_base + (int32_t)a1 : __ldg(kmer_ids + a1));
+                v1.y = (IdT)(AFFINE ? affine_base + (int32_t)b1 : __ldg(kmer_ids + b1));
+                *reinterpret_cast<Pair*>(d) = v0;
+                *reinterpret_cast<Pair*>(d + 64) = v1;
+                if (FUSE_MASK) { *reinterpret_cast<Pair*>(d + mdelta) = one; *reinterpret_cast<Pair*>(d + mdelta + 64) = one; }
+                gw += 32 * K; d += 128; base += 128; w += 128;
             }
+            if (w >= n_win) break;
+            if (base >= cap) break;
         }
-        if (chunk >= n_chunks) break;
-        if (base >= cap) { clipped = true; break; }
         // one chunk by the general route (dirty windows, row edges, the last tokens before the cap)
-        const Two t0 = decode(chunk);
-        emit(chunk, t0);
-        ++chunk;
+        const int nwin = al ? 64 : 63;
+        const Two t0 = decode(w, nwin);
+        emit(w, nwin, t0);
+        w += nwin;
     }
-    if (chunk < n_chunks) clipped = true;
+    if (w < n_win) clipped = true;
     if (base > cap) clipped = true;
 
     const int n = base < cap ? base : cap;
