@@ -309,7 +309,6 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
     if (!ragged && f.pad_left) shift = (int)f.out_stride - lengths_in[row];
     IdT* dst = orow + shift + (has_cls ? 1 : 0);
     IdT* mdst = FUSE_MASK ? reinterpret_cast<IdT*>(mask) + (dst - ids) : nullptr;
-    const bool pair_aligned = (reinterpret_cast<uintptr_t>(dst) % (2 * sizeof(IdT))) == 0;
 
     int base = 0;              // content tokens placed so far (uncapped)
     int w = 0;                 // next window of the row
