@@ -453,10 +453,18 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                 uint32_t a0, b0, a1, b1;
                 const uint32_t bad0 = decode_tight(gw, sh, &a0, &b0);
                 const uint32_t bad1 = decode_tight(gw + 16 * K, sh, &a1, &b1);
-                if (__any_sync(0xffffffffu, (bad0 | bad1) != 0)) break;
                 Pair v0, v1;
                 v0.x = (IdT)(AFFINE ? affine_base + (int32_t)a0 : __ldg(kmer_ids + a0));
                 v0.y = (IdT)(AFFINE ? affine_base + (int32_t)b0 : __ldg(kmer_ids + b0));
+                if (__any_sync(0xffffffffu, (bad0 | bad1) != 0)) {
+                    // the general route takes over; a clean first chunk is still placed from here
+                    if (!__any_sync(0xffffffffu, bad0 != 0)) {
+                        *reinterpret_cast<Pair*>(d) = v0;
+                        if (FUSE_MASK) *reinterpret_cast<Pair*>(d + mdelta) = one;
+                        base += 64; w += 64;
+                    }
+                    break;
+                }
                 v1.x = (IdT)(AFFINE ? affine_base + (int32_t)a1 : __ldg(kmer_ids + a1));
                 v1.y = (IdT)(AFFINE ? affine_base + (int32_t)b1 : __ldg(kmer_ids + b1));
                 *reinterpret_cast<Pair*>(d) = v0;
