@@ -381,6 +381,24 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(kind, 1)
         if not args.no_extra:
             line["per_config"] = per_config(local, peak, args)
+    if world > 1 and args.gather and "input_ids" in enc and enc["input_ids"].dim() == 2:
+        # optional step, not part of the metric: bring every rank's padded ids to rank 0 over NCCL
+        import torch.distributed as dist
+        from dnatok_b200 import shard
+        ids = enc["input_ids"]
+        rows = [int(ids.shape[0])] * world
+        shard.gather_padded(ids, rows, int(ids.shape[1]), tok.pad_token_id)          # warm-up
+        torch.cuda.synchronize(); dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        got = shard.gather_padded(ids, rows, int(ids.shape[1]), tok.pad_token_id)
+        b.record(); torch.cuda.synchronize()
+        gt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(gt, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            ok = bool(torch.equal(got[:ids.shape[0]], ids))
+            line["gather"] = {"ms": round(float(gt[0]), 3), "bytes_to_rank0": int(ids.numel() * ids.element_size() * (world - 1)),
+                              "rank0_rows_ok": ok, "backend": "nccl"}
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -554,6 +572,8 @@ def main():
     ap.add_argument("--workload", default="kmer6", choices=["kmer6", "char", "byte", "bpe4k", "bpe32k"])
     ap.add_argument("--scale", type=int, default=0, help="batch multiplier over the literal shape (0: default)")
     ap.add_argument("--no-extra", action="store_true", help="skip the per_config section")
+    ap.add_argument("--gather", action="store_true",
+                    help="multi-GPU: also time the optional NCCL gather of the padded ids to rank 0 (outside the timed region)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no e2e, no CPU baseline): the form used under ncu")
     args = ap.parse_args()
