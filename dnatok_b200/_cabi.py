@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "csrc", "libdnatok_b200.so")
 
 OK = 0
-ROW_TOO_LONG, ROW_NOT_CONVERGED, ROW_CLIPPED = 1, 2, 4
+ROW_TOO_LONG, ROW_NOT_CONVERGED, ROW_CLIPPED, ROW_OUTSIDE_HINT = 1, 2, 4, 8
 KIND_CHAR, KIND_KMER, KIND_BPE = 0, 1, 2
 BPE_MAX_WORD = 49152
 
@@ -22,7 +22,7 @@ EXPORTS = (
     "dnatok_create_bpe", "dnatok_destroy", "dnatok_kind", "dnatok_scratch_bytes",
     "dnatok_max_tokens", "dnatok_prepare", "dnatok_write", "dnatok_encode",
     "dnatok_scan_lengths", "dnatok_encode_host", "dnatok_launch_count",
-    "dnatok_encode_bpe_builtin_scratch", "dnatok_set_option",
+    "dnatok_encode_bpe_builtin_scratch", "dnatok_set_option", "dnatok_set_row_bytes_hint",
 )
 BUILTIN_SCRATCH_BYTES = 8 << 20
 
@@ -73,6 +73,7 @@ def lib() -> ctypes.CDLL:
     L.dnatok_encode.argtypes = [p, p, p, c_int64, c_int64, POINTER(Format), p, p, p, p, p, p, c_size_t, p]
     L.dnatok_encode_bpe_builtin_scratch.argtypes = [p, p, p, c_int64, c_int64, POINTER(Format), p, p, p, p, p, p]
     L.dnatok_set_option.argtypes = [c_char_p, c_int64]
+    L.dnatok_set_row_bytes_hint.argtypes = [p, c_int64, c_int64]
     L.dnatok_scan_lengths.argtypes = [p, c_int64, p, p]
     L.dnatok_encode_host.argtypes = [p, c_int, p, p, c_int64, POINTER(Format), p, c_int64, p, p, p, p,
                                      POINTER(c_int64)]

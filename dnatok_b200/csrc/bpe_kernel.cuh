@@ -89,10 +89,12 @@ __device__ __forceinline__ uint32_t carry_then(uint32_t a, uint32_t b) {
 }
 
 // Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].  One atomic per
-// warp and class (rows of a batch mostly share a class).
+// warp and class (rows of a batch mostly share a class).  Classes outside class_mask are not
+// launched by the host; a row that belongs to one is flagged instead of being dropped silently.
 __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t n_rows,
                                     int32_t* __restrict__ class_count, int32_t* __restrict__ class_list,
-                                    int32_t* __restrict__ counts, int32_t* __restrict__ status) {
+                                    int32_t* __restrict__ counts, int32_t* __restrict__ status,
+                                    uint32_t class_mask) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int lane = threadIdx.x & 31;
     int c = -1;
@@ -103,6 +105,7 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
             c = 0;
             while (c < BPE_N_CLASSES && (int64_t)bpe_class_capacity(c) < n) ++c;
             if (c >= BPE_N_CLASSES) { if (status) atomicOr(status + i, 1); c = -1; }
+            else if (!((class_mask >> c) & 1u)) { if (status) atomicOr(status + i, 8); c = -1; }   // outside the caller's length hint
         }
     }
     for (int k = 0; k < BPE_N_CLASSES; ++k) {

@@ -95,6 +95,7 @@ struct dnatok_handle {
     std::vector<int32_t> kmer_ids;
     int32_t kmer_affine_base = -1;     // >= 0 when kmer_ids[i] == base + i for every i
     bool lut_identity = false;         // char: id == byte value for every byte (byte-level tokenizers)
+    int64_t hint_min_row = 0, hint_max_row = 0;   // caller's bounds on row length in bytes; 0, 0: unknown
     BpeHostTable bpe;
     std::mutex mu;
     std::map<int, DeviceTables> dev;
@@ -251,15 +252,24 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     if (s.bytes > scratch_bytes) return fail(DNATOK_ERR_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, s.bytes);
     if (n_rows == 0) return 0;
     CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 128, st));   // class_count and work are adjacent
+    // classes that can hold a row of this batch: bounded by the total size and by the caller's hint
+    uint32_t class_mask = 0;
+    {
+        int64_t lo = 1, hi = total_bytes;
+        if (h->hint_max_row > 0) { lo = h->hint_min_row > 1 ? h->hint_min_row : 1; if (h->hint_max_row < hi) hi = h->hint_max_row; }
+        for (int c = 0; c < BPE_N_CLASSES; ++c) {
+            const int64_t c_lo = c == 0 ? 1 : bpe_class_capacity(c - 1) + 1, c_hi = bpe_class_capacity(c);
+            if (c_hi >= lo && c_lo <= hi) class_mask |= 1u << c;
+        }
+    }
     bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
-                                                                       s.class_list, s.counts, status);
+                                                                       s.class_list, s.counts, status, class_mask);
     LAUNCH_CHECK("bpe_classify_kernel");
     BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.future, d.hot, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
-    // Classes that cannot hold a row of this batch are skipped: the longest row is at most total_bytes.
+    // Classes outside the mask are not launched; a row that falls into one is flagged by the classifier.
     int rc;
 #define BPE_CLASS(CLS)                                                                                         \
-    if ((CLS == 0 || total_bytes > bpe_class_capacity(CLS == 0 ? 0 : CLS - 1)) &&                                \
-        (rc = launch_bpe_class<CLS>(d, t, bytes, offsets, n_rows, s, status, st)))                               \
+    if (((class_mask >> CLS) & 1u) && (rc = launch_bpe_class<CLS>(d, t, bytes, offsets, n_rows, s, status, st))) \
         return rc;
     // longest class first: its few, slow words start while nothing else competes for the SMs
     BPE_CLASS(8) BPE_CLASS(7) BPE_CLASS(6) BPE_CLASS(5) BPE_CLASS(4) BPE_CLASS(3) BPE_CLASS(2) BPE_CLASS(1) BPE_CLASS(0)
@@ -480,6 +490,14 @@ void dnatok_destroy(dnatok_handle* h) {
 }
 
 int dnatok_kind(const dnatok_handle* h) { return h ? h->kind : DNATOK_ERR_INVALID; }
+
+int dnatok_set_row_bytes_hint(dnatok_handle* h, int64_t min_bytes, int64_t max_bytes) {
+    if (!h || min_bytes < 0 || max_bytes < 0 || (max_bytes > 0 && min_bytes > max_bytes))
+        return fail(DNATOK_ERR_INVALID, "bad row length hint");
+    h->hint_min_row = min_bytes;
+    h->hint_max_row = max_bytes;
+    return DNATOK_OK;
+}
 
 size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes) {
     if (!h || h->kind != DNATOK_KIND_BPE || n_rows < 0 || total_bytes < 0) return 0;
@@ -731,6 +749,19 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
     if (h_offsets[0] != 0) return fail(DNATOK_ERR_INVALID, "offsets must start at 0");
     if (int rc = check_batch(h, h_bytes, h_offsets, n_rows, total)) return rc;
     CUDA_TRY(cudaSetDevice(device));
+    struct HintGuard {          // row lengths are known here: bound the BPE classes for this call only
+        dnatok_handle* h; int64_t lo, hi;
+        ~HintGuard() { h->hint_min_row = lo; h->hint_max_row = hi; }
+    } guard{h, h->hint_min_row, h->hint_max_row};
+    if (n_rows > 0) {
+        int64_t lo = INT64_MAX, hi = 0;
+        for (int64_t i = 0; i < n_rows; ++i) {
+            const int64_t n = h_offsets[i + 1] - h_offsets[i];
+            if (n < lo) lo = n;
+            if (n > hi) hi = n;
+        }
+        h->hint_min_row = lo; h->hint_max_row = hi > 0 ? hi : 1;
+    }
     DeviceTables* d;
     if (int rc = tables_for_current_device(h, &d)) return rc;
     if (!d->stream) CUDA_TRY(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));

@@ -143,6 +143,13 @@ class B200Tokenizer:
             raise ValueError("padding='max_length' needs max_length")
         ns = self._n_special(add_special_tokens)
         out = out or {}
+        if self.spec.kind == "bpe":
+            # row lengths known on the host bound the length classes the BPE path has to launch
+            if host_offsets is not None and B:
+                lens = np.diff(host_offsets)
+                _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, int(lens.min()), max(int(lens.max()), 1)))
+            else:
+                _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, 0, 0))
         with torch.cuda.device(dev):
             stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
             need = L.dnatok_scratch_bytes(self.handle.ptr, B, total)
@@ -220,6 +227,9 @@ class B200Tokenizer:
             raise RuntimeError("%d row(s) exceed the BPE kernel's word limit of %d bytes (first: row %d)"
                                % (int(np.count_nonzero(st & _cabi.ROW_TOO_LONG)), _cabi.BPE_MAX_WORD,
                                   int(np.flatnonzero(st & _cabi.ROW_TOO_LONG)[0])))
+        if np.any(st & _cabi.ROW_OUTSIDE_HINT):
+            raise RuntimeError("row %d is outside the row-length bounds given to dnatok_set_row_bytes_hint"
+                               % int(np.flatnonzero(st & _cabi.ROW_OUTSIDE_HINT)[0]))
         if np.any(st & _cabi.ROW_NOT_CONVERGED):
             raise RuntimeError("BPE merge loop hit its pass limit on row %d" %
                                int(np.flatnonzero(st & _cabi.ROW_NOT_CONVERGED)[0]))

@@ -49,6 +49,7 @@ extern "C" {
 #define DNATOK_ROW_TOO_LONG       1   /* BPE word longer than the kernel's shared-memory slot; row left empty */
 #define DNATOK_ROW_NOT_CONVERGED  2   /* BPE pass limit reached (cannot happen for a consistent table) */
 #define DNATOK_ROW_CLIPPED        4   /* row had more tokens than out_stride and was cut to fit */
+#define DNATOK_ROW_OUTSIDE_HINT   8   /* BPE row length outside dnatok_set_row_bytes_hint; row left empty */
 
 #define DNATOK_KIND_CHAR 0
 #define DNATOK_KIND_KMER 1
@@ -88,6 +89,13 @@ int dnatok_create_bpe(const int32_t* merge_a, const int32_t* merge_b, const int3
                       dnatok_handle** out);
 void dnatok_destroy(dnatok_handle* h);
 int dnatok_kind(const dnatok_handle* h);
+
+/* Optional bounds on the row lengths (bytes) of the batches that follow on this handle; 0, 0 clears
+ * them.  The BPE path launches one kernel per length class and, without bounds, has to launch every
+ * class the batch size allows; with bounds only the classes in range are launched.  A row outside
+ * the bounds gets DNATOK_ROW_OUTSIDE_HINT and no tokens.  dnatok_encode_host derives the bounds from
+ * its host offsets by itself.  No reference counterpart (its kernel is one launch, one block per row). */
+int dnatok_set_row_bytes_hint(dnatok_handle* h, int64_t min_bytes, int64_t max_bytes);
 
 /* Bytes of caller-owned device scratch dnatok_prepare / dnatok_encode need for this batch
  * (0 for char).  The scratch must be 256-byte aligned. */

@@ -477,3 +477,36 @@ def test_seeded_fuzz_against_live_hf(toks, name):
             assert np.array_equal(got["attention_mask"].cpu().numpy(), want["attention_mask"]), (name, trial, side, kw)
         rows = hf(strs, add_special_tokens=special)["input_ids"]
         assert mine(strs, add_special_tokens=special)["input_ids"] == [list(r) for r in rows]
+
+
+def test_row_length_hint_flags_rows_outside_it():
+    """A wrong dnatok_set_row_bytes_hint must not lose rows silently: they get a status bit."""
+    import ctypes
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    handle = _cabi.Handle(H.spec("bpe4096"))
+    flat, offs = H.pack_strs(["ACGT" * 10, "ACGTTGCA" * 100, "AC"])
+    d_b, d_o = dev(flat, offs)
+    B, total = 3, len(flat)
+    need = L.dnatok_scratch_bytes(handle.ptr, B, total)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    ids = torch.zeros((B, 64), dtype=torch.int64, device="cuda")
+    lengths = torch.zeros(B, dtype=torch.int32, device="cuda")
+    status = torch.zeros(B, dtype=torch.int32, device="cuda")
+    fmt = _cabi.Format(64, 0, 1, 0, 64, 64)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    _cabi.check(L.dnatok_set_row_bytes_hint(handle.ptr, 1, 256))
+    _cabi.check(L.dnatok_encode(handle.ptr, p(d_b), p(d_o), B, total, ctypes.byref(fmt), p(ids), None, p(lengths), None,
+                                p(status), p(scratch), need, None))
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, _cabi.ROW_OUTSIDE_HINT, 0]
+    assert lengths.tolist()[1] == 2                      # only the special tokens
+    _cabi.check(L.dnatok_set_row_bytes_hint(handle.ptr, 0, 0))
+    _cabi.check(L.dnatok_encode(handle.ptr, p(d_b), p(d_o), B, total, ctypes.byref(fmt), p(ids), None, p(lengths), None,
+                                p(status), p(scratch), need, None))
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0]
+    want, _ = H.oracle_batch("bpe4096", flat, offs, padding="max_length", max_length=64, truncation=True)
+    assert np.array_equal(ids.cpu().numpy(), want)
+    assert L.dnatok_set_row_bytes_hint(handle.ptr, 5, 2) == -1
+    handle.close()
