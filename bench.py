@@ -408,7 +408,7 @@ def run_ours(args):
 
 # dram bytes per launch of the dominant kernel from the committed ncu summaries (profiles/), scaled to
 # the default workload where the capture ran on a smaller case; None until a capture exists.
-TRAFFIC = {"kmer6": 665.7e6, "char": 1090.9e6}
+TRAFFIC = {"kmer6": 667.5e6, "char": 1085.3e6}
 
 
 def per_config(local, peak, args):
