@@ -510,3 +510,25 @@ def test_row_length_hint_flags_rows_outside_it():
     assert np.array_equal(ids.cpu().numpy(), want)
     assert L.dnatok_set_row_bytes_hint(handle.ptr, 5, 2) == -1
     handle.close()
+
+
+def test_cli_validate_info_encode(capsys):
+    """The command line front end: validate exits 0 only when every window matches Hugging Face."""
+    import json
+    import os
+    from dnatok_b200 import cli
+    fixture = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bpe4096.tokenizer.json.gz")
+    for spec, path in (("char", "ascii_lut"), ("kmer6", "kmer_lut"), ("byte", "ascii_lut"), (fixture, "gpu_bpe")):
+        assert cli.main(["validate", "--tokenizer", spec, "--n", "40", "--window", "515", "--json"]) == 0
+        out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert out["n_match"] == 40 and out["n_mismatch"] == 0 and out["selected_path"] == path
+    assert cli.main(["info", "--tokenizer", "kmer6", "--json"]) == 0
+    info = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert info["kmer_k"] == 6 and info["vocab_size"] == 4106 and info["id_pad"] == 0
+    assert cli.main(["encode", "--tokenizer", "char", "--seq", "ACGTN", "--json"]) == 0
+    enc = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert enc["token_ids"] == [5, 6, 7, 8, 9] and enc["n_tokens"] == 5
+    assert cli.main(["bench", "--tokenizer", "char", "--n", "64", "--window", "256", "--json"]) == 0
+    b = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert b["total_bp"] == 64 * 256 and b["dnatok_mbp_per_s"] > 0
+    assert cli.main(["info", "--tokenizer", "/nonexistent/dir"]) == 2
