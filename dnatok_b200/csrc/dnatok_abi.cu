@@ -622,6 +622,57 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
                               nullptr, d_status, st);
 }
 
+// ------------------------------------------------------------------ host packing
+
+// FASTA text -> packed sequence bytes + row offsets.  Header lines start with '>' (or ';'), sequence
+// lines are concatenated without their line ends (LF or CRLF); blank lines are skipped.  Call with
+// out_bytes == NULL to size: *n_records and *n_bytes are always set.  Returns DNATOK_ERR_CAPACITY when
+// a given buffer is too small.  Text before the first header counts as one unnamed record.
+int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int64_t bytes_capacity,
+                      int64_t* out_offsets, int64_t offsets_capacity, int64_t* n_records, int64_t* n_bytes) {
+    if ((!text && n_text) || n_text < 0 || !n_records || !n_bytes) return fail(DNATOK_ERR_INVALID, "bad argument");
+    int64_t rec = 0, nb = 0;
+    bool open_record = false;
+    const bool write = out_bytes != nullptr && out_offsets != nullptr;
+    int64_t i = 0;
+    while (i < n_text) {
+        const char* nl = (const char*)memchr(text + i, '\n', (size_t)(n_text - i));
+        int64_t end = nl ? (nl - text) : n_text;          // line is [i, end)
+        int64_t stop = end;
+        while (stop > i && (text[stop - 1] == '\r' || text[stop - 1] == ' ' || text[stop - 1] == '\t')) --stop;
+        if (stop > i) {
+            if (text[i] == '>' || text[i] == ';') {
+                if (write) {
+                    if (rec >= offsets_capacity - 1) return fail(DNATOK_ERR_CAPACITY, "offsets buffer too small");
+                    out_offsets[rec] = nb;
+                }
+                ++rec;
+                open_record = true;
+            } else {
+                if (!open_record) {                           // sequence before any header
+                    if (write) {
+                        if (rec >= offsets_capacity - 1) return fail(DNATOK_ERR_CAPACITY, "offsets buffer too small");
+                        out_offsets[rec] = nb;
+                    }
+                    ++rec;
+                    open_record = true;
+                }
+                const int64_t len = stop - i;
+                if (write) {
+                    if (nb + len > bytes_capacity) return fail(DNATOK_ERR_CAPACITY, "bytes buffer too small");
+                    memcpy(out_bytes + nb, text + i, (size_t)len);
+                }
+                nb += len;
+            }
+        }
+        i = end + 1;
+    }
+    if (write) out_offsets[rec] = nb;
+    *n_records = rec;
+    *n_bytes = nb;
+    return DNATOK_OK;
+}
+
 // ------------------------------------------------------------------ BPE without caller scratch
 //
 // The merge kernels need working memory beyond their inputs and outputs (merged tokens, per-row

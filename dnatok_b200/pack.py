@@ -50,3 +50,19 @@ def pack_any(x) -> Packed:
         b, n = x.shape
         return np.ascontiguousarray(x).reshape(-1), np.arange(b + 1, dtype=np.int64) * n
     return pack_strings(x)
+
+
+def pack_fasta(text: Union[bytes, bytearray, memoryview]) -> Packed:
+    """FASTA text -> (flat uint8 bytes, int64 offsets), one row per record, through the native packer."""
+    import ctypes
+    from . import _cabi
+    L = _cabi.lib()
+    buf = np.frombuffer(bytes(text), dtype=np.uint8)
+    n_rec, n_bytes = ctypes.c_int64(0), ctypes.c_int64(0)
+    ptr = _cabi.np_ptr(buf) if buf.size else None
+    _cabi.check(L.dnatok_pack_fasta(ptr, buf.size, None, 0, None, 0, ctypes.byref(n_rec), ctypes.byref(n_bytes)))
+    flat = np.empty(n_bytes.value, dtype=np.uint8)
+    offsets = np.zeros(n_rec.value + 1, dtype=np.int64)
+    _cabi.check(L.dnatok_pack_fasta(ptr, buf.size, _cabi.np_ptr(flat), flat.size, _cabi.np_ptr(offsets), offsets.size,
+                                    ctypes.byref(n_rec), ctypes.byref(n_bytes)))
+    return flat, offsets

@@ -171,6 +171,15 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes,
                        void* h_ids, int64_t ids_capacity, void* h_mask, int32_t* h_lengths,
                        int64_t* h_out_offsets, int32_t* h_status, int64_t* out_stride_used);
 
+/* Host packing of FASTA text into the (bytes, offsets) layout the encode entry points take: header
+ * lines ('>' or ';') start a record, sequence lines are joined without their line ends.  Call once
+ * with out_bytes == NULL to get *n_records and *n_bytes, then with buffers of n_bytes bytes and
+ * n_records + 1 offsets.  Stands in for the reference's per-string packing loops
+ * (src/dna_tokenizer.py:2594-2651, src/dnatok_bpe_kernel/dnatok_bpe.cu:872-887), which start from
+ * Python strings. */
+int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int64_t bytes_capacity,
+                      int64_t* out_offsets, int64_t offsets_capacity, int64_t* n_records, int64_t* n_bytes);
+
 /* Process-wide tuning knobs (no reference counterpart):
  *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
  *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)

@@ -90,3 +90,47 @@ def test_bad_arguments_return_codes_not_crashes():
     assert L.dnatok_create_char(_cabi.np_ptr(lut), ctypes.byref(bad), ctypes.byref(h)) == -1
     assert L.dnatok_kind(None) == -1
     L.dnatok_destroy(None)
+
+
+def test_pack_fasta_native_packer():
+    """Records, multi-line sequences, CRLF, blank lines, sequence before the first header."""
+    from dnatok_b200.pack import pack_fasta
+
+    def ref(text):
+        rows, cur = [], None
+        for line in text.decode().split("\n"):
+            line = line.rstrip("\r \t")
+            if not line:
+                continue
+            if line[0] in ">;":
+                cur = []
+                rows.append(cur)
+            else:
+                if cur is None:
+                    cur = []
+                    rows.append(cur)
+                cur.append(line)
+        return ["".join(r) for r in rows]
+
+    cases = [b">a\nACGT\nACG\n>b desc\nTT\n", b"ACGT\nAC\n>x\nGG", b">only header\n", b"", b"\n\n>r1\r\nAC\r\nGT\r\n\r\n>r2\r\nNN",
+             b">a\n>b\nA\n;c\nCC\n  \n"]
+    rng = np.random.default_rng(0)
+    big = []
+    for i in range(300):
+        n = int(rng.integers(0, 400))
+        seq = bytes(np.frombuffer(b"ACGTN", np.uint8)[rng.integers(0, 5, n)])
+        big.append(b">read%d\n" % i + b"\n".join(seq[j:j + 60] for j in range(0, n, 60)) + b"\n")
+    cases.append(b"".join(big))
+    for text in cases:
+        flat, offs = pack_fasta(text)
+        want = ref(text)
+        assert len(offs) == len(want) + 1 and offs[0] == 0
+        got = [bytes(flat[offs[i]:offs[i + 1]]).decode() for i in range(len(want))]
+        assert got == want
+    L = _cabi.lib()
+    n1, n2 = ctypes.c_int64(), ctypes.c_int64()
+    small = np.zeros(2, np.uint8)
+    offs = np.zeros(8, np.int64)
+    text = np.frombuffer(b">a\nACGT\n", np.uint8)
+    assert L.dnatok_pack_fasta(_cabi.np_ptr(text), text.size, _cabi.np_ptr(small), 2, _cabi.np_ptr(offs), 8,
+                               ctypes.byref(n1), ctypes.byref(n2)) == -5
