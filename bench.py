@@ -442,7 +442,36 @@ def per_config(local, peak, args):
                 "launches_per_step": launches // steps}
             del d_bytes, d_off, enc
             torch.cuda.empty_cache()
+    out["embed_char/scaled"] = embed_line(local, peak)
     return out
+
+
+def embed_line(local, peak):
+    """Fused tokenise -> embedding gather (char shape, 4,096 x 1,024 bp, 256-wide bf16 rows): ids never stored."""
+    import torch
+    from dnatok_b200.tokenizer import B200Tokenizer
+    tok = B200Tokenizer(spec_for("char"), device=local)
+    flat, offsets, call, desc = make_workload("char", 64)
+    d_bytes, d_off = torch.from_numpy(flat).cuda(), torch.from_numpy(offsets).cuda()
+    weight = torch.randn((10, 256), device="cuda").to(torch.bfloat16).contiguous()
+    first = tok.embed_device(d_bytes, d_off, weight, host_offsets=offsets, padding="longest")
+    buf = first["embeddings"]
+    stride = int(buf.shape[1])
+    run = lambda: tok.embed_device(d_bytes, d_off, weight, host_offsets=offsets, padding="max_length", max_length=stride, out=buf)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    steps = 10
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in ev:
+        a.record(); run(); b.record()
+    torch.cuda.synchronize()
+    ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+    ab = int(offsets[-1]) + buf.numel() * buf.element_size()
+    return {"workload": "char tokenise + gather of 256-wide bf16 rows, %d x 1024 bp" % (len(offsets) - 1),
+            "ms_per_step": round(ms, 5), "Mbp/s": round(int(offsets[-1]) / ms / 1e3, 1),
+            "algorithmic_GB/s": round(ab / ms / 1e6, 1), "frac_of_hbm_peak": round(ab / ms / 1e6 / peak, 4),
+            "launches_per_step": 1}
 
 
 # ----------------------------------------------------------------------------- CPU arm

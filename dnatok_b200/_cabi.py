@@ -23,7 +23,7 @@ EXPORTS = (
     "dnatok_max_tokens", "dnatok_prepare", "dnatok_write", "dnatok_encode",
     "dnatok_scan_lengths", "dnatok_encode_host", "dnatok_launch_count",
     "dnatok_encode_bpe_builtin_scratch", "dnatok_set_option", "dnatok_set_row_bytes_hint",
-    "dnatok_pack_fasta",
+    "dnatok_pack_fasta", "dnatok_embed",
 )
 BUILTIN_SCRATCH_BYTES = 8 << 20
 
@@ -74,6 +74,7 @@ def lib() -> ctypes.CDLL:
     L.dnatok_encode.argtypes = [p, p, p, c_int64, c_int64, POINTER(Format), p, p, p, p, p, p, c_size_t, p]
     L.dnatok_encode_bpe_builtin_scratch.argtypes = [p, p, p, c_int64, c_int64, POINTER(Format), p, p, p, p, p, p]
     L.dnatok_pack_fasta.argtypes = [p, c_int64, p, c_int64, p, c_int64, POINTER(c_int64), POINTER(c_int64)]
+    L.dnatok_embed.argtypes = [p, p, p, c_int64, c_int64, POINTER(Format), p, c_int64, c_int64, p, p, p, p]
     L.dnatok_set_option.argtypes = [c_char_p, c_int64]
     L.dnatok_set_row_bytes_hint.argtypes = [p, c_int64, c_int64]
     L.dnatok_scan_lengths.argtypes = [p, c_int64, p, p]

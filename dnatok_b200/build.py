@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(CSRC, "libdnatok_b200.so")
 SOURCES = ["dnatok_abi.cu", "bpe_table.cc"]
-DEPS = SOURCES + ["common.cuh", "emit_kernel.cuh", "kmer_kernel.cuh", "bpe_kernel.cuh", "bpe_table.h",
+DEPS = SOURCES + ["common.cuh", "emit_kernel.cuh", "embed_kernel.cuh", "kmer_kernel.cuh", "bpe_kernel.cuh", "bpe_table.h",
                   os.path.join("..", "..", "include", "dnatok_b200.h")]
 
 

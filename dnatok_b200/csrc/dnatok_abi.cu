@@ -16,6 +16,7 @@
 
 #include "bpe_kernel.cuh"
 #include "bpe_table.h"
+#include "embed_kernel.cuh"
 #include "emit_kernel.cuh"
 #include "kmer_kernel.cuh"
 
@@ -620,6 +621,42 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     }
     return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
                               nullptr, d_status, st);
+}
+
+// ------------------------------------------------------------------ fused embedding gather
+
+int dnatok_embed(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets, int64_t n_rows,
+                 int64_t total_bytes, const dnatok_format* fmt, const void* d_weight, int64_t vocab_rows,
+                 int64_t row_bytes, void* d_out, int32_t* d_lengths, int32_t* d_status, dnatok_stream stream) {
+    if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
+    if (int rc = check_format(fmt, false)) return rc;
+    if (h->kind != DNATOK_KIND_CHAR) return fail(DNATOK_ERR_UNSUPPORTED, "dnatok_embed needs a one-token-per-byte handle");
+    if (fmt->out_stride <= 0) return fail(DNATOK_ERR_INVALID, "dnatok_embed needs a padded layout (out_stride > 0)");
+    if (!d_weight || !d_out) return fail(DNATOK_ERR_INVALID, "NULL weight or output");
+    if (row_bytes <= 0 || row_bytes % 16 || vocab_rows <= 0) return fail(DNATOK_ERR_INVALID, "row_bytes must be a positive multiple of 16");
+    if ((reinterpret_cast<uintptr_t>(d_weight) | reinterpret_cast<uintptr_t>(d_out)) & 15)
+        return fail(DNATOK_ERR_INVALID, "weight and output must be 16-byte aligned");
+    if (h->sp.pad_id >= vocab_rows) return fail(DNATOK_ERR_INVALID, "pad id outside the weight matrix");
+    cudaStream_t st = (cudaStream_t)stream;
+    DeviceTables* d;
+    if (int rc = tables_for_current_device(h, &d)) return rc;
+    RowFormat rf;
+    if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
+    if (n_rows == 0) return DNATOK_OK;
+    if (d_status) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
+    const int pieces = (int)(row_bytes / 16);
+    int lanes = 1;
+    while (lanes < 32 && lanes * 2 <= pieces) lanes *= 2;
+    const int64_t tokens = n_rows * fmt->out_stride;
+    const int groups = EMBED_THREADS / lanes;
+    int64_t blocks = (tokens + groups - 1) / groups;
+    const int64_t cap = (int64_t)d->sm_count * 32;
+    if (blocks > cap) blocks = cap;
+    embed_padded_kernel<<<(unsigned)blocks, EMBED_THREADS, 0, st>>>(d_bytes, d_offsets, n_rows, d->lut256, rf,
+                                                                    (const uint4*)d_weight, vocab_rows, pieces, lanes,
+                                                                    (uint4*)d_out, d_lengths, d_status);
+    LAUNCH_CHECK("embed_padded_kernel");
+    return DNATOK_OK;
 }
 
 // ------------------------------------------------------------------ host packing

@@ -218,6 +218,50 @@ class B200Tokenizer:
                 self._raise_on_status(status[:B], truncation)
         return res
 
+    def embed_device(self, d_bytes, d_offsets, weight, *, host_offsets: Optional[np.ndarray] = None,
+                     padding: Union[bool, str] = "longest", max_length: Optional[int] = None,
+                     truncation: bool = False, add_special_tokens: bool = True, out=None):
+        """Fused tokenise -> embedding lookup for char / byte-level tokenizers: returns
+        ``weight[input_ids]`` as a ``[B, T, D]`` CUDA tensor (and ``lengths``) without materialising the
+        ids.  ``weight`` is a contiguous ``[vocab, D]`` CUDA tensor whose rows are a multiple of 16 bytes."""
+        torch = _torch()
+        L = _cabi.lib()
+        if self.spec.kind != "char":
+            raise RuntimeError("embed_device needs a one-token-per-character tokenizer")
+        B = d_offsets.shape[0] - 1
+        ns = self._n_special(add_special_tokens)
+        max_tokens = int(max_length) if (truncation and max_length) else 0
+        if padding in (True, "longest"):
+            if host_offsets is None:
+                host_offsets = d_offsets.cpu().numpy()
+            lens = np.diff(host_offsets)
+            if max_tokens:
+                lens = np.minimum(lens, max_tokens - ns)
+            stride = int(lens.max()) + ns if B else 0
+        elif padding == "max_length" and max_length:
+            stride = int(max_length)
+        else:
+            raise ValueError("embed_device needs padding='longest' or 'max_length'")
+        if not weight.is_contiguous() or weight.dim() != 2:
+            raise ValueError("weight must be a contiguous [vocab, D] tensor")
+        row_bytes = weight.shape[1] * weight.element_size()
+        dev = d_bytes.device
+        if out is None or tuple(out.shape) != (B, stride, weight.shape[1]) or out.dtype != weight.dtype:
+            out = torch.empty((B, stride, weight.shape[1]), dtype=weight.dtype, device=dev)
+        lengths = torch.empty(max(B, 1), dtype=torch.int32, device=dev)
+        status = torch.empty(max(B, 1), dtype=torch.int32, device=dev)
+        fmt = self._format(id_bits=64, mask_bits=0, add_special=add_special_tokens, max_tokens=max_tokens,
+                           out_stride=stride)
+        if B and stride:
+            with torch.cuda.device(dev):
+                stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+                _cabi.check(L.dnatok_embed(self.handle.ptr, ctypes.c_void_p(d_bytes.data_ptr()),
+                                           ctypes.c_void_p(d_offsets.data_ptr()), B, int(d_bytes.shape[0]),
+                                           ctypes.byref(fmt), ctypes.c_void_p(weight.data_ptr()), int(weight.shape[0]),
+                                           int(row_bytes), ctypes.c_void_p(out.data_ptr()),
+                                           ctypes.c_void_p(lengths.data_ptr()), ctypes.c_void_p(status.data_ptr()), stream))
+        return BatchEncoding(embeddings=out, lengths=lengths[:B])
+
     def _raise_on_status(self, status, truncation: bool) -> None:
         bits = int(status.max().item()) if status.numel() else 0
         if not bits:

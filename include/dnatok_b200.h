@@ -171,6 +171,16 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes,
                        void* h_ids, int64_t ids_capacity, void* h_mask, int32_t* h_lengths,
                        int64_t* h_out_offsets, int32_t* h_status, int64_t* out_stride_used);
 
+/* Fused tokenise -> embedding gather for char / byte-level handles: d_out[row, col, :] =
+ * d_weight[id(row, col), :] for the padded layout fmt describes (out_stride > 0; id_bits / mask_bits are
+ * not used), without writing the ids.  d_weight is [vocab_rows, row_bytes] bytes per row (any element
+ * type; row_bytes a multiple of 16), d_out is [n_rows, out_stride, row_bytes]; both 16-byte aligned.
+ * Padding columns read the pad row.  Stands in for the reference's opt-in Triton kernel
+ * _fused_tokenize_gather, src/dna_tokenizer.py:3465-3532. */
+int dnatok_embed(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets, int64_t n_rows,
+                 int64_t total_bytes, const dnatok_format* fmt, const void* d_weight, int64_t vocab_rows,
+                 int64_t row_bytes, void* d_out, int32_t* d_lengths, int32_t* d_status, dnatok_stream stream);
+
 /* Host packing of FASTA text into the (bytes, offsets) layout the encode entry points take: header
  * lines ('>' or ';') start a record, sequence lines are joined without their line ends.  Call once
  * with out_bytes == NULL to get *n_records and *n_bytes, then with buffers of n_bytes bytes and

@@ -532,3 +532,33 @@ def test_cli_validate_info_encode(capsys):
     b = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert b["total_bp"] == 64 * 256 and b["dnatok_mbp_per_s"] > 0
     assert cli.main(["info", "--tokenizer", "/nonexistent/dir"]) == 2
+
+
+@pytest.mark.parametrize("name", ["char", "byte"])
+@pytest.mark.parametrize("dim,dtype", [(128, "float16"), (1024, "bfloat16"), (20, "float32"), (8, "float16")])
+def test_fused_embedding_gather(toks, name, dim, dtype):
+    """dnatok_embed: out == weight[input_ids] bit for bit (rows are copied), ids never materialised."""
+    tok = toks[name]
+    rng = np.random.default_rng(dim)
+    B = 37
+    lens = rng.integers(0, 600, size=B)
+    a = synth.config4(batch=B, length=600, seed=3) if name == "byte" else synth.config1(batch=B, length=600, seed=3)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat = np.concatenate([a[i, :lens[i]] for i in range(B)])
+    d_b, d_o = dev(flat, offs)
+    vocab = tok.vocab_size if name == "char" else 512
+    weight = torch.randn((vocab, dim), device="cuda").to(getattr(torch, dtype)).contiguous()
+    for kw in (dict(padding="longest"), dict(padding="max_length", max_length=77, truncation=True)):
+        for side in ("right", "left"):
+            tok.padding_side = side
+            try:
+                got = tok.embed_device(d_b, d_o, weight, host_offsets=offs, **kw)
+                ref = tok.encode_device(d_b, d_o, host_offsets=offs, **kw)
+            finally:
+                tok.padding_side = "right"
+            torch.cuda.synchronize()
+            o_ids, _ = H.oracle_batch(name, flat, offs, pad_left=(side == "left"), **kw)
+            assert np.array_equal(ref["input_ids"].cpu().numpy(), o_ids)
+            want = weight[torch.from_numpy(o_ids).cuda()]
+            assert torch.equal(got["embeddings"], want)
+            assert torch.equal(got["lengths"], ref["lengths"])
