@@ -647,9 +647,8 @@ int dnatok_embed(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
     const int pieces = (int)(row_bytes / 16);
     int lanes = 1;
     while (lanes < 32 && lanes * 2 <= pieces) lanes *= 2;
-    const int64_t tokens = n_rows * fmt->out_stride;
-    const int groups = EMBED_THREADS / lanes;
-    int64_t blocks = (tokens + groups - 1) / groups;
+    const int64_t spans = n_rows * ((fmt->out_stride + 31) / 32);
+    int64_t blocks = (spans + EMBED_THREADS / 32 - 1) / (EMBED_THREADS / 32);
     const int64_t cap = (int64_t)d->sm_count * 32;
     if (blocks > cap) blocks = cap;
     embed_padded_kernel<<<(unsigned)blocks, EMBED_THREADS, 0, st>>>(d_bytes, d_offsets, n_rows, d->lut256, rf,
