@@ -20,7 +20,6 @@ __device__ __forceinline__ int kmer_code(uint32_t c) {       // A C G T -> 0..3,
 struct KmerSmem {
     int32_t single[256];
     int32_t warp_sum[KMER_THREADS / 32];
-    int32_t tile_total;
 };
 
 // Exclusive block scan of one int per thread; returns the thread's offset, total in *total.
