@@ -150,7 +150,7 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
     uint8_t* slot = reinterpret_cast<uint8_t*>(bpe_dyn) + (size_t)team * bpe_slot_bytes(C);
     uint16_t* tok = reinterpret_cast<uint16_t*>(slot);          // [C] live tokens, compact
     uint16_t* rk = tok + C;                                     // [C] rank of the pair (i, i+1)
-    uint32_t* m_leq = reinterpret_cast<uint32_t*>(rk + C);      // [G] bit i: rank(i-1) <= rank(i)
+    uint32_t* m_leq = reinterpret_cast<uint32_t*>(rk + C);      // [G] bit i: rank(i-1) <= rank(i); after step 3: survivors
     uint32_t* m_cs = m_leq + G;                                 // [G] candidates, then selected pairs
     uint32_t* g_aux = m_cs + G;                                 // [G] right-walk parity, then output base
     const int n_words = *list_count;
@@ -287,7 +287,7 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
                         const int y = __shfl_up_sync(0xffffffffu, incl, d);
                         if (lane >= d) incl += y;
                     }
-                    if (live) { m_cs[g] = sel; g_aux[g] = (uint32_t)(base + incl - x); }
+                    if (live) { m_cs[g] = sel; m_leq[g] = kept; g_aux[g] = (uint32_t)(base + incl - x); }   // m_leq is free now: survivors
                     base += __shfl_sync(0xffffffffu, incl, 31);
                 }
                 if (lane == 0) s_word[team][1] = base;
@@ -303,10 +303,7 @@ bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
                 int base = 0;
                 if (g < groups) {
                     const uint32_t sel = m_cs[g];
-                    const uint32_t prev = g > 0 ? (m_cs[g - 1] >> 31) : 0u;
-                    const int cnt_pos = n - g * 32;
-                    const uint32_t valid = cnt_pos >= 32 ? 0xFFFFFFFFu : ((1u << cnt_pos) - 1u);
-                    kept = valid & ~((sel << 1) | prev);
+                    kept = m_leq[g];                           // survivors of this group, from step 3
                     base = (int)g_aux[g];
                     if (i < n) v = tok[i];
                     if ((sel >> lane) & 1u) v = __ldg(t.merge_out + rk[i]);
