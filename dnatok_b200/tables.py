@@ -233,14 +233,30 @@ def bpe_spec_from_json(cfg: Dict[str, Any], *, pad_id: Optional[int] = None,
 
 # --------------------------------------------------------------------------- probing (char / k-mer)
 
+def _flat_ids(x) -> List[int]:
+    if hasattr(x, "tolist"):
+        x = x.tolist()
+    while isinstance(x, list) and len(x) == 1 and isinstance(x[0], list):
+        x = x[0]
+    return [int(v) for v in x]
+
+
 def _ids(tok: Any, texts: List[str]) -> List[List[int]]:
-    enc = tok(texts, add_special_tokens=False)
-    return [list(map(int, r)) for r in enc["input_ids"]]
+    """ids of each text without special tokens; tokenizers that cannot take a ragged batch (the
+    reference's dict-based ``CharTokenizer``, ``src/dnatok_compat.py:220-238``) are asked one text at a time."""
+    try:
+        enc = tok(texts, add_special_tokens=False)
+        rows = [_flat_ids(r) for r in enc["input_ids"]]
+        if len(rows) == len(texts):
+            return rows
+    except Exception:
+        pass
+    return [_flat_ids(tok(t, add_special_tokens=False)["input_ids"]) for t in texts]
 
 
 def _probe_specials(tok: Any) -> Tuple[int, int]:
     plain = _ids(tok, ["A"])[0]
-    full = list(map(int, tok(["A"], add_special_tokens=True)["input_ids"][0]))
+    full = _flat_ids(tok(["A"], add_special_tokens=True)["input_ids"][0])
     if full == plain:
         return -1, -1
     n = len(plain)

@@ -6,7 +6,8 @@
 Writes ``tests/golden/golden.json`` (hashes + small literal cases) from three sources:
   * live Hugging Face tokenizers built by ``oracle/hf_oracle.py`` - the parity target;
   * the reference's own CPU paths imported from that checkout: ``DNATok`` (numpy LUT and
-    k-mer paths) wrapped around those tokenizers, and ``dnatok_compat.Evo2ByteTokenizer``;
+    k-mer paths) wrapped around those tokenizers, and the tokenizer classes of ``dnatok_compat``
+    (``NTv3Tokenizer``, ``Evo2ByteTokenizer``, ``CharTokenizer``);
   * the reference's normaliser known answers (``tests/test_gputok_bpe_backend.py:319-425``),
     re-derived by calling its ``_compile_normalizer_step``.
 The reference cannot travel to the GPU box; these vectors can.
@@ -157,6 +158,27 @@ def main():
                                              "mask_dtype": str(m2.dtype)})
             api["cases"].append(case)
     G["dnatok_api"] = api
+
+    # the reference's own tokenizer classes (src/dnatok_compat.py:135-238): the table this package
+    # discovers from each by probing, and the class's own ids for every non-empty adversarial string
+    from dnatok_compat import CharTokenizer, NTv3Tokenizer
+    from dnatok_b200 import tables
+    compat = {"inputs": [s for s in ADVERSARIAL if s], "tokenizers": {}}
+    for cname, ctok in (("NTv3Tokenizer", NTv3Tokenizer()), ("Evo2ByteTokenizer", Evo2ByteTokenizer(vocab_size=512)),
+                        ("CharTokenizer", CharTokenizer())):
+        spec = tables.spec_from_tokenizer(ctok)
+        rows = []
+        for s_ in compat["inputs"]:
+            r = ctok(s_, add_special_tokens=False)["input_ids"]
+            r = r.tolist() if hasattr(r, "tolist") else r
+            while len(r) == 1 and isinstance(r[0], list):
+                r = r[0]
+            rows.append([int(v) for v in r])
+        compat["tokenizers"][cname] = {
+            "kind": spec.kind, "vocab_size": int(spec.vocab_size), "lut256": [int(v) for v in spec.lut256],
+            "pad_id": int(spec.specials.pad_id), "unk_id": int(spec.specials.unk_id),
+            "cls_id": int(spec.specials.cls_id), "sep_id": int(spec.specials.sep_id), "ids": rows}
+    G["compat_tokenizers"] = compat
 
     # normaliser known answers, produced by the reference's compiler
     cases = [

@@ -75,3 +75,13 @@ TOKENIZERS = ["char", "kmer6", "bpe4096", "byte", "bpe32000"]
 def pack_strs(strs):
     from dnatok_b200.pack import pack_strings
     return pack_strings(strs)
+
+
+COMPAT_TOKENIZERS = ["NTv3Tokenizer", "Evo2ByteTokenizer", "CharTokenizer"]
+
+
+def compat_spec(g: dict):
+    """TokenizerSpec from the table recorded for one of the reference's own tokenizer classes."""
+    return tables.TokenizerSpec(kind=g["kind"], vocab_size=g["vocab_size"], lut256=np.asarray(g["lut256"], dtype=np.int32),
+                                specials=tables.Specials(pad_id=g["pad_id"], unk_id=g["unk_id"], cls_id=g["cls_id"],
+                                                         sep_id=g["sep_id"]))

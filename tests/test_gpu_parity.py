@@ -114,6 +114,25 @@ def test_adversarial_strings(golden, toks, name):
             assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
 
 
+@pytest.mark.parametrize("cls", H.COMPAT_TOKENIZERS)
+def test_reference_tokenizer_classes(golden, cls):
+    """The reference's own tokenizer classes (src/dnatok_compat.py:135-238): the kernel on the table
+    discovered from each class reproduces the ids the class itself gave."""
+    from dnatok_b200.tokenizer import B200Tokenizer
+    g = golden["compat_tokenizers"]["tokenizers"][cls]
+    tok = B200Tokenizer(H.compat_spec(g), device=0)
+    strs = golden["compat_tokenizers"]["inputs"]
+    flat, offs = H.pack_strs(strs)
+    enc = run_device(tok, flat, offs, padding=False, add_special_tokens=False)
+    ids, oo = enc["input_ids"].cpu().numpy(), enc["offsets"].cpu().numpy()
+    assert [ids[oo[i]:oo[i + 1]].tolist() for i in range(len(strs))] == g["ids"]
+    enc = run_device(tok, flat, offs, padding="longest", add_special_tokens=True)
+    ids, mask = enc["input_ids"].cpu().numpy(), enc["attention_mask"].cpu().numpy()
+    for i, want in enumerate(g["ids"]):
+        assert ids[i, :len(want)].tolist() == want and mask[i].sum() == len(want)
+        assert (ids[i, len(want):] == g["pad_id"]).all()
+
+
 @pytest.mark.parametrize("name", H.TOKENIZERS)
 @pytest.mark.parametrize("ids_dtype,mask_dtype", [("int64", "int64"), ("int32", "uint8"), ("int64", "int32")])
 def test_ragged_lengths_truncation_dtypes(toks, name, ids_dtype, mask_dtype):

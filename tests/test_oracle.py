@@ -50,6 +50,18 @@ def test_oracle_matches_reference_evo2_tokenizer(golden):
     assert (s.specials.pad_id, s.specials.unk_id) == (g["pad_token_id"], g["unk_token_id"])
 
 
+@pytest.mark.parametrize("cls", H.COMPAT_TOKENIZERS)
+def test_oracle_matches_reference_tokenizer_classes(golden, cls):
+    """ids the reference's own tokenizer classes (src/dnatok_compat.py:135-238) gave for the non-empty
+    adversarial strings, against the oracle run on the table discovered from each class."""
+    g = golden["compat_tokenizers"]["tokenizers"][cls]
+    s = H.compat_spec(g)
+    assert s.kind == "char"
+    flat, offs = H.pack_strs(golden["compat_tokenizers"]["inputs"])
+    ids, counts = oracle.encode_ragged("char", flat, offs, lut256=s.lut256)
+    assert [r.tolist() for r in oracle.rows(ids, offs, counts)] == g["ids"]
+
+
 @pytest.mark.parametrize("name", H.TOKENIZERS)
 def test_oracle_matches_golden_adversarial(golden, name):
     strs = golden["adversarial_inputs"]

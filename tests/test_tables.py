@@ -89,3 +89,21 @@ def test_supported_tokenizer_rules():
     assert backend._extract_merges({"model": {"merges": [["A", "C"], "G T"]}}) == ["A C", "G T"]
     with pytest.raises(ValueError):
         backend._extract_merges({"model": {"merges": [["A"]]}})
+
+
+def test_discovery_of_a_tokenizer_that_rejects_ragged_batches():
+    """A dict tokenizer that upper-cases, returns a rectangular tensor and so fails on a ragged
+    batch (like the reference's CharTokenizer, src/dnatok_compat.py:220-238) is probed one text at a time."""
+    import torch
+
+    class Plain:
+        pad_token_id, unk_token_id = 0, 9
+
+        def __call__(self, text, **kw):
+            texts = [text] if isinstance(text, str) else list(text)
+            table = {"A": 3, "C": 4, "G": 5, "T": 6}
+            return {"input_ids": torch.tensor([[table.get(c, 9) for c in t.upper()] for t in texts])}
+
+    s = tables.spec_from_tokenizer(Plain())
+    assert s.kind == "char" and (s.specials.pad_id, s.specials.unk_id, s.specials.cls_id) == (0, 9, -1)
+    assert [int(s.lut256[ord(c)]) for c in "ACGTacgtNx"] == [3, 4, 5, 6, 3, 4, 5, 6, 9, 9]
