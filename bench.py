@@ -187,6 +187,9 @@ def device_kwargs(call):
     return kw
 
 
+KMER_NO_SCRATCH = False     # --kmer-no-scratch: time the k-mer kernel that encodes one row per warp
+
+
 def time_device(tok, d_bytes, d_off, offsets, call, steps, warmup, barrier=None):
     """CUDA-event timing of ``steps`` encodes with inputs resident on the device.  Outputs and scratch
     are allocated once (first warm-up) and reused, so the timed region launches kernels only."""
@@ -201,6 +204,8 @@ def time_device(tok, d_bytes, d_off, offsets, call, steps, warmup, barrier=None)
     if not ragged and kw.get("padding") == "longest":
         # the stride is known now; later steps use it directly so no host sync sits in the loop
         kw = dict(kw, padding="max_length", max_length=int(enc["input_ids"].shape[1]))
+    if KMER_NO_SCRATCH and tok.spec.kind == "kmer":
+        scratch = False
     run = lambda: tok.encode_device(d_bytes, d_off, host_offsets=offsets, out=out, scratch=scratch, check=False, **kw)
     if ragged:
         run = make_ragged_runner(tok, d_bytes, d_off, offsets, kw, scratch, enc)
@@ -601,11 +606,20 @@ def main():
     ap.add_argument("--workload", default="kmer6", choices=["kmer6", "char", "byte", "bpe4k", "bpe32k"])
     ap.add_argument("--scale", type=int, default=0, help="batch multiplier over the literal shape (0: default)")
     ap.add_argument("--no-extra", action="store_true", help="skip the per_config section")
+    ap.add_argument("--kmer-no-scratch", action="store_true",
+                    help="k-mer without scratch memory: one warp per row instead of queued row segments")
+    ap.add_argument("--kmer-segment-windows", type=int, default=0,
+                    help="windows per k-mer row segment (library option kmer_segment_windows; 0: library default)")
     ap.add_argument("--gather", action="store_true",
                     help="multi-GPU: also time the optional NCCL gather of the padded ids to rank 0 (outside the timed region)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no e2e, no CPU baseline): the form used under ncu")
     args = ap.parse_args()
+    global KMER_NO_SCRATCH
+    KMER_NO_SCRATCH = args.kmer_no_scratch
+    if args.kmer_segment_windows:
+        from dnatok_b200 import _cabi
+        _cabi.check(_cabi.lib().dnatok_set_option(b"kmer_segment_windows", args.kmer_segment_windows))
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)

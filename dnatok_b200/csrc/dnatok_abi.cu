@@ -26,6 +26,8 @@ namespace {
 
 thread_local std::string g_err;
 std::atomic<int64_t> g_launches{0};
+std::atomic<int64_t> g_kmer_segment_windows{KSEG_WINDOWS};    // windows per k-mer row segment (scratch path)
+std::atomic<int64_t> g_kmer_force_segments{0};                // 1: segment encoder whenever scratch is given
 std::atomic<int64_t> g_host_chunk_bytes{256ll << 20};        // bytes (in + out) per chunk of the host pipeline
 std::atomic<int64_t> g_host_chunk_threshold{4ll << 30};      // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
@@ -331,6 +333,63 @@ void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_
 #undef KLAUNCH
 }
 
+// Scratch of the segmented k-mer kernel: one flag per (segment, row).  The number of segments follows
+// the average row (or the caller's row-length hint, when that is larger); longer rows finish inside
+// the last segment.
+struct KmerScratch { int* flags; int n_seg; int seg_windows; size_t bytes; };
+
+KmerScratch kmer_scratch_layout(const dnatok_handle* h, void* base, int64_t n_rows, int64_t total_bytes) {
+    KmerScratch s{};
+    if (n_rows <= 0) { s.n_seg = 1; s.seg_windows = (int)g_kmer_segment_windows; s.bytes = 256; return s; }
+    const int64_t k = h->k;
+    int64_t row_bytes = (total_bytes + n_rows - 1) / n_rows;
+    const int64_t segw = g_kmer_segment_windows;
+    s.seg_windows = (int)segw;
+    const int64_t total_seg = total_bytes / (k * segw) + 1;                    // segments the whole batch holds
+    if (h->hint_max_row > row_bytes) row_bytes = h->hint_max_row;
+    int64_t n_seg = ((row_bytes + k - 1) / k + segw - 1) / segw;
+    // a hint far above the average must not blow the ticket space up
+    const int64_t most = 4 * total_seg / n_rows + 1;
+    if (n_seg > most) n_seg = most;
+    if (n_seg < 1) n_seg = 1;
+    if (n_seg > (1 << 20)) n_seg = 1 << 20;
+    s.n_seg = (int)n_seg;
+    s.flags = (int*)base;
+    s.bytes = 256 + (size_t)n_seg * (size_t)n_rows * 4;
+    return s;
+}
+
+template <typename IdT, int K>
+void launch_kmer_seg_k(const DeviceTables& d, int32_t affine_base, const uint8_t* bytes, const int64_t* offsets,
+                       int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
+                       const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets, int32_t* status,
+                       const KmerScratch& ks, cudaStream_t st) {
+    const int64_t tickets = n_rows * ks.n_seg;
+    const int64_t want = (tickets + KW_WARPS - 1) / KW_WARPS, resident = (int64_t)d.sm_count * KSEG_BLOCKS_PER_SM;
+    const unsigned grid = (unsigned)(want < resident ? want : resident);
+    const bool fuse = mask && rf.mask_bits == (int)sizeof(IdT) * 8;
+    const bool affine = affine_base >= 0;
+#define KLAUNCH(A, F) kmer_seg_rows_kernel<IdT, K, A, F><<<grid, KW_WARPS * 32, 0, st>>>(                           \
+        bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
+        lengths_out, out_offsets, status, ks.n_seg, ks.seg_windows, ks.flags)
+    if (affine && fuse) KLAUNCH(true, true);
+    else if (affine) KLAUNCH(true, false);
+    else if (fuse) KLAUNCH(false, true);
+    else KLAUNCH(false, false);
+#undef KLAUNCH
+}
+
+template <typename IdT>
+void launch_kmer_seg(int k, const DeviceTables& d, int32_t affine_base, const uint8_t* bytes, const int64_t* offsets,
+                     int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
+                     const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets, int32_t* status,
+                     const KmerScratch& ks, cudaStream_t st) {
+#define KCASE(KK) case KK: launch_kmer_seg_k<IdT, KK>(d, affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, \
+                                                      lengths_in, lengths_out, out_offsets, status, ks, st); break;
+    switch (k) { KCASE(1) KCASE(2) KCASE(3) KCASE(4) KCASE(5) KCASE(6) KCASE(7) KCASE(8) }
+#undef KCASE
+}
+
 template <typename IdT>
 void launch_kmer_warp(int k, const DeviceTables& d, int32_t affine_base, const uint8_t* bytes, const int64_t* offsets,
                       int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
@@ -342,16 +401,35 @@ void launch_kmer_warp(int k, const DeviceTables& d, int32_t affine_base, const u
 #undef KCASE
 }
 
-// Rows of ordinary length go one per warp; batches of very long rows keep the block-per-row kernel.
+// With a scratch buffer the encoder runs row segments through a ticket queue (any row length).
+// Without one, rows of ordinary length go one per warp and batches of very long rows one per block.
 constexpr int64_t KMER_WARP_MAX_AVG_LEN = 32768;
 
 template <bool COUNT_ONLY>
 int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
                 int64_t n_rows, int64_t total_bytes, const RowFormat& rf, int id_bits, void* ids, void* mask,
                 const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets,
-                int32_t* status, cudaStream_t st) {
+                int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t st) {
     if (n_rows == 0) return 0;
     const int k = h->k;
+    // The segment encoder pays a little per segment, and its fixed deal of segments to warps cannot
+    // follow SMs that run at different speeds the way block scheduling does: it is the choice where
+    // one warp per row would leave the GPU short of work (rows fewer than the warps it keeps
+    // resident) or rows are very long; large batches of ordinary rows run faster one row per warp.
+    const bool few_rows = n_rows < (int64_t)d.sm_count * KW_BLOCKS_PER_SM * KW_WARPS;
+    const bool long_rows = total_bytes / n_rows > KMER_WARP_MAX_AVG_LEN;
+    if (!COUNT_ONLY && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && (few_rows || long_rows || g_kmer_force_segments)) {
+        const KmerScratch ks = kmer_scratch_layout(h, scratch, n_rows, total_bytes);
+        if (ks.bytes <= scratch_bytes && (ks.n_seg > 1 || g_kmer_force_segments)) {
+            CUDA_TRY(cudaMemsetAsync(scratch, 0, ks.bytes, st));
+            if (id_bits == 64) launch_kmer_seg<int64_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask,
+                                                        lengths_in, lengths_out, out_offsets, status, ks, st);
+            else launch_kmer_seg<int32_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask,
+                                          lengths_in, lengths_out, out_offsets, status, ks, st);
+            LAUNCH_CHECK("kmer_seg_rows_kernel");
+            return 0;
+        }
+    }
     if (COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
         const unsigned grid = (unsigned)((n_rows + KW_WARPS - 1) / KW_WARPS);
 #define KCASE(KK) case KK: kmer_warp_count_kernel<KK><<<grid, KW_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, total_bytes, rf, \
@@ -411,6 +489,12 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
     if (value < 0) return fail(DNATOK_ERR_INVALID, "bad option value");
     if (!strcmp(name, "host_chunk_bytes")) { g_host_chunk_bytes = value; return DNATOK_OK; }
+    if (!strcmp(name, "kmer_force_segments")) { g_kmer_force_segments = value ? 1 : 0; return DNATOK_OK; }
+    if (!strcmp(name, "kmer_segment_windows")) {
+        if (value < 64 || value > (1 << 24) || (value & 63)) return fail(DNATOK_ERR_INVALID, "kmer_segment_windows must be a multiple of 64 in 64..2^24");
+        g_kmer_segment_windows = value;
+        return DNATOK_OK;
+    }
     if (!strcmp(name, "host_chunk_threshold")) { g_host_chunk_threshold = value; return DNATOK_OK; }
     return fail(DNATOK_ERR_INVALID, "unknown option %s", name);
 }
@@ -501,7 +585,9 @@ int dnatok_set_row_bytes_hint(dnatok_handle* h, int64_t min_bytes, int64_t max_b
 }
 
 size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes) {
-    if (!h || h->kind != DNATOK_KIND_BPE || n_rows < 0 || total_bytes < 0) return 0;
+    if (!h || n_rows < 0 || total_bytes < 0) return 0;
+    if (h->kind == DNATOK_KIND_KMER) return kmer_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
+    if (h->kind != DNATOK_KIND_BPE) return 0;
     return bpe_scratch_layout(nullptr, n_rows, total_bytes).bytes;
 }
 
@@ -534,7 +620,7 @@ int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_of
             return launch_span_lengths(d_offsets, nullptr, n_rows, rf, d_lengths, d_status, st);
         case DNATOK_KIND_KMER:
             return launch_kmer<true>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, 64, nullptr, nullptr, nullptr, d_lengths,
-                                     nullptr, d_status, st);
+                                     nullptr, d_status, nullptr, 0, st);
         default: {
             if (int rc = run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, st))
                 return rc;
@@ -569,7 +655,7 @@ int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
             if (fmt->out_stride > 0 && fmt->pad_left && !d_lengths)
                 return fail(DNATOK_ERR_INVALID, "left padding needs d_lengths from dnatok_prepare");
             return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, d_lengths,
-                                      nullptr, d_out_offsets, d_status, st);
+                                      nullptr, d_out_offsets, d_status, d_scratch, scratch_bytes, st);
         default: {
             if (!d_scratch) return fail(DNATOK_ERR_SCRATCH, "BPE write needs the scratch filled by dnatok_prepare");
             BpeScratch s = bpe_scratch_layout(d_scratch, n_rows, total_bytes);
@@ -620,7 +706,7 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
                                           d_mask, d_lengths, nullptr, d_status, st);
     }
     return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
-                              nullptr, d_status, st);
+                              nullptr, d_status, d_scratch, scratch_bytes, st);
 }
 
 // ------------------------------------------------------------------ fused embedding gather

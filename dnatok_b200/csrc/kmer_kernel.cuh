@@ -188,6 +188,8 @@ kmer_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 namespace dnatok {
 
 constexpr int KW_WARPS = 8;
+constexpr int KW_BLOCKS_PER_SM = 6;     // row-per-warp encoder: 65,536 / (6 * 256) registers, i.e. 40 per thread
+constexpr int KSEG_BLOCKS_PER_SM = 5;   // segment encoder (it also holds the next ticket's row bounds): 48 per thread
 
 // 2-bit codes of four ASCII bytes at once (A C G T -> 0 1 2 3 in each byte's low bits), and a word
 // that is zero exactly in the bytes that are one of A, C, G, T.
@@ -276,43 +278,54 @@ kmer_warp_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restr
     }
 }
 
+// Everything one row's windows need, resolved once per row (or per row segment).
+template <typename IdT>
+struct KmerRow {
+    const uint8_t* src;        // first byte of the row
+    int len;                   // bytes in the row
+    int n_win;                 // windows, the short last one included
+    int64_t room_total;        // bytes from the row start to the end of the input buffer
+    IdT* orow;                 // first output column of the row
+    IdT* dst;                  // first content column (after padding and [CLS])
+    int shift;                 // left padding columns
+};
+
+// off, end: the row's bounds in the input buffer (offsets[row], offsets[row + 1])
+template <typename IdT, int K>
+__device__ __forceinline__ KmerRow<IdT> kmer_row_setup(const uint8_t* bytes, int64_t off, int64_t end, int64_t row,
+                                                       int64_t total_bytes, const RowFormat& f, IdT* ids,
+                                                       const int32_t* lengths_in, const int64_t* out_offsets) {
+    KmerRow<IdT> r;
+    const int64_t len64 = end - off;
+    r.len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);              // rows are < 2 GiB
+    r.n_win = (r.len + K - 1) / K;
+    r.src = bytes + off;
+    r.room_total = total_bytes - off;
+    const bool ragged = f.out_stride == 0;
+    r.orow = ragged ? ids + out_offsets[row] : ids + row * f.out_stride;
+    r.shift = 0;
+    if (!ragged && f.pad_left) r.shift = (int)f.out_stride - lengths_in[row];
+    r.dst = r.orow + r.shift + (f.cls_id >= 0 ? 1 : 0);
+    return r;
+}
+
+// One warp encodes windows [w, w_end) of a row whose earlier windows produced `base` content tokens;
+// returns the token count after them (it stops early once the cap is reached) and reports clipping.
 // AFFINE: the 4**K table is base + index (checked on the host), so no gather is needed.
-// FUSE_MASK: the mask has the ids' element type and is stored next to each id in the main loop.
+// FUSE_MASK: the mask has the ids' element type and is stored next to each id (mdelta elements away).
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
-__global__ void __launch_bounds__(KW_WARPS * 32, 6)
-kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
-                      int64_t total_bytes, const int32_t* __restrict__ kmer_ids, int32_t affine_base,
-                      const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
-                      void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
-                      int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
-                      int32_t* __restrict__ status) {
+__device__ __forceinline__ int kmer_encode_windows(const KmerRow<IdT>& r, int cap, const int32_t* __restrict__ kmer_ids,
+                                                   int32_t affine_base, const int32_t* __restrict__ single_ids,
+                                                   int64_t mdelta, int lane, int w, int w_end, int base, bool* clipped) {
     constexpr int NW = (2 * K + 3 + 3) / 4;            // aligned words covering 2K bytes at any byte offset
     constexpr uint32_t IDX_MASK = (1u << (2 * K)) - 1u;
     using Pair = typename IdPair<IdT>::type;
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
-    if (row >= n_rows) return;
-    const bool has_cls = f.cls_id >= 0, has_sep = f.sep_id >= 0;
-    const int n_special = (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
-    const bool ragged = f.out_stride == 0;
-    const int64_t off = offsets[row];
-    const int64_t len64 = offsets[row + 1] - off;
-    const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);       // rows are < 2 GiB
-    const int n_win = (len + K - 1) / K;
-    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
-    const uint8_t* src = bytes + off;
-    const int64_t room_total = total_bytes - off;      // bytes from the row start to the end of the buffer
-
-    IdT* orow = ragged ? ids + out_offsets[row] : ids + row * f.out_stride;
-    int shift = 0;
-    if (!ragged && f.pad_left) shift = (int)f.out_stride - lengths_in[row];
-    IdT* dst = orow + shift + (has_cls ? 1 : 0);
-    IdT* mdst = FUSE_MASK ? reinterpret_cast<IdT*>(mask) + (dst - ids) : nullptr;
-
-    int base = 0;              // content tokens placed so far (uncapped)
-    int w = 0;                 // next window of the row
+    const uint8_t* src = r.src;
+    const int len = r.len;
+    const int64_t room_total = r.room_total;
+    IdT* dst = r.dst;
+    IdT* mdst = dst + mdelta;
     const int n_full = len / K;                          // complete windows
-    bool clipped = false;
 
     // The two windows of this lane in the chunk of `nwin` windows starting at window w0:
     // lengths, table indices, cleanliness.
@@ -321,7 +334,7 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
         Two t;
         const int wa = w0 + 2 * lane;
         int lim = w0 + nwin;                              // one past the chunk's last window
-        if (lim > n_win) lim = n_win;
+        if (lim > w_end) lim = w_end;
         t.p = wa * K;
         t.idxA = 0; t.idxB = 0;
         // both windows complete, inside the chunk, and the aligned words inside the buffer: the wide route
@@ -336,9 +349,9 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
             uint32_t P = 0, dA = 0, dB = 0;
 #pragma unroll
             for (int i = 0; i < NW - 1; ++i) {
-                const uint32_t r = __funnelshift_r(wd[i], wd[i + 1], sh);     // bytes 4i .. 4i+3 of the pair
+                const uint32_t rr = __funnelshift_r(wd[i], wd[i + 1], sh);    // bytes 4i .. 4i+3 of the pair
                 uint32_t c, d;
-                acgt_codes4(r, &c, &d);
+                acgt_codes4(rr, &c, &d);
                 P |= pack_codes4(c) << (24 - 8 * i);
                 // byte b of this word belongs to window A when 4i+b < K, to window B when K <= 4i+b < 2K
                 uint32_t mA = 0, mB = 0;
@@ -382,7 +395,7 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                 if (t.lenA && pos < cap) { dst[pos] = a; if (FUSE_MASK) mdst[pos] = 1; }
                 if (t.lenB && pos + 1 < cap) { dst[pos + 1] = b; if (FUSE_MASK) mdst[pos + 1] = 1; }
             }
-            const int left = n_win - w0;
+            const int left = w_end - w0;
             base += left < nwin ? left : nwin;
         } else {
             const int cntA = t.lenA == 0 ? 0 : (t.cleanA ? 1 : t.lenA);
@@ -407,18 +420,19 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
         }
     };
 
-    // Wide-route decode of the two windows at g (no bounds checks): table indices and a word that is
-    // non-zero when either window holds anything but ACGT.
-    auto decode_tight = [&](const uint32_t* gw, uint32_t sh, uint32_t* idxA, uint32_t* idxB) -> uint32_t {
-        uint32_t wd[NW];
+    // Wide-route decode of the two windows held in wd (no bounds checks): table indices and a word
+    // that is non-zero when either window holds anything but ACGT.
+    auto load_words = [&](const uint32_t* gw, uint32_t* wd) {
 #pragma unroll
         for (int i = 0; i < NW; ++i) wd[i] = __ldg(gw + i);
+    };
+    auto decode_words = [&](const uint32_t* wd, uint32_t sh, uint32_t* idxA, uint32_t* idxB) -> uint32_t {
         uint32_t P = 0, bad = 0;
 #pragma unroll
         for (int i = 0; i < NW - 1; ++i) {
-            const uint32_t r = __funnelshift_r(wd[i], wd[i + 1], sh);
+            const uint32_t rr = __funnelshift_r(wd[i], wd[i + 1], sh);
             uint32_t c, d;
-            acgt_codes4(r, &c, &d);
+            acgt_codes4(rr, &c, &d);
             P |= pack_codes4(c) << (24 - 8 * i);
             uint32_t m = 0;
 #pragma unroll
@@ -429,29 +443,35 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
         *idxB = (P >> (32 - 4 * K)) & IDX_MASK;
         return bad;
     };
-    // windows [0, n_tight) are complete and their aligned words stay in the buffer
-    int n_tight = n_full;
+    // windows [0, n_tight) are complete, inside [.., w_end) and their aligned words stay in the buffer
+    int n_tight = n_full < w_end ? n_full : w_end;
     {
         const int64_t fit = (room_total - 8) / K;
         if (fit < n_tight) n_tight = fit < 0 ? 0 : (int)fit;
     }
-    const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
     Pair one; one.x = 1; one.y = 1;
 
-    while (w < n_win && base < cap) {
-        // 16-byte stores need an even element offset; after an odd number of tokens (a chunk with
-        // single-base fallbacks) one chunk of 63 windows puts the row back in step
+    bool peel = true;          // an odd element offset is first answered by a chunk of one window
+    while (w < w_end && base < cap) {
+        // 16-byte stores need an even element offset.  After an odd number of tokens (the [CLS] slot,
+        // a chunk with single-base fallbacks) one window on its own puts the row back in step when it
+        // is a clean k-mer; if it was not, a chunk of 63 windows follows.
         const bool al = (reinterpret_cast<uintptr_t>(dst + base) % (2 * sizeof(IdT))) == 0;
         if (al) {
+            peel = true;
+            bool dirty = false;
             // tight stretch: clean full chunks, two per trip, no per-token checks
             const uint8_t* g = src + (w + 2 * lane) * K;
             const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;   // constant while w moves by 64: 64K % 4 == 0
             const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
             IdT* d = dst + base + 2 * lane;
             while (w + 128 <= n_tight && base + 128 <= cap) {
+                uint32_t c0[NW], c1[NW];
+                load_words(gw, c0);
+                load_words(gw + 16 * K, c1);
                 uint32_t a0, b0, a1, b1;
-                const uint32_t bad0 = decode_tight(gw, sh, &a0, &b0);
-                const uint32_t bad1 = decode_tight(gw + 16 * K, sh, &a1, &b1);
+                const uint32_t bad0 = decode_words(c0, sh, &a0, &b0);
+                const uint32_t bad1 = decode_words(c1, sh, &a1, &b1);
                 Pair v0, v1;
                 v0.x = (IdT)(AFFINE ? affine_base + (int32_t)a0 : __ldg(kmer_ids + a0));
                 v0.y = (IdT)(AFFINE ? affine_base + (int32_t)b0 : __ldg(kmer_ids + b0));
@@ -462,6 +482,7 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                         if (FUSE_MASK) *reinterpret_cast<Pair*>(d + mdelta) = one;
                         base += 64; w += 64;
                     }
+                    dirty = true;
                     break;
                 }
                 v1.x = (IdT)(AFFINE ? affine_base + (int32_t)a1 : __ldg(kmer_ids + a1));
@@ -471,20 +492,46 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                 if (FUSE_MASK) { *reinterpret_cast<Pair*>(d + mdelta) = one; *reinterpret_cast<Pair*>(d + mdelta + 64) = one; }
                 gw += 32 * K; d += 128; base += 128; w += 128;
             }
-            if (w >= n_win) break;
+            // one more clean full chunk where two no longer fit
+            if (!dirty && w + 64 <= n_tight && base + 64 <= cap) {
+                uint32_t a0, b0, c0[NW];
+                load_words(gw, c0);
+                const uint32_t bad0 = decode_words(c0, sh, &a0, &b0);
+                if (!__any_sync(0xffffffffu, bad0 != 0)) {
+                    Pair v0;
+                    v0.x = (IdT)(AFFINE ? affine_base + (int32_t)a0 : __ldg(kmer_ids + a0));
+                    v0.y = (IdT)(AFFINE ? affine_base + (int32_t)b0 : __ldg(kmer_ids + b0));
+                    *reinterpret_cast<Pair*>(d) = v0;
+                    if (FUSE_MASK) *reinterpret_cast<Pair*>(d + mdelta) = one;
+                    base += 64; w += 64;
+                }
+            }
+            if (w >= w_end) break;
             if (base >= cap) break;
         }
         // one chunk by the general route (dirty windows, row edges, the last tokens before the cap)
-        const int nwin = al ? 64 : 63;
+        const int nwin = al ? 64 : (peel ? 1 : 63);
+        if (!al) peel = false;
         const Two t0 = decode(w, nwin);
         emit(w, nwin, t0);
         w += nwin;
     }
-    if (w < n_win) clipped = true;
-    if (base > cap) clipped = true;
+    if (w < w_end) *clipped = true;
+    if (base > cap) *clipped = true;
+    return base;
+}
 
+// What remains once the content tokens of a row are placed: lengths, [CLS]/[SEP], padding, mask.
+template <typename IdT, bool FUSE_MASK>
+__device__ __forceinline__ void kmer_finish_row(const KmerRow<IdT>& r, int64_t row, int base, int cap, bool clipped,
+                                                const RowFormat& f, IdT* ids, void* mask, int32_t* lengths_out,
+                                                const int64_t* out_offsets, int32_t* status, int lane) {
+    const bool has_cls = f.cls_id >= 0, has_sep = f.sep_id >= 0;
+    const bool ragged = f.out_stride == 0;
     const int n = base < cap ? base : cap;
-    const int T = n + n_special;
+    const int T = n + (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
+    IdT* orow = r.orow;
+    const int shift = r.shift;
     if (lane == 0) {
         if (lengths_out) lengths_out[row] = (int32_t)T;
         if (status && f.clip_is_error && clipped) atomicOr(status + row, 4);
@@ -508,6 +555,124 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
         if (f.mask_bits == 64) warp_write_run<int64_t>((int64_t*)mask + o, T, lane, [](int64_t) { return (int64_t)1; });
         else if (f.mask_bits == 32) warp_write_run<int32_t>((int32_t*)mask + o, T, lane, [](int64_t) { return (int32_t)1; });
         else warp_write_run<uint8_t>((uint8_t*)mask + o, T, lane, [](int64_t) { return (uint8_t)1; });
+    }
+}
+
+// One warp per row, no scratch memory: used when the caller passes no scratch buffer.
+template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
+__global__ void __launch_bounds__(KW_WARPS * 32, KW_BLOCKS_PER_SM)
+kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                      int64_t total_bytes, const int32_t* __restrict__ kmer_ids, int32_t affine_base,
+                      const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
+                      void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
+                      int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
+                      int32_t* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const KmerRow<IdT> r = kmer_row_setup<IdT, K>(bytes, offsets[row], offsets[row + 1], row, total_bytes, f, ids, lengths_in,
+                                                  out_offsets);
+    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
+    const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
+    bool clipped = false;
+    const int base = kmer_encode_windows<IdT, K, AFFINE, FUSE_MASK>(r, cap, kmer_ids, affine_base, single_ids, mdelta, lane,
+                                                                    0, r.n_win, 0, &clipped);
+    kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
+}
+
+// Rows cut into segments of seg_windows windows (an even number) and dealt round-robin to a grid of resident warps:
+// ticket t stands for segment t / n_rows of row t % n_rows, warp g of G takes tickets g, g + G, ...,
+// so all first segments are under way before any second segment.  A segment needs the number of
+// tokens its predecessors produced: each warp publishes that count (+1, 0 = not yet) in
+// flags[segment * n_rows + row] when it is done, and the warp holding the next segment of the row
+// polls it.  The grid never exceeds what the GPU keeps resident and every warp takes its tickets in
+// rising order, so the holder of an earlier ticket waits only on still earlier ones and the polls
+// end; they are bounded all the same, and a row whose wait ran out is reported with
+// DNATOK_ROW_STALLED instead of tokens.
+// Segment boundaries sit where the output offset is even when every earlier window was a clean
+// k-mer, so a segment starts on a 16-byte boundary in the common case.  The last segment index has
+// no upper bound: rows longer than n_seg * seg_windows windows finish inside it.
+constexpr int KSEG_WINDOWS = 256;
+constexpr int KSEG_POLL_LIMIT = 1 << 20;
+constexpr int KSEG_POISON = 0x7fffffff;
+
+template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
+__global__ void __launch_bounds__(KW_WARPS * 32, KSEG_BLOCKS_PER_SM)
+kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                     int64_t total_bytes, const int32_t* __restrict__ kmer_ids, int32_t affine_base,
+                     const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
+                     void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
+                     int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
+                     int32_t* __restrict__ status, int n_seg, int seg_windows, int* __restrict__ flags) {
+    const int lane = threadIdx.x & 31;
+    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
+    const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
+    const int64_t n_tickets = n_rows * (int64_t)n_seg;
+    const int64_t n_warps = (int64_t)gridDim.x * KW_WARPS;
+    // (segment, row) of the ticket after this warp's current one, kept in step without dividing; its
+    // row bounds and its predecessor's flag are fetched while the current ticket is being worked on
+    const int64_t t0 = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
+    if (t0 >= n_tickets) return;
+    int seg2 = (int)(t0 / n_rows);
+    int64_t row2 = t0 - (int64_t)seg2 * n_rows;
+    const int step_seg = (int)(n_warps / n_rows);
+    const int64_t step_row = n_warps - (int64_t)step_seg * n_rows;
+    int64_t off2 = offsets[row2], end2 = offsets[row2 + 1];
+    int flag2 = seg2 > 0 ? *(const volatile int*)(flags + (int64_t)(seg2 - 1) * n_rows + row2) : 0;
+    for (int64_t t = t0; t < n_tickets; t += n_warps) {
+        const int seg = seg2;
+        const int64_t row = row2, off = off2, end = end2;
+        const int flag_seen = flag2;
+        seg2 += step_seg;
+        row2 += step_row;
+        if (row2 >= n_rows) { row2 -= n_rows; ++seg2; }
+        if (t + n_warps < n_tickets) {
+            off2 = offsets[row2];
+            end2 = offsets[row2 + 1];
+            flag2 = seg2 > 0 ? *(const volatile int*)(flags + (int64_t)(seg2 - 1) * n_rows + row2) : 0;
+        }
+        const KmerRow<IdT> r = kmer_row_setup<IdT, K>(bytes, off, end, row, total_bytes, f, ids, lengths_in, out_offsets);
+        // boundary of segment s >= 1: s * seg_windows (+1 when the first content column has an odd offset)
+        const int odd = (int)((reinterpret_cast<uintptr_t>(r.dst) / sizeof(IdT)) & 1u);
+        const int64_t w0 = seg == 0 ? 0 : (int64_t)seg * seg_windows + odd;
+        if (seg > 0 && w0 >= r.n_win) continue;                                  // the row ended in an earlier segment
+        const int64_t w1 = (int64_t)(seg + 1) * seg_windows + odd;
+        const bool last = seg == n_seg - 1 || w1 >= r.n_win;
+        const int w_end = last ? r.n_win : (int)w1;
+        int base = 0;
+        if (seg > 0) {
+            const volatile int* fl = flags + (int64_t)(seg - 1) * n_rows + row;
+            int v = flag_seen;
+            if (lane == 0 && v == 0) {
+                int polls = 0;
+                while ((v = *fl) == 0) {
+                    if (++polls > KSEG_POLL_LIMIT) { v = KSEG_POISON; break; }
+                    __nanosleep(100);
+                }
+            }
+            v = __shfl_sync(0xffffffffu, v, 0);
+            if (v == KSEG_POISON) {
+                if (lane == 0) {
+                    if (status) atomicOr(status + row, 16);
+                    if (!last) { flags[(int64_t)seg * n_rows + row] = KSEG_POISON; }
+                    else if (lengths_out) lengths_out[row] = 0;
+                }
+                continue;
+            }
+            base = v - 1;
+        }
+        bool clipped = false;
+        base = kmer_encode_windows<IdT, K, AFFINE, FUSE_MASK>(r, cap, kmer_ids, affine_base, single_ids, mdelta, lane,
+                                                              (int)w0, w_end, base, &clipped);
+        if (!last) {
+            if (lane == 0) {
+                if (status && f.clip_is_error && clipped) atomicOr(status + row, 4);
+                // the count travels in the flag itself and nobody reads this warp's tokens: no fence
+                *(volatile int*)(flags + (int64_t)seg * n_rows + row) = base + 1;
+            }
+        } else {
+            kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
+        }
     }
 }
 

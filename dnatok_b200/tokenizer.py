@@ -116,7 +116,8 @@ class B200Tokenizer:
         ``input_ids`` (and ``attention_mask``) for padded output, or ``input_ids`` (flat),
         ``offsets`` (int64[B+1]) for ``padding=False``.  ``lengths`` (int32[B]) is always included.
         ``out`` may carry preallocated ``input_ids`` / ``attention_mask`` tensors and ``scratch`` a
-        uint8 scratch tensor, which makes the call allocation-free for fixed strides.
+        uint8 scratch tensor, which makes the call allocation-free for fixed strides;
+        ``scratch=False`` runs a k-mer tokenizer without scratch memory (one warp per row).
         """
         torch = _torch()
         L = _cabi.lib()
@@ -143,8 +144,9 @@ class B200Tokenizer:
             raise ValueError("padding='max_length' needs max_length")
         ns = self._n_special(add_special_tokens)
         out = out or {}
-        if self.spec.kind == "bpe":
-            # row lengths known on the host bound the length classes the BPE path has to launch
+        if self.spec.kind in ("bpe", "kmer"):
+            # row lengths known on the host bound the length classes the BPE path has to launch and
+            # the number of segments the k-mer path cuts a row into
             if host_offsets is not None and B:
                 lens = np.diff(host_offsets)
                 _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, int(lens.min()), max(int(lens.max()), 1)))
@@ -153,6 +155,10 @@ class B200Tokenizer:
         with torch.cuda.device(dev):
             stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
             need = L.dnatok_scratch_bytes(self.handle.ptr, B, total)
+            if scratch is False:
+                if self.spec.kind == "bpe":
+                    raise ValueError("the BPE path needs a scratch buffer")
+                need = 0                       # k-mer without scratch: one warp (or block) per row
             if need and (scratch is None or scratch.numel() < need):
                 scratch = torch.empty(need, dtype=torch.uint8, device=dev)
             sc_ptr = ctypes.c_void_p(scratch.data_ptr()) if need else None
@@ -277,6 +283,9 @@ class B200Tokenizer:
         if np.any(st & _cabi.ROW_NOT_CONVERGED):
             raise RuntimeError("BPE merge loop hit its pass limit on row %d" %
                                int(np.flatnonzero(st & _cabi.ROW_NOT_CONVERGED)[0]))
+        if np.any(st & _cabi.ROW_STALLED):
+            raise RuntimeError("k-mer row %d: a row segment gave up waiting for the one before it"
+                               % int(np.flatnonzero(st & _cabi.ROW_STALLED)[0]))
         if np.any(st & _cabi.ROW_CLIPPED):
             raise ValueError("row %d has more tokens than max_length and truncation is off "
                              "(Hugging Face cannot build a tensor from such a batch either)"

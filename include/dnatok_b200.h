@@ -50,6 +50,7 @@ extern "C" {
 #define DNATOK_ROW_NOT_CONVERGED  2   /* BPE pass limit reached (cannot happen for a consistent table) */
 #define DNATOK_ROW_CLIPPED        4   /* row had more tokens than out_stride and was cut to fit */
 #define DNATOK_ROW_OUTSIDE_HINT   8   /* BPE row length outside dnatok_set_row_bytes_hint; row left empty */
+#define DNATOK_ROW_STALLED        16  /* k-mer row segment gave up waiting for the segment before it; row left unfinished */
 
 #define DNATOK_KIND_CHAR 0
 #define DNATOK_KIND_KMER 1
@@ -97,8 +98,13 @@ int dnatok_kind(const dnatok_handle* h);
  * its host offsets by itself.  No reference counterpart (its kernel is one launch, one block per row). */
 int dnatok_set_row_bytes_hint(dnatok_handle* h, int64_t min_bytes, int64_t max_bytes);
 
-/* Bytes of caller-owned device scratch dnatok_prepare / dnatok_encode need for this batch
- * (0 for char).  The scratch must be 256-byte aligned. */
+/* Bytes of caller-owned device scratch dnatok_prepare / dnatok_encode use for this batch
+ * (0 for char).  The scratch must be 256-byte aligned.  BPE requires it.  For k-mer it is optional
+ * (one flag per row segment): with it, batches that one warp per row could not spread over the
+ * whole GPU (few rows, or very long rows) are cut into segments of 256 windows dealt round-robin
+ * to resident warps; without it one warp (or one block, for very long rows) encodes each row.
+ * Results are identical.  The size depends on the handle's row-length hint: query it after
+ * dnatok_set_row_bytes_hint. */
 size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes);
 
 /* Upper bound on the number of ids a ragged output can hold for this batch. */
@@ -194,6 +200,8 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
  *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)
  *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB)
+ *   "kmer_segment_windows"  windows per k-mer row segment, a multiple of 64 (default 256)
+ *   "kmer_force_segments"   1: use the k-mer segment encoder whenever scratch is given, whatever the batch shape
  *   "bpe_block_team_rows"   BPE batches of at most this many rows give every word a whole thread block
  *                           instead of one warp (lower latency when the batch cannot fill the GPU);
  *                           -1 (default): 8 rows per SM */

@@ -45,7 +45,14 @@ def test_handles_for_all_five_tokenizers(name):
     kind = {"char": 0, "kmer": 1, "bpe": 2}[H.spec(name).kind]
     assert L.dnatok_kind(h.ptr) == kind
     sb = L.dnatok_scratch_bytes(h.ptr, 1000, 1 << 20)
-    assert (sb > 2 * (1 << 20)) if kind == 2 else sb == 0
+    if kind == 2:
+        assert sb > 2 * (1 << 20)
+    elif kind == 1:
+        # one flag per segment of 256 windows and row (1,048 bp rows of 6-mers: one segment each)
+        assert sb == 256 + 4 * 1000
+        assert L.dnatok_scratch_bytes(h.ptr, 10, 1 << 20) == 256 + 4 * 10 * 69
+    else:
+        assert sb == 0
     fmt = _cabi.Format(64, 64, 1, 0, 0, 0)
     ns = (H.spec(name).specials.cls_id >= 0) + (H.spec(name).specials.sep_id >= 0)
     assert L.dnatok_max_tokens(h.ptr, 10, 500, ctypes.byref(fmt)) == 500 + 10 * ns

@@ -246,6 +246,58 @@ def _kmer_spec(k):
                          kmer_ids=(5 + rng.permutation(4 ** k)).astype(np.int32))
 
 
+@pytest.mark.parametrize("k,shape", [(6, "mixed"), (6, "uniform"), (3, "mixed"), (5, "long_tail")])
+def test_kmer_segment_queue_equals_row_per_warp(k, shape):
+    """k-mer with scratch (rows cut into segments taken from a ticket queue) against the oracle and
+    against the same call without scratch (one warp per row): rows of many segments, N runs that
+    change the token parity between segments, a row far longer than the average, every output layout."""
+    from dnatok_b200.tokenizer import B200Tokenizer
+    from oracle import oracle
+    spec = _kmer_spec(k)
+    tok = B200Tokenizer(spec, device=0)
+    rng = np.random.default_rng(7 * k + len(shape))
+    if shape == "uniform":
+        lens = np.full(300, 6000)
+    elif shape == "mixed":
+        lens = rng.integers(0, 40000, size=150)
+        lens[:6] = [0, 1, 256 * k, 256 * k + 1, 257 * k, 512 * k + k - 1]
+    else:
+        lens = rng.integers(0, 3000, size=200)
+        lens[17] = 700001
+    rows_b = []
+    for n in lens:
+        r = np.frombuffer(b"ACGT", np.uint8)[rng.integers(0, 4, int(n))].copy()
+        for _ in range(int(n) // 1500):
+            s0 = int(rng.integers(0, n))
+            r[s0:s0 + int(rng.integers(1, 40))] = ord("N")
+        rows_b.append(r)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat = np.concatenate(rows_b) if len(rows_b) else np.zeros(0, np.uint8)
+    ids, counts = oracle.encode_ragged("kmer", flat, offs, lut256=spec.lut256, k=k, kmer_ids=spec.kmer_ids)
+    rows = oracle.rows(ids, offs, counts)
+    calls = [dict(padding="longest"), dict(padding="max_length", max_length=1000, truncation=True),
+             dict(padding="longest", add_special_tokens=False, ids_dtype=torch.int32, mask_dtype=torch.uint8),
+             dict(padding="max_length", max_length=777, truncation=True, add_special_tokens=False)]
+    for left in (False, True):
+        tok.padding_side = "left" if left else "right"
+        for kw in calls:
+            a = run_device(tok, flat, offs, **kw)
+            b = run_device(tok, flat, offs, scratch=False, **kw)
+            want_ids, want_mask = oracle.assemble(rows, pad_id=0, cls_id=2, sep_id=3,
+                                                  add_special=kw.get("add_special_tokens", True),
+                                                  max_length=kw.get("max_length", 0), truncation=kw.get("truncation", False),
+                                                  padding=kw["padding"], pad_left=left)
+            for enc in (a, b):
+                assert np.array_equal(enc["input_ids"].cpu().numpy(), want_ids), (kw, left)
+                assert np.array_equal(enc["attention_mask"].cpu().numpy(), want_mask), (kw, left)
+                assert np.array_equal(enc["lengths"].cpu().numpy()[:len(lens)], want_mask.sum(axis=1)), (kw, left)
+    tok.padding_side = "right"
+    want = np.concatenate(oracle.assemble(rows, pad_id=0, cls_id=2, sep_id=3, padding=False))
+    for sc in (None, False):
+        enc = run_device(tok, flat, offs, padding=False, scratch=sc)
+        assert np.array_equal(enc["input_ids"].cpu().numpy()[:len(want)], want)
+
+
 @pytest.mark.parametrize("k", [1, 2, 3, 4, 5, 7, 8])
 def test_kmer_other_k(k):
     """Every window width the kernel is instantiated for, ragged rows, odd byte alignments."""
