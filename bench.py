@@ -608,8 +608,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the per_config section")
     ap.add_argument("--kmer-no-scratch", action="store_true",
                     help="k-mer without scratch memory: one warp per row instead of queued row segments")
-    ap.add_argument("--kmer-segment-windows", type=int, default=0,
-                    help="windows per k-mer row segment (library option kmer_segment_windows; 0: library default)")
+    ap.add_argument("--kmer-force-segments", action="store_true",
+                    help="k-mer: use the segment encoder whatever the batch shape (library option kmer_force_segments)")
     ap.add_argument("--gather", action="store_true",
                     help="multi-GPU: also time the optional NCCL gather of the padded ids to rank 0 (outside the timed region)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -617,9 +617,9 @@ def main():
     args = ap.parse_args()
     global KMER_NO_SCRATCH
     KMER_NO_SCRATCH = args.kmer_no_scratch
-    if args.kmer_segment_windows:
+    if args.kmer_force_segments:
         from dnatok_b200 import _cabi
-        _cabi.check(_cabi.lib().dnatok_set_option(b"kmer_segment_windows", args.kmer_segment_windows))
+        _cabi.check(_cabi.lib().dnatok_set_option(b"kmer_force_segments", 1))
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)

@@ -26,7 +26,6 @@ namespace {
 
 thread_local std::string g_err;
 std::atomic<int64_t> g_launches{0};
-std::atomic<int64_t> g_kmer_segment_windows{KSEG_WINDOWS};    // windows per k-mer row segment (scratch path)
 std::atomic<int64_t> g_kmer_force_segments{0};                // 1: segment encoder whenever scratch is given
 std::atomic<int64_t> g_host_chunk_bytes{256ll << 20};        // bytes (in + out) per chunk of the host pipeline
 std::atomic<int64_t> g_host_chunk_threshold{4ll << 30};      // batches below this size are not chunked
@@ -286,18 +285,25 @@ int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, 
                 int32_t* lengths, const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
     if (n_rows == 0) return 0;
     if (rf.out_stride > 0) {
-        const int64_t spr = (rf.out_stride + EMIT_SPAN - 1) / EMIT_SPAN;
+        const uint8_t* sb = reinterpret_cast<const uint8_t*>(src);
+        const uint8_t* se = sb + (size_t)total_bytes * sizeof(SrcT);
+        // 32-bit ids on rows of several thousand columns: wider spans, so a trip stores 4 KiB as it does for 64-bit ids
+        const bool wide = id_bits == 32 && sizeof(SrcT) == 1 && rf.out_stride >= 4 * EMIT_SPAN_WIDE;
+        const int64_t span_cols = wide ? EMIT_SPAN_WIDE : EMIT_SPAN;
+        const int64_t spr = (rf.out_stride + span_cols - 1) / span_cols;
         const int64_t n_spans = spr * n_rows;
         const int64_t blocks = (n_spans + EMIT_WARPS - 1) / EMIT_WARPS;
         const unsigned grid = (unsigned)(blocks < (int64_t)d.sm_count * 32 ? blocks : (int64_t)d.sm_count * 32);
-        const uint8_t* sb = reinterpret_cast<const uint8_t*>(src);
-        const uint8_t* se = sb + (size_t)total_bytes * sizeof(SrcT);
         if (id_bits == 64)
-            emit_padded_kernel<SrcT, int64_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
-                                                                                  (int64_t*)ids, mask, lengths, status, spr, n_spans);
+            emit_padded_kernel<SrcT, int64_t, LUT, EMIT_SPAN><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
+                                                                                             (int64_t*)ids, mask, lengths, status, spr, n_spans);
+        else if (wide)
+            emit_padded_kernel<uint8_t, int32_t, LUT, EMIT_SPAN_WIDE><<<grid, EMIT_THREADS, 0, st>>>(
+                reinterpret_cast<const uint8_t*>(src), sb, se, offsets, counts, n_rows, d.lut256, rf, (int32_t*)ids, mask, lengths,
+                status, spr, n_spans);
         else
-            emit_padded_kernel<SrcT, int32_t, LUT><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
-                                                                                  (int32_t*)ids, mask, lengths, status, spr, n_spans);
+            emit_padded_kernel<SrcT, int32_t, LUT, EMIT_SPAN><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
+                                                                                             (int32_t*)ids, mask, lengths, status, spr, n_spans);
         LAUNCH_CHECK("emit_padded_kernel");
     } else {
         const int64_t bound = total_bytes + 2 * n_rows;
@@ -336,15 +342,14 @@ void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_
 // Scratch of the segmented k-mer kernel: one flag per (segment, row).  The number of segments follows
 // the average row (or the caller's row-length hint, when that is larger); longer rows finish inside
 // the last segment.
-struct KmerScratch { int* flags; int n_seg; int seg_windows; size_t bytes; };
+struct KmerScratch { uint32_t* flags; int n_seg; size_t bytes; };
 
 KmerScratch kmer_scratch_layout(const dnatok_handle* h, void* base, int64_t n_rows, int64_t total_bytes) {
     KmerScratch s{};
-    if (n_rows <= 0) { s.n_seg = 1; s.seg_windows = (int)g_kmer_segment_windows; s.bytes = 256; return s; }
+    if (n_rows <= 0) { s.n_seg = 1; s.bytes = 256; return s; }
     const int64_t k = h->k;
     int64_t row_bytes = (total_bytes + n_rows - 1) / n_rows;
-    const int64_t segw = g_kmer_segment_windows;
-    s.seg_windows = (int)segw;
+    const int64_t segw = KSEG_WINDOWS;
     const int64_t total_seg = total_bytes / (k * segw) + 1;                    // segments the whole batch holds
     if (h->hint_max_row > row_bytes) row_bytes = h->hint_max_row;
     int64_t n_seg = ((row_bytes + k - 1) / k + segw - 1) / segw;
@@ -354,7 +359,7 @@ KmerScratch kmer_scratch_layout(const dnatok_handle* h, void* base, int64_t n_ro
     if (n_seg < 1) n_seg = 1;
     if (n_seg > (1 << 20)) n_seg = 1 << 20;
     s.n_seg = (int)n_seg;
-    s.flags = (int*)base;
+    s.flags = (uint32_t*)base;
     s.bytes = 256 + (size_t)n_seg * (size_t)n_rows * 4;
     return s;
 }
@@ -371,7 +376,7 @@ void launch_kmer_seg_k(const DeviceTables& d, int32_t affine_base, const uint8_t
     const bool affine = affine_base >= 0;
 #define KLAUNCH(A, F) kmer_seg_rows_kernel<IdT, K, A, F><<<grid, KW_WARPS * 32, 0, st>>>(                           \
         bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
-        lengths_out, out_offsets, status, ks.n_seg, ks.seg_windows, ks.flags)
+        lengths_out, out_offsets, status, ks.n_seg, ks.flags)
     if (affine && fuse) KLAUNCH(true, true);
     else if (affine) KLAUNCH(true, false);
     else if (fuse) KLAUNCH(false, true);
@@ -401,9 +406,12 @@ void launch_kmer_warp(int k, const DeviceTables& d, int32_t affine_base, const u
 #undef KCASE
 }
 
-// With a scratch buffer the encoder runs row segments through a ticket queue (any row length).
-// Without one, rows of ordinary length go one per warp and batches of very long rows one per block.
+// With a scratch buffer, batches of few or very long rows are encoded (and counted) as row segments.
+// Otherwise rows of ordinary length go one per warp and batches of very long rows one per block.
 constexpr int64_t KMER_WARP_MAX_AVG_LEN = 32768;
+
+int launch_span_lengths(const int64_t* offsets, const int32_t* counts, int64_t n_rows, const RowFormat& rf,
+                        int32_t* lengths, int32_t* status, cudaStream_t st);
 
 template <bool COUNT_ONLY>
 int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
@@ -412,13 +420,17 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
                 int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t st) {
     if (n_rows == 0) return 0;
     const int k = h->k;
-    // The segment encoder pays a little per segment, and its fixed deal of segments to warps cannot
-    // follow SMs that run at different speeds the way block scheduling does: it is the choice where
-    // one warp per row would leave the GPU short of work (rows fewer than the warps it keeps
-    // resident) or rows are very long; large batches of ordinary rows run faster one row per warp.
-    const bool few_rows = n_rows < (int64_t)d.sm_count * KW_BLOCKS_PER_SM * KW_WARPS;
+    // The segment encoder spends about half as many instructions again per row (look-back, a second
+    // pass over segments that hold an N), and its fixed deal of segments to warps cannot follow SMs
+    // that run at different speeds the way block scheduling does: it is the choice where one warp
+    // per row would leave the GPU short of work (few rows) or rows are very long; large batches of
+    // ordinary rows run faster one row per warp.
+    const bool few_rows = n_rows < (int64_t)d.sm_count * 8;
     const bool long_rows = total_bytes / n_rows > KMER_WARP_MAX_AVG_LEN;
-    if (!COUNT_ONLY && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && (few_rows || long_rows || g_kmer_force_segments)) {
+    // the flags carry 30-bit token counts: a row that might hold 2^30 tokens stays with the other kernels
+    const int64_t longest = h->hint_max_row > 0 && h->hint_max_row < total_bytes ? h->hint_max_row : total_bytes;
+    if (!COUNT_ONLY && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && longest < (1ll << 30) &&
+        (few_rows || long_rows || g_kmer_force_segments)) {
         const KmerScratch ks = kmer_scratch_layout(h, scratch, n_rows, total_bytes);
         if (ks.bytes <= scratch_bytes && (ks.n_seg > 1 || g_kmer_force_segments)) {
             CUDA_TRY(cudaMemsetAsync(scratch, 0, ks.bytes, st));
@@ -428,6 +440,21 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
                                           lengths_in, lengths_out, out_offsets, status, ks, st);
             LAUNCH_CHECK("kmer_seg_rows_kernel");
             return 0;
+        }
+    }
+    if (COUNT_ONLY && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && (few_rows || long_rows)) {
+        const KmerScratch ks = kmer_scratch_layout(h, scratch, n_rows, total_bytes);
+        if (ks.bytes <= scratch_bytes && ks.n_seg > 1) {
+            int32_t* counts = reinterpret_cast<int32_t*>(ks.flags);
+            CUDA_TRY(cudaMemsetAsync(counts, 0, (size_t)n_rows * 4, st));
+            const int64_t want = (n_rows * ks.n_seg + KW_WARPS - 1) / KW_WARPS, most = (int64_t)d.sm_count * 8;
+            const unsigned grid = (unsigned)(want < most ? want : most);
+#define KCASE(KK) case KK: kmer_seg_count_kernel<KK><<<grid, KW_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, total_bytes, ks.n_seg, \
+                                                                                 KSEG_WINDOWS, counts); break;
+            switch (k) { KCASE(1) KCASE(2) KCASE(3) KCASE(4) KCASE(5) KCASE(6) KCASE(7) KCASE(8) }
+#undef KCASE
+            LAUNCH_CHECK("kmer_seg_count_kernel");
+            return launch_span_lengths(offsets, counts, n_rows, rf, lengths_out, status, st);
         }
     }
     if (COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
@@ -490,11 +517,6 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (value < 0) return fail(DNATOK_ERR_INVALID, "bad option value");
     if (!strcmp(name, "host_chunk_bytes")) { g_host_chunk_bytes = value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_force_segments")) { g_kmer_force_segments = value ? 1 : 0; return DNATOK_OK; }
-    if (!strcmp(name, "kmer_segment_windows")) {
-        if (value < 64 || value > (1 << 24) || (value & 63)) return fail(DNATOK_ERR_INVALID, "kmer_segment_windows must be a multiple of 64 in 64..2^24");
-        g_kmer_segment_windows = value;
-        return DNATOK_OK;
-    }
     if (!strcmp(name, "host_chunk_threshold")) { g_host_chunk_threshold = value; return DNATOK_OK; }
     return fail(DNATOK_ERR_INVALID, "unknown option %s", name);
 }
@@ -620,7 +642,7 @@ int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_of
             return launch_span_lengths(d_offsets, nullptr, n_rows, rf, d_lengths, d_status, st);
         case DNATOK_KIND_KMER:
             return launch_kmer<true>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, 64, nullptr, nullptr, nullptr, d_lengths,
-                                     nullptr, d_status, nullptr, 0, st);
+                                     nullptr, d_status, d_scratch, scratch_bytes, st);
         default: {
             if (int rc = run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, st))
                 return rc;

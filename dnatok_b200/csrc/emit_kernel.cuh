@@ -16,18 +16,19 @@ __device__ __forceinline__ int32_t emit_load(const SrcT* __restrict__ p, const i
 }
 
 constexpr int EMIT_WARPS = EMIT_THREADS / 32;
-constexpr int EMIT_SPAN = 512;           // output columns one warp produces per trip
+constexpr int EMIT_SPAN = 512;           // output columns one warp produces per trip ...
+constexpr int EMIT_SPAN_WIDE = 1024;     // ... and for 32-bit ids on long rows, where a trip of 512 stores too little
 
 // Padded output [n_rows, out_stride].  counts == nullptr: a row's content is its byte span.
 //
-// A warp takes 512 consecutive columns of one row.  The source elements under those columns are
+// A warp takes SPAN consecutive columns of one row.  The source elements under those columns are
 // fetched as aligned 16-byte chunks (one or two per lane) into a per-warp shared-memory window,
 // whatever the row's byte alignment and the one-column shift a leading special token causes; each
 // lane then reads the N = 16/sizeof(IdT) elements of its output vector back as aligned words plus a
 // funnel shift, maps them (LUT or identity) and issues one 16-byte store, so both the global loads
 // and the global stores of a warp are contiguous.  Vectors that touch a special token, the
 // truncation point or the padding take a per-column route.
-template <typename SrcT, typename IdT, bool USE_LUT>
+template <typename SrcT, typename IdT, bool USE_LUT, int SPAN>
 __global__ void __launch_bounds__(EMIT_THREADS)
 emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src_begin,
                    const uint8_t* __restrict__ src_end, const int64_t* __restrict__ offsets,
@@ -37,7 +38,7 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
                    int32_t* __restrict__ status, int64_t spans_per_row, int64_t n_spans) {
     constexpr int N = Vec16<IdT>::N;
     constexpr int SZ = (int)sizeof(SrcT);
-    constexpr int CHUNKS = EMIT_SPAN * SZ / 16 + 1;          // 16-byte chunks covering a span at any alignment
+    constexpr int CHUNKS = SPAN * SZ / 16 + 1;               // 16-byte chunks covering a span at any alignment
     constexpr int VB = N * SZ;                                // source bytes under one output vector: 2, 4 or 8
     __shared__ int32_t s_lut[256];
     __shared__ uint4 s_win[EMIT_WARPS][CHUNKS + 1];
@@ -56,7 +57,7 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
     struct Span {
         int64_t row, cs, n, T, shift, t_lo;
         const uint8_t* wbase;
-        int ncol, a;
+        int ncol, a, need;                                    // need: window chunks that hold content of this span
         bool any_content;
     };
     auto describe = [&](int64_t span) {
@@ -64,10 +65,10 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
         if (small) {
             const uint32_t r32 = (uint32_t)span / (uint32_t)spans_per_row;
             p.row = r32;
-            p.cs = (int64_t)((uint32_t)span - r32 * (uint32_t)spans_per_row) * EMIT_SPAN;
+            p.cs = (int64_t)((uint32_t)span - r32 * (uint32_t)spans_per_row) * SPAN;
         } else {
             p.row = span / spans_per_row;
-            p.cs = (span - p.row * spans_per_row) * EMIT_SPAN;
+            p.cs = (span - p.row * spans_per_row) * SPAN;
         }
         const int64_t off = offsets[p.row];
         const int64_t n_in = counts ? (int64_t)counts[p.row] : offsets[p.row + 1] - off;
@@ -78,12 +79,17 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
             if (lengths_out) lengths_out[p.row] = (int32_t)p.T;
             if (status && f.clip_is_error && n_in > p.n) atomicOr(status + p.row, 4);
         }
-        p.ncol = (int)(stride - p.cs < EMIT_SPAN ? stride - p.cs : EMIT_SPAN);
+        p.ncol = (int)(stride - p.cs < SPAN ? stride - p.cs : SPAN);
         p.t_lo = p.cs - (p.shift + (has_cls ? 1 : 0));        // content index under the span's first column
         const uint8_t* wptr = reinterpret_cast<const uint8_t*>(src + off) + p.t_lo * SZ;
         p.a = (int)(reinterpret_cast<uintptr_t>(wptr) & 15);
         p.wbase = wptr - p.a;
         p.any_content = p.t_lo + p.ncol > 0 && p.t_lo < p.n;  // else the span is specials and padding only
+        {
+            // content columns of the span end at min(t_lo + ncol, n); chunks past them are not fetched
+            const int64_t t_hi = p.t_lo + p.ncol < p.n ? p.t_lo + p.ncol : p.n;
+            p.need = p.any_content ? (int)((p.a + (t_hi - p.t_lo) * SZ + 15) >> 4) + 1 : 0;
+        }
         return p;
     };
     // the span's source window as aligned 16-byte chunks, into registers
@@ -92,7 +98,7 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
         for (int q = 0; q < R; ++q) {
             const int k = lane + 32 * q;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (p.any_content && k < CHUNKS) {
+            if (k < p.need && k < CHUNKS) {
                 const uint8_t* g = p.wbase + 16 * k;
                 if (g >= src_begin && g + 16 <= src_end) v = __ldg(reinterpret_cast<const uint4*>(g));
                 else {

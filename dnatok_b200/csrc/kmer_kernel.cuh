@@ -189,7 +189,6 @@ namespace dnatok {
 
 constexpr int KW_WARPS = 8;
 constexpr int KW_BLOCKS_PER_SM = 6;     // row-per-warp encoder: 65,536 / (6 * 256) registers, i.e. 40 per thread
-constexpr int KSEG_BLOCKS_PER_SM = 5;   // segment encoder (it also holds the next ticket's row bounds): 48 per thread
 
 // 2-bit codes of four ASCII bytes at once (A C G T -> 0 1 2 3 in each byte's low bits), and a word
 // that is zero exactly in the bytes that are one of A, C, G, T.
@@ -210,33 +209,21 @@ template <typename IdT> struct IdPair;
 template <> struct IdPair<int64_t> { using type = longlong2; };
 template <> struct IdPair<int32_t> { using type = int2; };
 
-// Token counts only (the sizing pass for 'longest' padding and for ragged output): one warp per row,
-// same window decoding as the encoder, no stores except lengths_out.
+// Tokens of windows [w_begin, w_end) of one row, counted by one warp with the encoder's window
+// decoding and no stores; counting stops once `stop_at` tokens are reached.  *done tells whether the
+// whole range was looked at.
 template <int K>
-__global__ void __launch_bounds__(KW_WARPS * 32)
-kmer_warp_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
-                       int64_t total_bytes, RowFormat f, int32_t* __restrict__ lengths_out,
-                       int32_t* __restrict__ status) {
+__device__ __forceinline__ int kmer_count_windows(const uint8_t* __restrict__ src, int len, int64_t room_total, int lane,
+                                                  int w_begin, int w_end, int stop_at, bool* done) {
     constexpr int NW = (2 * K + 3 + 3) / 4;
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
-    if (row >= n_rows) return;
-    const int n_special = (f.cls_id >= 0 ? 1 : 0) + (f.sep_id >= 0 ? 1 : 0);
-    const int64_t off = offsets[row];
-    const int64_t len64 = offsets[row + 1] - off;
-    const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);
-    const int n_win = (len + K - 1) / K;
     const int n_full = len / K;
-    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
-    const uint8_t* src = bytes + off;
-    const int64_t room_total = total_bytes - off;
-    const int n_chunks = (n_win + 63) >> 6;
-    int base = 0, chunk = 0;
-    for (; chunk < n_chunks && base < cap; ++chunk) {
-        const int wa = chunk * 64 + 2 * lane;
+    int total = 0, w0 = w_begin;
+    for (; w0 < w_end && total < stop_at; w0 += 64) {
+        const int wa = w0 + 2 * lane;
+        const int lim = w0 + 64 < w_end ? w0 + 64 : w_end;
         const int p = wa * K;
         int cnt = 0;
-        if (wa + 2 <= n_full && (int64_t)p + 2 * K + 8 <= room_total) {
+        if (wa + 2 <= lim && wa + 2 <= n_full && (int64_t)p + 2 * K + 8 <= room_total) {
             const uint8_t* g = src + p;
             const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;
             const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
@@ -261,20 +248,67 @@ kmer_warp_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restr
             }
             cnt = (dA == 0 ? 1 : K) + (dB == 0 ? 1 : K);
         } else {
-            int have = len - p;
-            have = have < 0 ? 0 : (have > 2 * K ? 2 * K : have);
-            const int lenA = have < K ? have : K, lenB = have - lenA;
+            int lenA = 0, lenB = 0;
+            if (wa < lim) { const int h = len - p; lenA = h < K ? h : K; }
+            if (wa + 1 < lim) { const int h = len - p - K; lenB = h < K ? h : K; }
             bool okA = lenA == K, okB = lenB == K;
             for (int i = 0; i < lenA; ++i) okA &= kmer_code(__ldg(src + p + i)) < 4;
             for (int i = 0; i < lenB; ++i) okB &= kmer_code(__ldg(src + p + K + i)) < 4;
             cnt = (lenA == 0 ? 0 : (okA ? 1 : lenA)) + (lenB == 0 ? 0 : (okB ? 1 : lenB));
         }
-        base += __reduce_add_sync(0xffffffffu, cnt);
+        total += __reduce_add_sync(0xffffffffu, cnt);
     }
+    *done = w0 >= w_end;
+    return total;
+}
+
+// Token counts only (the sizing pass for 'longest' padding and for ragged output): one warp per row.
+template <int K>
+__global__ void __launch_bounds__(KW_WARPS * 32)
+kmer_warp_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                       int64_t total_bytes, RowFormat f, int32_t* __restrict__ lengths_out,
+                       int32_t* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int n_special = (f.cls_id >= 0 ? 1 : 0) + (f.sep_id >= 0 ? 1 : 0);
+    const int64_t off = offsets[row];
+    const int64_t len64 = offsets[row + 1] - off;
+    const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);
+    const int n_win = (len + K - 1) / K;
+    const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
+    bool done;
+    const int base = kmer_count_windows<K>(bytes + off, len, total_bytes - off, lane, 0, n_win, cap, &done);
     if (lane == 0) {
         const int n = base < cap ? base : cap;
         lengths_out[row] = n + n_special;
-        if (status && f.clip_is_error && (base > cap || chunk < n_chunks)) atomicOr(status + row, 4);
+        if (status && f.clip_is_error && (base > cap || !done)) atomicOr(status + row, 4);
+    }
+}
+
+// The same count for batches of few or very long rows: every warp counts segments of KSEG_WINDOWS
+// windows (ticket t = segment t / n_rows of row t % n_rows, the last segment index without upper
+// bound) and adds them to counts[row], which the caller zeroed and turns into lengths afterwards.
+template <int K>
+__global__ void __launch_bounds__(KW_WARPS * 32)
+kmer_seg_count_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                      int64_t total_bytes, int n_seg, int seg_windows, int32_t* __restrict__ counts) {
+    const int lane = threadIdx.x & 31;
+    const int64_t n_tickets = n_rows * (int64_t)n_seg;
+    const int64_t n_warps = (int64_t)gridDim.x * KW_WARPS;
+    for (int64_t t = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5); t < n_tickets; t += n_warps) {
+        const int seg = (int)(t / n_rows);
+        const int64_t row = t - (int64_t)seg * n_rows;
+        const int64_t off = offsets[row];
+        const int64_t len64 = offsets[row + 1] - off;
+        const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);
+        const int n_win = (len + K - 1) / K;
+        const int64_t w0 = (int64_t)seg * seg_windows;
+        if (w0 >= n_win) continue;
+        const int w_end = (seg == n_seg - 1 || w0 + seg_windows >= n_win) ? n_win : (int)w0 + seg_windows;
+        bool done;
+        const int cnt = kmer_count_windows<K>(bytes + off, len, total_bytes - off, lane, (int)w0, w_end, 0x7fffffff, &done);
+        if (lane == 0 && cnt) atomicAdd(counts + row, cnt);
     }
 }
 
@@ -580,21 +614,28 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
     kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
 }
 
-// Rows cut into segments of seg_windows windows (an even number) and dealt round-robin to a grid of resident warps:
-// ticket t stands for segment t / n_rows of row t % n_rows, warp g of G takes tickets g, g + G, ...,
-// so all first segments are under way before any second segment.  A segment needs the number of
-// tokens its predecessors produced: each warp publishes that count (+1, 0 = not yet) in
-// flags[segment * n_rows + row] when it is done, and the warp holding the next segment of the row
-// polls it.  The grid never exceeds what the GPU keeps resident and every warp takes its tickets in
-// rising order, so the holder of an earlier ticket waits only on still earlier ones and the polls
-// end; they are bounded all the same, and a row whose wait ran out is reported with
-// DNATOK_ROW_STALLED instead of tokens.
-// Segment boundaries sit where the output offset is even when every earlier window was a clean
-// k-mer, so a segment starts on a 16-byte boundary in the common case.  The last segment index has
-// no upper bound: rows longer than n_seg * seg_windows windows finish inside it.
-constexpr int KSEG_WINDOWS = 256;
+// Rows cut into segments of KSEG_WINDOWS windows, dealt round-robin to a grid of resident warps:
+// ticket t stands for segment t / n_rows of row t % n_rows, warp g of G takes tickets g, g + G, ...
+// (a shared ticket counter was tried: one atomic per segment caps the rate near 400 M segments/s).
+// A segment's place in the output depends on the tokens all earlier segments of its row produce
+// (a window with an N yields K tokens, not one), which is settled by a decoupled look-back:
+//   1. the warp loads and decodes its 256 windows into registers and counts their tokens;
+//   2. it publishes that count in flags[segment * n_rows + row] as an "own" value;
+//   3. it sums the "own" values of the segments before it, 32 per step, back to the nearest one that
+//      already published a "total" (its own count plus everything before it) or to the row start;
+//   4. it publishes its "total" and stores its tokens.
+// Nothing is awaited before step 2, so the segments of one row run in parallel, and step 3 only
+// waits for flags of earlier tickets, whose holders are running warps (the grid never exceeds what
+// the GPU keeps resident, and every warp takes its tickets in rising order) that reach their own
+// step 2 without waiting for anybody.  The waits are bounded
+// all the same: a row whose wait ran out is reported with DNATOK_ROW_STALLED instead of tokens.
+// The last segment of a row (short windows, the len % K tail) and segments that hold anything but
+// clean k-mers place their tokens through kmer_encode_windows; clean ones store straight from
+// registers, as 16-byte pairs whatever the parity of their output offset.
+constexpr int KSEG_WINDOWS = 256;        // four chunks of 64 windows
+constexpr int KSEG_BLOCKS_PER_SM = 4;    // 64 registers per thread: the decoded segment stays in registers
 constexpr int KSEG_POLL_LIMIT = 1 << 20;
-constexpr int KSEG_POISON = 0x7fffffff;
+constexpr uint32_t KSEG_OWN = 1u << 30, KSEG_TOTAL = 2u << 30, KSEG_POISON = 3u << 30, KSEG_VALUE = (1u << 30) - 1u;
 
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
 __global__ void __launch_bounds__(KW_WARPS * 32, KSEG_BLOCKS_PER_SM)
@@ -603,14 +644,18 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
                      const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
                      void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
                      int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
-                     int32_t* __restrict__ status, int n_seg, int seg_windows, int* __restrict__ flags) {
+                     int32_t* __restrict__ status, int n_seg, uint32_t* __restrict__ flags) {
+    constexpr int NW = (2 * K + 3 + 3) / 4;
+    constexpr uint32_t IDX_MASK = (1u << (2 * K)) - 1u;
+    constexpr int NCH = KSEG_WINDOWS / 64;
+    using Pair = typename IdPair<IdT>::type;
     const int lane = threadIdx.x & 31;
     const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
     const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
     const int64_t n_tickets = n_rows * (int64_t)n_seg;
     const int64_t n_warps = (int64_t)gridDim.x * KW_WARPS;
     // (segment, row) of the ticket after this warp's current one, kept in step without dividing; its
-    // row bounds and its predecessor's flag are fetched while the current ticket is being worked on
+    // row bounds are fetched while the current ticket is being worked on
     const int64_t t0 = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
     if (t0 >= n_tickets) return;
     int seg2 = (int)(t0 / n_rows);
@@ -618,60 +663,165 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
     const int step_seg = (int)(n_warps / n_rows);
     const int64_t step_row = n_warps - (int64_t)step_seg * n_rows;
     int64_t off2 = offsets[row2], end2 = offsets[row2 + 1];
-    int flag2 = seg2 > 0 ? *(const volatile int*)(flags + (int64_t)(seg2 - 1) * n_rows + row2) : 0;
     for (int64_t t = t0; t < n_tickets; t += n_warps) {
         const int seg = seg2;
         const int64_t row = row2, off = off2, end = end2;
-        const int flag_seen = flag2;
         seg2 += step_seg;
         row2 += step_row;
         if (row2 >= n_rows) { row2 -= n_rows; ++seg2; }
-        if (t + n_warps < n_tickets) {
-            off2 = offsets[row2];
-            end2 = offsets[row2 + 1];
-            flag2 = seg2 > 0 ? *(const volatile int*)(flags + (int64_t)(seg2 - 1) * n_rows + row2) : 0;
-        }
+        if (t + n_warps < n_tickets) { off2 = offsets[row2]; end2 = offsets[row2 + 1]; }
+
         const KmerRow<IdT> r = kmer_row_setup<IdT, K>(bytes, off, end, row, total_bytes, f, ids, lengths_in, out_offsets);
-        // boundary of segment s >= 1: s * seg_windows (+1 when the first content column has an odd offset)
-        const int odd = (int)((reinterpret_cast<uintptr_t>(r.dst) / sizeof(IdT)) & 1u);
-        const int64_t w0 = seg == 0 ? 0 : (int64_t)seg * seg_windows + odd;
+        const int64_t w0 = (int64_t)seg * KSEG_WINDOWS;
         if (seg > 0 && w0 >= r.n_win) continue;                                  // the row ended in an earlier segment
-        const int64_t w1 = (int64_t)(seg + 1) * seg_windows + odd;
-        const bool last = seg == n_seg - 1 || w1 >= r.n_win;
-        const int w_end = last ? r.n_win : (int)w1;
-        int base = 0;
-        if (seg > 0) {
-            const volatile int* fl = flags + (int64_t)(seg - 1) * n_rows + row;
-            int v = flag_seen;
-            if (lane == 0 && v == 0) {
-                int polls = 0;
-                while ((v = *fl) == 0) {
-                    if (++polls > KSEG_POLL_LIMIT) { v = KSEG_POISON; break; }
-                    __nanosleep(100);
-                }
-            }
-            v = __shfl_sync(0xffffffffu, v, 0);
-            if (v == KSEG_POISON) {
-                if (lane == 0) {
-                    if (status) atomicOr(status + row, 16);
-                    if (!last) { flags[(int64_t)seg * n_rows + row] = KSEG_POISON; }
-                    else if (lengths_out) lengths_out[row] = 0;
-                }
-                continue;
-            }
-            base = v - 1;
-        }
-        bool clipped = false;
-        base = kmer_encode_windows<IdT, K, AFFINE, FUSE_MASK>(r, cap, kmer_ids, affine_base, single_ids, mdelta, lane,
-                                                              (int)w0, w_end, base, &clipped);
+        const bool last = seg == n_seg - 1 || w0 + KSEG_WINDOWS >= r.n_win;
+        const int w_end = last ? r.n_win : (int)w0 + KSEG_WINDOWS;
+        uint32_t* my_flag = flags + (int64_t)seg * n_rows + row;
+
+        // the flags of the 32 segments before this one: asked for now, looked at after the decode
+        uint32_t look = KSEG_TOTAL;                                              // before the row start: a total of 0
+        if (seg - 1 - lane >= 0) look = *(const volatile uint32_t*)(flags + (int64_t)(seg - 1 - lane) * n_rows + row);
+
+        // ---- 1. decode and count (segments that are not the last of their row hold complete windows only)
+        int count = 0;
+        bool in_regs = false, clean = false;
+        uint32_t packed[NCH];                                                    // idxA | idxB << 16 per chunk
         if (!last) {
-            if (lane == 0) {
-                if (status && f.clip_is_error && clipped) atomicOr(status + row, 4);
-                // the count travels in the flag itself and nobody reads this warp's tokens: no fence
-                *(volatile int*)(flags + (int64_t)seg * n_rows + row) = base + 1;
+            int64_t fit = (r.room_total - 8) / K;                                // windows whose aligned words stay in the buffer
+            if (w0 + KSEG_WINDOWS <= fit) {
+                in_regs = true;
+                const uint8_t* g = r.src + ((int)w0 + 2 * lane) * K;
+                const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;
+                const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
+                uint32_t wd[NCH][NW];
+#pragma unroll
+                for (int c = 0; c < NCH; ++c)
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) wd[c][i] = __ldg(gw + c * 16 * K + i);
+                int n_dirty = 0;
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    uint32_t P = 0, dA = 0, dB = 0;
+#pragma unroll
+                    for (int i = 0; i < NW - 1; ++i) {
+                        const uint32_t rr = __funnelshift_r(wd[c][i], wd[c][i + 1], sh);
+                        uint32_t cc, d;
+                        acgt_codes4(rr, &cc, &d);
+                        P |= pack_codes4(cc) << (24 - 8 * i);
+                        uint32_t mA = 0, mB = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const int pos = 4 * i + b;
+                            if (pos < K) mA |= 0xFFu << (8 * b);
+                            else if (pos < 2 * K) mB |= 0xFFu << (8 * b);
+                        }
+                        dA |= d & mA;
+                        dB |= d & mB;
+                    }
+                    packed[c] = ((P >> (32 - 2 * K)) & IDX_MASK) | (((P >> (32 - 4 * K)) & IDX_MASK) << 16);
+                    n_dirty += __popc(__ballot_sync(0xffffffffu, dA != 0)) + __popc(__ballot_sync(0xffffffffu, dB != 0));
+                }
+                clean = n_dirty == 0;
+                count = KSEG_WINDOWS + (K - 1) * n_dirty;
+            } else {
+                // the end of the input buffer is too close for aligned word loads: count byte by byte
+                int cnt = 0;
+                for (int w = (int)w0 + lane; w < w_end; w += 32) {
+                    bool ok = true;
+                    for (int i = 0; i < K; ++i) ok &= kmer_code(__ldg(r.src + w * K + i)) < 4;
+                    cnt += ok ? 1 : K;
+                }
+                count = __reduce_add_sync(0xffffffffu, cnt);
             }
+            // ---- 2. publish the own count (segment 0 knows its total already)
+            if (lane == 0) *(volatile uint32_t*)my_flag = (seg == 0 ? KSEG_TOTAL : KSEG_OWN) | (uint32_t)count;
+        }
+
+        // ---- 3. tokens before this segment
+        int base = 0;
+        bool stalled = false;
+        if (seg > 0) {
+            int behind = seg - 1;                                                // segment lane 0 looks at
+            int polls = 0;
+            uint32_t sum = 0;
+            for (;;) {
+                const uint32_t st = look >> 30;
+                const unsigned totals = __ballot_sync(0xffffffffu, st == 2u);
+                const unsigned empties = __ballot_sync(0xffffffffu, st == 0u);
+                if (__any_sync(0xffffffffu, st == 3u)) { stalled = true; break; }
+                const int first_total = totals ? __ffs(totals) - 1 : 32;
+                const unsigned wanted = first_total >= 31 ? 0xffffffffu : ((2u << first_total) - 1u);
+                if (empties & wanted) {
+                    if (++polls > KSEG_POLL_LIMIT) { stalled = true; break; }
+                    __nanosleep(64);
+                } else {
+                    sum += __reduce_add_sync(0xffffffffu, lane <= first_total ? (look & KSEG_VALUE) : 0u);
+                    if (first_total < 32) break;
+                    behind -= 32;
+                }
+                look = KSEG_TOTAL;
+                if (behind - lane >= 0) look = *(const volatile uint32_t*)(flags + (int64_t)(behind - lane) * n_rows + row);
+            }
+            base = (int)sum;
+        }
+        if (stalled) {
+            if (lane == 0) {
+                if (status) atomicOr(status + row, 16);
+                if (!last) *(volatile uint32_t*)my_flag = KSEG_POISON;
+                else if (lengths_out) lengths_out[row] = 0;
+            }
+            continue;
+        }
+        // ---- 4. publish the total, place the tokens
+        if (!last && seg > 0 && lane == 0) *(volatile uint32_t*)my_flag = KSEG_TOTAL | (uint32_t)(base + count);
+
+        if (in_regs && clean && base + KSEG_WINDOWS <= cap) {
+            IdT* d = r.dst + base;
+            Pair one; one.x = 1; one.y = 1;
+            if ((reinterpret_cast<uintptr_t>(d) % (2 * sizeof(IdT))) == 0) {
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    const uint32_t a = packed[c] & 0xFFFFu, b = packed[c] >> 16;
+                    Pair v;
+                    v.x = (IdT)(AFFINE ? affine_base + (int32_t)a : __ldg(kmer_ids + a));
+                    v.y = (IdT)(AFFINE ? affine_base + (int32_t)b : __ldg(kmer_ids + b));
+                    *reinterpret_cast<Pair*>(d + 64 * c + 2 * lane) = v;
+                    if (FUSE_MASK) *reinterpret_cast<Pair*>(d + mdelta + 64 * c + 2 * lane) = one;
+                }
+            } else {
+                // odd offset: the aligned pairs are (second window of this lane, first window of the next
+                // lane); the segment's first and last token go out alone
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    const uint32_t a = packed[c] & 0xFFFFu, b = packed[c] >> 16;
+                    uint32_t a_next = __shfl_down_sync(0xffffffffu, a, 1);
+                    const uint32_t a_chunk = c + 1 < NCH ? __shfl_sync(0xffffffffu, packed[c + 1 < NCH ? c + 1 : c] & 0xFFFFu, 0) : 0u;
+                    if (lane == 31) a_next = a_chunk;
+                    const IdT vb = (IdT)(AFFINE ? affine_base + (int32_t)b : __ldg(kmer_ids + b));
+                    IdT* q = d + 64 * c + 2 * lane + 1;
+                    if (c + 1 < NCH || lane < 31) {
+                        Pair v;
+                        v.x = vb;
+                        v.y = (IdT)(AFFINE ? affine_base + (int32_t)a_next : __ldg(kmer_ids + a_next));
+                        *reinterpret_cast<Pair*>(q) = v;
+                        if (FUSE_MASK) *reinterpret_cast<Pair*>(q + mdelta) = one;
+                    } else {
+                        *q = vb;
+                        if (FUSE_MASK) q[mdelta] = 1;
+                    }
+                    if (c == 0 && lane == 0) {
+                        d[0] = (IdT)(AFFINE ? affine_base + (int32_t)a : __ldg(kmer_ids + a));
+                        if (FUSE_MASK) d[mdelta] = 1;
+                    }
+                }
+            }
+            base += KSEG_WINDOWS;
         } else {
-            kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
+            bool clipped = false;
+            base = kmer_encode_windows<IdT, K, AFFINE, FUSE_MASK>(r, cap, kmer_ids, affine_base, single_ids, mdelta, lane,
+                                                                  (int)w0, w_end, base, &clipped);
+            if (last) kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
+            else if (lane == 0 && status && f.clip_is_error && clipped) atomicOr(status + row, 4);
         }
     }
 }

@@ -200,7 +200,6 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
  *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)
  *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB)
- *   "kmer_segment_windows"  windows per k-mer row segment, a multiple of 64 (default 256)
  *   "kmer_force_segments"   1: use the k-mer segment encoder whenever scratch is given, whatever the batch shape
  *   "bpe_block_team_rows"   BPE batches of at most this many rows give every word a whole thread block
  *                           instead of one warp (lower latency when the batch cannot fill the GPU);
