@@ -324,6 +324,10 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    cores, all_cores = None, os.sched_getaffinity(0)
+    if not args.no_affinity:
+        from dnatok_b200.shard import bind_host_to_gpu
+        cores = bind_host_to_gpu(local)          # before any pinned buffer is allocated
     barrier = None
     if world > 1:
         import torch.distributed as dist
@@ -349,6 +353,7 @@ def run_ours(args):
         e2e_s, h2d, d2h = float("nan"), 0, 0
     else:
         e2e_s, h2d, d2h = time_e2e(tok, flat, offsets, call, max(3, min(args.steps, 10)), 2)
+    os.sched_setaffinity(0, all_cores)           # the CPU baseline below may use every core again
 
     t = torch.tensor([total_ms, e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -376,7 +381,8 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": abytes, "kernel_ms": round(kernel_ms, 5)},
         "e2e": {"value": round(world * total_bp / e2e_s / 1e6, 1), "unit": "Mbp/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "path": "dnatok_encode_host, pinned host buffers"},
+                "path": "dnatok_encode_host, pinned host buffers",
+                "host_cores": ("%d cores next to the GPU" % len(cores)) if cores else "as given"},
         "gpu_launches": int(launches), "clocks": clk.summary(),
     }
     if args.kernel_only:
@@ -606,6 +612,8 @@ def main():
     ap.add_argument("--workload", default="kmer6", choices=["kmer6", "char", "byte", "bpe4k", "bpe32k"])
     ap.add_argument("--scale", type=int, default=0, help="batch multiplier over the literal shape (0: default)")
     ap.add_argument("--no-extra", action="store_true", help="skip the per_config section")
+    ap.add_argument("--no-affinity", action="store_true",
+                    help="leave the process on whatever cores it has instead of those next to its GPU")
     ap.add_argument("--kmer-no-scratch", action="store_true",
                     help="k-mer without scratch memory: one warp per row instead of queued row segments")
     ap.add_argument("--kmer-force-segments", action="store_true",

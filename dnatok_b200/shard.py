@@ -92,3 +92,30 @@ def gather_padded(ids, n_rows_per_rank: List[int], width: int, pad_id: int, dst:
         return torch.cat([bucket[r][:n_rows_per_rank[r]] for r in range(world)], dim=0)
     dist.gather(buf, None, dst=dst, group=group)
     return None
+
+
+def bind_host_to_gpu(device_index: int):
+    """Pin the calling process to the CPU cores next to GPU ``device_index`` (NVML's ideal CPU
+    affinity), so that the pinned host buffers it allocates afterwards land on the NUMA node the
+    GPU's PCIe link hangs off.  With one process per GPU this keeps each rank's host<->device copies
+    off the inter-socket link.  Returns the list of cores the process is bound to, or None when
+    NVML is missing, reports nothing, or none of its cores is allowed to this process (cgroup)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            h = pynvml.nvmlDeviceGetHandleByIndex(int(device_index))
+            n_words = (os.cpu_count() + 63) // 64
+            words = pynvml.nvmlDeviceGetCpuAffinity(h, n_words)
+        finally:
+            pynvml.nvmlShutdown()
+    except Exception:
+        return None
+    ideal = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+    allowed = os.sched_getaffinity(0)
+    cores = sorted(ideal & allowed)
+    if not cores or len(cores) == len(allowed):
+        return cores or None
+    os.sched_setaffinity(0, cores)
+    return cores

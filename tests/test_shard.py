@@ -86,3 +86,15 @@ def test_two_rank_shard_and_gather_gloo():
         p.join(120)
         assert p.exitcode == 0
     assert q.get(timeout=5) is True
+
+
+def test_bind_host_to_gpu_is_harmless_without_nvml():
+    """On a machine without a GPU driver the binding helper reports None and leaves the affinity alone."""
+    import os
+    from dnatok_b200.shard import bind_host_to_gpu
+    before = os.sched_getaffinity(0)
+    got = bind_host_to_gpu(0)
+    assert got is None or set(got) <= before
+    if got is None:
+        assert os.sched_getaffinity(0) == before
+    os.sched_setaffinity(0, before)
