@@ -382,7 +382,8 @@ def run_ours(args):
         "e2e": {"value": round(world * total_bp / e2e_s / 1e6, 1), "unit": "Mbp/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "path": "dnatok_encode_host, pinned host buffers",
-                "host_cores": ("%d cores next to the GPU" % len(cores)) if cores else "as given"},
+                "host_cores": "as given" if not cores or len(cores) == len(all_cores)
+                else "%d of %d, those next to the GPU" % (len(cores), len(all_cores))},
         "gpu_launches": int(launches), "clocks": clk.summary(),
     }
     if args.kernel_only:
