@@ -41,7 +41,11 @@ namespace dnatok {
 
 constexpr uint32_t BPE_NONE = 0xFFFFu;          // no rank
 constexpr int BPE_N_CLASSES = 9;
-constexpr int BPE_BLOCK_WARPS = 8;              // warps per block; a block holds 8 / W words
+constexpr int BPE_BLOCK_WARPS = 8;              // largest team: a whole block of 8 warps on one word
+// Warps per block for teams of W warps.  One-warp teams sit 16 to a block: the block's fixed shared
+// memory (pair table, reduction slots) is then paid three times per SM instead of five and 48 warps
+// fit where 40 did.
+__host__ __device__ constexpr int bpe_block_warps(int W) { return W == 1 ? 16 : BPE_BLOCK_WARPS; }
 
 __host__ __device__ constexpr int bpe_class_capacity(int c) {
     return c < 8 ? (256 << c) : 49152;          // 256 ... 32768, 49152
@@ -129,18 +133,19 @@ __device__ __forceinline__ void team_sync(int team) {
 
 // C: capacity in positions; W: warps per word.
 template <int C, int W>
-__global__ void __launch_bounds__(BPE_BLOCK_WARPS * 32)
+__global__ void __launch_bounds__(bpe_block_warps(W) * 32)
 bpe_rounds_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
                   const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
                   int32_t* __restrict__ work_counter, BpeDeviceTable t,
                   uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
                   int32_t* __restrict__ status) {
-    constexpr int TEAMS = BPE_BLOCK_WARPS / W;
+    constexpr int BW = bpe_block_warps(W);
+    constexpr int TEAMS = BW / W;
     constexpr int G = C / 32;
     extern __shared__ uint4 bpe_dyn[];
-    __shared__ uint32_t s_red[BPE_BLOCK_WARPS][2];            // per-warp partial minima
+    __shared__ uint32_t s_red[BW][2];            // per-warp partial minima
     __shared__ uint32_t s_hot[32 * 32];                       // direct table for pairs of small ids
-    for (int i = threadIdx.x; i < 32 * 32; i += BPE_BLOCK_WARPS * 32) s_hot[i] = __ldg(t.hot + i);
+    for (int i = threadIdx.x; i < 32 * 32; i += BW * 32) s_hot[i] = __ldg(t.hot + i);
     __syncthreads();
     __shared__ int32_t s_word[TEAMS][2];                      // claimed word index, new length
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

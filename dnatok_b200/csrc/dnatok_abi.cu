@@ -204,7 +204,8 @@ template <int CLS, int W>
 int launch_bpe_team(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
                     int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
     constexpr int C = bpe_class_capacity(CLS);
-    constexpr int TEAMS = BPE_BLOCK_WARPS / W;                 // words in flight per block
+    constexpr int BW = bpe_block_warps(W);
+    constexpr int TEAMS = BW / W;                              // words in flight per block
     const size_t smem = (size_t)TEAMS * bpe_slot_bytes(C);
     static std::mutex mu;
     static std::map<int, int> blocks_per_sm;         // device -> resident blocks (also marks the attribute as set)
@@ -216,7 +217,7 @@ int launch_bpe_team(const DeviceTables& d, const BpeDeviceTable& t, const uint8_
         auto it = blocks_per_sm.find(dev);
         if (it == blocks_per_sm.end()) {
             CUDA_TRY(cudaFuncSetAttribute(bpe_rounds_kernel<C, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_rounds_kernel<C, W>, BPE_BLOCK_WARPS * 32, smem));
+            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_rounds_kernel<C, W>, BW * 32, smem));
             if (bps < 1) bps = 1;
             blocks_per_sm[dev] = bps;
         } else bps = it->second;
@@ -226,7 +227,7 @@ int launch_bpe_team(const DeviceTables& d, const BpeDeviceTable& t, const uint8_
     const int64_t need = (n_rows + TEAMS - 1) / TEAMS;
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
-    bpe_rounds_kernel<C, W><<<(unsigned)grid, BPE_BLOCK_WARPS * 32, smem, st>>>(
+    bpe_rounds_kernel<C, W><<<(unsigned)grid, BW * 32, smem, st>>>(
         bytes, offsets, s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
         s.tokens, s.counts, status);
     LAUNCH_CHECK("bpe_rounds_kernel");
