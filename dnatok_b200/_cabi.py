@@ -21,7 +21,7 @@ EXPORTS = (
     "dnatok_version", "dnatok_last_error", "dnatok_create_char", "dnatok_create_kmer",
     "dnatok_create_bpe", "dnatok_destroy", "dnatok_kind", "dnatok_scratch_bytes",
     "dnatok_max_tokens", "dnatok_prepare", "dnatok_write", "dnatok_encode",
-    "dnatok_scan_lengths", "dnatok_encode_host", "dnatok_launch_count",
+    "dnatok_scan_lengths", "dnatok_encode_host", "dnatok_launch_count", "dnatok_host_copy_bytes",
     "dnatok_encode_bpe_builtin_scratch", "dnatok_set_option", "dnatok_set_row_bytes_hint",
     "dnatok_pack_fasta", "dnatok_embed",
 )
@@ -59,6 +59,8 @@ def lib() -> ctypes.CDLL:
     L.dnatok_version.restype = c_int
     L.dnatok_last_error.restype = c_char_p
     L.dnatok_launch_count.restype = c_int64
+    L.dnatok_host_copy_bytes.restype = None
+    L.dnatok_host_copy_bytes.argtypes = [ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]
     L.dnatok_create_char.argtypes = [p, POINTER(Specials), POINTER(p)]
     L.dnatok_create_kmer.argtypes = [c_int, p, p, POINTER(Specials), POINTER(p)]
     L.dnatok_create_bpe.argtypes = [p, p, p, c_int32, p, POINTER(Specials), POINTER(p)]

@@ -12,6 +12,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "bpe_kernel.cuh"
@@ -26,6 +27,9 @@ namespace {
 
 thread_local std::string g_err;
 std::atomic<int64_t> g_launches{0};
+std::atomic<int64_t> g_host_mask_threads{-1};                 // -1: as many as the host has cores, at most 16; 0: mask copied from the device
+std::atomic<int64_t> g_host_mask_min_bytes{16ll << 20};      // smaller masks are not worth the threads
+thread_local int64_t g_last_h2d = 0, g_last_d2h = 0;          // bytes the last dnatok_encode_host of this thread copied
 std::atomic<int64_t> g_kmer_force_segments{0};                // 1: segment encoder whenever scratch is given
 std::atomic<int64_t> g_host_chunk_bytes{256ll << 20};        // bytes (in + out) per chunk of the host pipeline
 std::atomic<int64_t> g_host_chunk_threshold{4ll << 30};      // batches below this size are not chunked
@@ -74,6 +78,7 @@ struct DeviceTables {
     int64_t* st_out_offsets = nullptr;
     void* st_scratch = nullptr;   size_t st_scratch_cap = 0;
     cudaStream_t stream = nullptr;
+    cudaEvent_t ev_lengths = nullptr;  // marks the arrival of the row lengths in host memory
     // chunked host pipeline: three independent slots (buffers + stream), grow only
     struct PipeSlot {
         cudaStream_t stream = nullptr;
@@ -495,6 +500,52 @@ int launch_span_lengths(const int64_t* offsets, const int32_t* counts, int64_t n
     return 0;
 }
 
+// Attention mask of a padded batch written by host threads from the row lengths the GPU produced:
+// ones on [shift, shift + T) of every row, zeros elsewhere.  The mask is a function of the lengths
+// alone, so a large one is cheaper to make where it is wanted than to carry over the host link.
+template <typename M>
+void fill_mask_rows(M* mask, const int32_t* lengths, int64_t r0, int64_t r1, int64_t stride, bool pad_left) {
+    for (int64_t r = r0; r < r1; ++r) {
+        M* row = mask + r * stride;
+        int64_t T = lengths[r];
+        if (T < 0) T = 0;
+        if (T > stride) T = stride;
+        const int64_t lo = pad_left ? stride - T : 0;
+        for (int64_t j = 0; j < lo; ++j) row[j] = 0;
+        for (int64_t j = lo; j < lo + T; ++j) row[j] = 1;
+        for (int64_t j = lo + T; j < stride; ++j) row[j] = 0;
+    }
+}
+
+// The attention mask of a large padded batch, written by n_threads host workers once the row lengths
+// have arrived, while the ids are still being copied back.
+struct HostMask {
+    int device = 0;
+    void* mask = nullptr; int mask_bits = 0; const int32_t* lengths = nullptr; int64_t n_rows = 0, stride = 0;
+    bool pad_left = false; cudaEvent_t ev_lengths = nullptr;
+};
+
+void host_mask_worker(const HostMask& hm, int t, int n_threads, int* err) {
+    if (cudaSetDevice(hm.device) != cudaSuccess || cudaEventSynchronize(hm.ev_lengths) != cudaSuccess) { *err = 1; return; }
+    const int64_t r0 = hm.n_rows * t / n_threads, r1 = hm.n_rows * (t + 1) / n_threads;
+    if (hm.mask_bits == 64) fill_mask_rows<int64_t>((int64_t*)hm.mask, hm.lengths, r0, r1, hm.stride, hm.pad_left);
+    else if (hm.mask_bits == 32) fill_mask_rows<int32_t>((int32_t*)hm.mask, hm.lengths, r0, r1, hm.stride, hm.pad_left);
+    else fill_mask_rows<uint8_t>((uint8_t*)hm.mask, hm.lengths, r0, r1, hm.stride, hm.pad_left);
+}
+
+int host_mask_fill(const HostMask& hm, int n_threads) {
+    if (n_threads > hm.n_rows) n_threads = (int)hm.n_rows;
+    if (n_threads < 1) n_threads = 1;
+    std::vector<int> errs((size_t)n_threads, 0);
+    std::vector<std::thread> pool;
+    pool.reserve((size_t)n_threads);
+    for (int t = 1; t < n_threads; ++t) pool.emplace_back(host_mask_worker, std::cref(hm), t, n_threads, &errs[(size_t)t]);
+    host_mask_worker(hm, 0, n_threads, &errs[0]);
+    for (auto& th : pool) th.join();
+    for (int e : errs) if (e) return fail(DNATOK_ERR_CUDA, "a host worker could not wait for the row lengths");
+    return 0;
+}
+
 int check_batch(const dnatok_handle* h, const void* bytes, const void* offsets, int64_t n_rows, int64_t total) {
     if (!h) return fail(DNATOK_ERR_INVALID, "handle is NULL");
     if (n_rows < 0 || total < 0) return fail(DNATOK_ERR_INVALID, "negative size");
@@ -511,10 +562,16 @@ extern "C" {
 int dnatok_version(void) { return DNATOK_ABI_VERSION; }
 const char* dnatok_last_error(void) { return g_err.c_str(); }
 int64_t dnatok_launch_count(void) { return g_launches.load(); }
+void dnatok_host_copy_bytes(int64_t* h2d, int64_t* d2h) {
+    if (h2d) *h2d = g_last_h2d;
+    if (d2h) *d2h = g_last_d2h;
+}
 
 int dnatok_set_option(const char* name, int64_t value) {
     if (!name) return fail(DNATOK_ERR_INVALID, "bad option");
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
+    if (!strcmp(name, "host_mask_min_bytes")) { g_host_mask_min_bytes = value < 0 ? 0 : value; return DNATOK_OK; }
+    if (!strcmp(name, "host_mask_threads")) { g_host_mask_threads = value < -1 ? -1 : value; return DNATOK_OK; }
     if (value < 0) return fail(DNATOK_ERR_INVALID, "bad option value");
     if (!strcmp(name, "host_chunk_bytes")) { g_host_chunk_bytes = value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_force_segments")) { g_kmer_force_segments = value ? 1 : 0; return DNATOK_OK; }
@@ -587,6 +644,7 @@ void dnatok_destroy(dnatok_handle* h) {
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);
+        if (d.ev_lengths) cudaEventDestroy(d.ev_lengths);
         for (auto& ps : d.pipe) {
             if (ps.stream) { cudaStreamSynchronize(ps.stream); cudaStreamDestroy(ps.stream); }
             for (void* p : {ps.bytes, ps.offsets, ps.ids, ps.mask, ps.rows, ps.scratch}) if (p) cudaFree(p);
@@ -1052,9 +1110,18 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
     const int64_t out_elems = ragged ? dnatok_max_tokens(h, n_rows, total, fmt) : n_rows * stride;
     if (!ragged && out_elems > ids_capacity) return fail(DNATOK_ERR_CAPACITY, "ids buffer holds %lld elements, %lld needed",
                                                          (long long)ids_capacity, (long long)out_elems);
+    // a large mask of a padded batch is written by host threads while the ids are on their way back
+    int mask_threads = (int)g_host_mask_threads.load();
+    if (mask_threads < 0) {
+        const unsigned hc = std::thread::hardware_concurrency();
+        mask_threads = hc == 0 ? 1 : (hc > 16 ? 16 : (int)hc);
+    }
+    const bool host_mask = mask_sz && h_mask && !ragged && mask_threads > 0 &&
+                           (int64_t)((size_t)out_elems * mask_sz) >= g_host_mask_min_bytes.load();
     if (int rc = grow(&d->st_ids, &d->st_ids_cap, (size_t)out_elems * id_sz + 64)) return rc;
-    if (mask_sz && h_mask) if (int rc = grow(&d->st_mask, &d->st_mask_cap, (size_t)out_elems * mask_sz + 64)) return rc;
-    void* dmask = (mask_sz && h_mask) ? d->st_mask : nullptr;
+    if (mask_sz && h_mask && !host_mask)
+        if (int rc = grow(&d->st_mask, &d->st_mask_cap, (size_t)out_elems * mask_sz + 64)) return rc;
+    void* dmask = (mask_sz && h_mask && !host_mask) ? d->st_mask : nullptr;
     if (!dmask) f.mask_bits = 0;
 
     int rc;
@@ -1078,10 +1145,31 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
         if (h_out_offsets)
             CUDA_TRY(cudaMemcpyAsync(h_out_offsets, d->st_out_offsets, (size_t)(n_rows + 1) * 8, cudaMemcpyDeviceToHost, st));
     }
+    g_last_h2d = total + (n_rows + 1) * 8;
+    g_last_d2h = n_out * (int64_t)id_sz + (ragged && h_out_offsets ? (n_rows + 1) * 8 : 0);
+    if (host_mask && n_rows) {
+        // lengths first (small), then the ids; the mask is filled while the ids are still being copied
+        std::vector<int32_t> tmp;
+        int32_t* hl = h_lengths;
+        if (!hl) { tmp.resize((size_t)n_rows); hl = tmp.data(); }
+        CUDA_TRY(cudaMemcpyAsync(hl, d->st_lengths, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+        if (h_status) CUDA_TRY(cudaMemcpyAsync(h_status, d->st_status, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+        if (!d->ev_lengths) CUDA_TRY(cudaEventCreateWithFlags(&d->ev_lengths, cudaEventDisableTiming));
+        CUDA_TRY(cudaEventRecord(d->ev_lengths, st));
+        if (n_out) CUDA_TRY(cudaMemcpyAsync(h_ids, d->st_ids, (size_t)n_out * id_sz, cudaMemcpyDeviceToHost, st));
+        HostMask hm;
+        hm.device = device; hm.mask = h_mask; hm.mask_bits = fmt->mask_bits; hm.lengths = hl; hm.n_rows = n_rows;
+        hm.stride = stride; hm.pad_left = fmt->pad_left != 0; hm.ev_lengths = d->ev_lengths;
+        if (int rc2 = host_mask_fill(hm, mask_threads)) return rc2;
+        g_last_d2h += n_rows * 4 * (h_status ? 2 : 1);
+        CUDA_TRY(cudaStreamSynchronize(st));
+        if (out_stride_used) *out_stride_used = stride;
+        return DNATOK_OK;
+    }
     if (n_out) CUDA_TRY(cudaMemcpyAsync(h_ids, d->st_ids, (size_t)n_out * id_sz, cudaMemcpyDeviceToHost, st));
-    if (dmask && n_out) CUDA_TRY(cudaMemcpyAsync(h_mask, dmask, (size_t)n_out * mask_sz, cudaMemcpyDeviceToHost, st));
-    if (h_lengths && n_rows) CUDA_TRY(cudaMemcpyAsync(h_lengths, d->st_lengths, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
-    if (h_status && n_rows) CUDA_TRY(cudaMemcpyAsync(h_status, d->st_status, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+    if (dmask && n_out) { CUDA_TRY(cudaMemcpyAsync(h_mask, dmask, (size_t)n_out * mask_sz, cudaMemcpyDeviceToHost, st)); g_last_d2h += n_out * (int64_t)mask_sz; }
+    if (h_lengths && n_rows) { CUDA_TRY(cudaMemcpyAsync(h_lengths, d->st_lengths, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st)); g_last_d2h += n_rows * 4; }
+    if (h_status && n_rows) { CUDA_TRY(cudaMemcpyAsync(h_status, d->st_status, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st)); g_last_d2h += n_rows * 4; }
     CUDA_TRY(cudaStreamSynchronize(st));
     if (out_stride_used) *out_stride_used = ragged ? n_out : stride;
     return DNATOK_OK;

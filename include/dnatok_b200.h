@@ -200,6 +200,11 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
  *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)
  *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB)
+ *   "host_mask_threads"     dnatok_encode_host, padded output with a mask of 16 MiB or more: the mask is written by
+ *                           this many host threads from the row lengths while the ids are copied back, instead of
+ *                           being produced on the GPU and copied too (-1, default: one per core, at most 16;
+ *                           0: always copy the mask from the device)
+ *   "host_mask_min_bytes"   the size from which a mask is written by host threads (default 16 MiB)
  *   "kmer_force_segments"   1: use the k-mer segment encoder whenever scratch is given, whatever the batch shape
  *   "bpe_block_team_rows"   BPE batches of at most this many rows give every word a whole thread block
  *                           instead of one warp (lower latency when the batch cannot fill the GPU);
@@ -208,6 +213,11 @@ int dnatok_set_option(const char* name, int64_t value);
 
 /* Number of kernels this library has launched from the calling process (for accounting). */
 int64_t dnatok_launch_count(void);
+
+/* Bytes the calling thread's last dnatok_encode_host (unchunked) copied host -> device and device ->
+ * host.  With "host_mask_threads" active the mask of a large padded batch is not among them: host
+ * threads write it from the row lengths the GPU returned.  No reference counterpart. */
+void dnatok_host_copy_bytes(int64_t* h2d, int64_t* d2h);
 
 #ifdef __cplusplus
 }

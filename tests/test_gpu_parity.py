@@ -407,6 +407,59 @@ def test_host_entry_chunked_pipeline(toks, name, rows, length, kw):
     assert np.array_equal(enc["lengths"], o_mask.sum(axis=1))
 
 
+@pytest.mark.parametrize("name", ["char", "kmer6", "bpe4096"])
+@pytest.mark.parametrize("mask_dtype", [np.int64, np.int32, np.uint8])
+def test_host_entry_mask_written_by_host_threads(toks, name, mask_dtype):
+    """dnatok_encode_host with the attention mask written by host threads from the GPU's row lengths
+    (forced here for a small batch) against the same call with the mask copied from the device and
+    against the oracle: ragged rows, empty rows, both padding sides, truncation."""
+    import ctypes
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    rng = np.random.default_rng(5)
+    B = 211
+    lens = rng.integers(0, 2000, size=B)
+    lens[:4] = [0, 1, 1999, 6]
+    a = synth.config3(batch=B, length=2000, seed=77) if name == "bpe4096" else synth.config2(batch=B, length=2000, seed=77)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat = np.concatenate([a[i, :lens[i]] for i in range(B)])
+    tok = toks[name]
+    for left in (False, True):
+        tok.padding_side = "left" if left else "right"
+        try:
+            for kw in (dict(padding="longest"), dict(padding="max_length", max_length=150, truncation=True)):
+                got = {}
+                for threads in (3, 0):
+                    _cabi.check(L.dnatok_set_option(b"host_mask_threads", threads))
+                    _cabi.check(L.dnatok_set_option(b"host_mask_min_bytes", 0))
+                    try:
+                        got[threads] = tok.encode_host((flat, offs), mask_dtype=mask_dtype, **kw)
+                        h2d, d2h = ctypes.c_int64(0), ctypes.c_int64(0)
+                        L.dnatok_host_copy_bytes(ctypes.byref(h2d), ctypes.byref(d2h))
+                        got[threads]["d2h"] = d2h.value
+                    finally:
+                        _cabi.check(L.dnatok_set_option(b"host_mask_threads", -1))
+                        _cabi.check(L.dnatok_set_option(b"host_mask_min_bytes", 16 << 20))
+                o_ids, o_mask = H.oracle_batch(name, flat, offs, pad_left=left,
+                                               **{k: v for k, v in kw.items()})
+                for threads in (3, 0):
+                    assert got[threads]["attention_mask"].dtype == mask_dtype
+                    assert np.array_equal(got[threads]["input_ids"], o_ids), (kw, left, threads)
+                    assert np.array_equal(got[threads]["attention_mask"], o_mask), (kw, left, threads)
+                # the mask crossed the link only in the second call
+                assert got[0]["d2h"] - got[3]["d2h"] == o_mask.size * np.dtype(mask_dtype).itemsize
+                # the same with 32-bit ids
+                _cabi.check(L.dnatok_set_option(b"host_mask_min_bytes", 0))
+                try:
+                    e32 = tok.encode_host((flat, offs), mask_dtype=mask_dtype, ids_dtype=np.int32, **kw)
+                finally:
+                    _cabi.check(L.dnatok_set_option(b"host_mask_min_bytes", 16 << 20))
+                assert e32["input_ids"].dtype == np.int32 and np.array_equal(e32["input_ids"], o_ids)
+                assert np.array_equal(e32["attention_mask"], o_mask)
+        finally:
+            tok.padding_side = "right"
+
+
 def test_dnatok_api_matches_reference_outputs(golden):
     """dnatok_b200.dna_tokenizer.DNATok against what the reference's DNATok returned for the same calls
     (recorded by tests/golden/make_golden.py): encode_batch_to_ids and encode_batch_with_padding."""
