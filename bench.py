@@ -330,6 +330,16 @@ def run_ours(args):
     if not args.no_affinity:
         from dnatok_b200.shard import bind_host_to_gpu
         cores = bind_host_to_gpu(local)          # before any pinned buffer is allocated
+    if world > 1:
+        # the ranks of one host share its cores: the threads that write attention masks are divided among them
+        from dnatok_b200 import _cabi
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+        per_rank = min(16, len(all_cores) // max(local_world, 1))
+        if per_rank < 8:
+            per_rank = 0                 # too few cores per rank to beat the copy (measured: 2 per rank at N=8 lose 10 %)
+        if os.environ.get("DNATOK_HOST_MASK_THREADS") is not None:
+            per_rank = int(os.environ["DNATOK_HOST_MASK_THREADS"])
+        _cabi.check(_cabi.lib().dnatok_set_option(b"host_mask_threads", per_rank))
     barrier = None
     if world > 1:
         import torch.distributed as dist
