@@ -144,14 +144,15 @@ class B200Tokenizer:
             raise ValueError("padding='max_length' needs max_length")
         ns = self._n_special(add_special_tokens)
         out = out or {}
-        if self.spec.kind in ("bpe", "kmer"):
-            # row lengths known on the host bound the length classes the BPE path has to launch and
-            # the number of segments the k-mer path cuts a row into
-            if host_offsets is not None and B:
-                lens = np.diff(host_offsets)
-                _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, int(lens.min()), max(int(lens.max()), 1)))
-            else:
-                _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, 0, 0))
+        # row lengths known on the host bound the length classes the BPE path has to launch and the
+        # number of segments the k-mer path cuts a row into (which only batches of few or very long
+        # rows use: large batches of ordinary rows skip the scan of the offsets)
+        wants_hint = self.spec.kind == "bpe" or (self.spec.kind == "kmer" and (B < 4096 or total > 32768 * B))
+        if wants_hint and host_offsets is not None and B:
+            lens = np.diff(host_offsets)
+            _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, int(lens.min()), max(int(lens.max()), 1)))
+        elif self.spec.kind in ("bpe", "kmer"):
+            _cabi.check(L.dnatok_set_row_bytes_hint(self.handle.ptr, 0, 0))
         with torch.cuda.device(dev):
             stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
             need = L.dnatok_scratch_bytes(self.handle.ptr, B, total)
