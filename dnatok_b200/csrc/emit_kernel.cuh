@@ -135,6 +135,13 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
         IdT* orow = ids + row * stride + cs;
         const bool aligned = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
 
+        // content occupies columns [c_lo, c_hi) of the span: vectors inside need no per-column checks
+        int c_lo = 0, c_hi = 0;
+        {
+            const int64_t lo64 = t_lo < 0 ? -t_lo : 0, hi64 = n - t_lo;
+            c_lo = (int)(lo64 < ncol ? lo64 : ncol);
+            c_hi = (int)(hi64 < 0 ? 0 : (hi64 < ncol ? hi64 : ncol));
+        }
         // ---- ids
         for (int v = lane; v * N < ncol; v += 32) {
             const int c0 = v * N;                              // column within the span
@@ -149,7 +156,7 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
             }
             IdT vals[N];
             const int64_t t0 = t_lo + c0;
-            const bool interior = t0 >= 0 && t0 + N <= n && c0 + N <= ncol;
+            const bool interior = c0 >= c_lo && c0 + N <= c_hi;
 #pragma unroll
             for (int e = 0; e < N; ++e) {
                 uint32_t word = (e * SZ < 4) ? lo : hi;
