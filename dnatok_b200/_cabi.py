@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(HERE, "csrc", "libdnatok_b200.so")
 OK = 0
 ROW_TOO_LONG, ROW_NOT_CONVERGED, ROW_CLIPPED, ROW_OUTSIDE_HINT, ROW_STALLED = 1, 2, 4, 8, 16
 KIND_CHAR, KIND_KMER, KIND_BPE = 0, 1, 2
-BPE_MAX_WORD = 49152
+BPE_MAX_WORD = 1 << 30
 
 EXPORTS = (
     "dnatok_version", "dnatok_last_error", "dnatok_create_char", "dnatok_create_kmer",

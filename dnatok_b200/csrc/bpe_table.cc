@@ -46,7 +46,7 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
     for (uint32_t i = 0; i < n_tokens; ++i) if (!rows[i].empty()) order.push_back(i);
     std::stable_sort(order.begin(), order.end(), [&](uint32_t x, uint32_t y) { return rows[x].size() > rows[y].size(); });
 
-    std::vector<uint32_t> slots((size_t)n_tokens, 0xFFFFFFFFu);
+    std::vector<uint32_t> slots((size_t)n_tokens, 0xFFFFFFFFu);      // low words first; widened below
     std::vector<uint32_t> disp(n_tokens, 0);
     size_t first_free = 0;
     for (uint32_t ai : order) {
@@ -70,7 +70,6 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
     }
 
     t->disp.swap(disp);
-    t->slots.swap(slots);
     t->merge_out.resize(n);
     for (int32_t r = 0; r < n; ++r) t->merge_out[r] = (uint16_t)o[r];
     t->future.assign(n, 0xFFFFu);
@@ -80,11 +79,19 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
             if (c >= 0 && (uint32_t)r < t->future[c]) t->future[c] = (uint16_t)r;
         }
     }
+    auto entry = [&](int32_t r) {
+        const uint64_t lo = ((uint64_t)a[r] << 16) | (uint64_t)r;
+        const uint64_t hi = ((uint64_t)o[r] << 16) | (uint64_t)t->future[r];
+        return lo | (hi << 32);
+    };
+    t->slots.assign(slots.size(), ~0ull);
+    for (size_t i = 0; i < slots.size(); ++i)
+        if (slots[i] != 0xFFFFFFFFu) t->slots[i] = entry((int32_t)(slots[i] & 0xFFFFu));
     // direct table for pairs of small ids (the initial symbols and the first merges of a trained
-    // vocabulary): one shared-memory load answers rank and future rank
-    t->hot.assign(32 * 32, 0xFFFFFFFFu);
+    // vocabulary): one shared-memory load answers the whole entry
+    t->hot.assign(32 * 32, ~0ull);
     for (int32_t r = 0; r < n; ++r)
-        if (a[r] < 32 && b[r] < 32) t->hot[a[r] * 32 + b[r]] = (uint32_t)r | ((uint32_t)t->future[r] << 16);
+        if (a[r] < 32 && b[r] < 32) t->hot[a[r] * 32 + b[r]] = entry(r);
     t->byte_tok.resize(256);
     for (int i = 0; i < 256; ++i) t->byte_tok[i] = (uint16_t)byte_ids[i];
     t->n_tokens = n_tokens;

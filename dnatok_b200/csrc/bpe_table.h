@@ -1,9 +1,10 @@
 // Host-side construction of the BPE merge table the kernels read.
 //
 // The table is a perfect hash of the pair (left id, right id) by row displacement: every left
-// token `a` owns a row offset disp[a]; the pair (a, b) lives in slots[disp[a] + b], which holds
-// (a << 16) | rank.  A lookup is two dependent loads and an equality test, with no probing and
-// no false positives.  Ids are Hugging Face ids, so the kernels emit final ids with no remap.
+// token `a` owns a row offset disp[a]; the pair (a, b) lives in slots[disp[a] + b], a 64-bit
+// entry: low word (a << 16) | rank, high word (created id << 16) | future rank.  A lookup is two
+// dependent loads and an equality test, with no probing and no false positives, and brings
+// everything a merge needs.  Ids are Hugging Face ids, so the kernels emit final ids with no remap.
 // (The reference keeps a cuco::static_map keyed by a 64-bit pair and remaps kernel ids to HF
 // ids afterwards: src/dnatok_bpe_kernel/dnatok_bpe.cu:123-132,761-791,822-837 and
 // src/gputok_bpe_backend.py:447-466.)
@@ -16,10 +17,11 @@ namespace dnatok {
 
 struct BpeHostTable {
     std::vector<uint32_t> disp;        // [n_tokens]
-    std::vector<uint32_t> slots;       // [max disp + n_tokens], 0xFFFFFFFF when empty
+    std::vector<uint64_t> slots;       // [max disp + n_tokens]; low 32 bits (a << 16) | rank, high 32 bits
+                                       // (created id << 16) | future rank; all ones when empty
     std::vector<uint16_t> merge_out;   // [n_merges] id created by each rank
     std::vector<uint16_t> future;      // [n_merges] lowest rank of any pair containing that id, 0xFFFF if none
-    std::vector<uint32_t> hot;         // [32 * 32] pairs of ids < 32: rank | future << 16, 0xFFFFFFFF if no merge
+    std::vector<uint64_t> hot;         // [32 * 32] pairs of ids < 32 in the slot format, all ones if no merge
     std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
     uint32_t n_tokens = 0;
     uint32_t n_merges = 0;

@@ -62,10 +62,9 @@ struct DeviceTables {
     int32_t* lut256 = nullptr;       // char LUT / k-mer single ids
     int32_t* kmer_ids = nullptr;
     uint32_t* disp = nullptr;
-    uint32_t* slots = nullptr;
+    uint64_t* slots = nullptr;
     uint16_t* merge_out = nullptr;
-    uint16_t* future = nullptr;
-    uint32_t* hot = nullptr;
+    uint64_t* hot = nullptr;
     uint16_t* byte_tok = nullptr;
     int sm_count = 0;
     // host-pipeline staging (grow only)
@@ -119,6 +118,9 @@ int upload(T** dst, const std::vector<T>& src) {
     return 0;
 }
 
+struct BpeLaunchInfo;
+int bpe_launch_info(int dev, const BpeLaunchInfo** out);
+
 // Tables of the handle on the current device (uploaded on first use).
 int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
     int dev = 0;
@@ -135,9 +137,10 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
             if ((rc = upload(&d.disp, h->bpe.disp))) return rc;
             if ((rc = upload(&d.slots, h->bpe.slots))) return rc;
             if ((rc = upload(&d.merge_out, h->bpe.merge_out))) return rc;
-            if ((rc = upload(&d.future, h->bpe.future))) return rc;
             if ((rc = upload(&d.hot, h->bpe.hot))) return rc;
             if ((rc = upload(&d.byte_tok, h->bpe.byte_tok))) return rc;
+            const BpeLaunchInfo* info;
+            if ((rc = bpe_launch_info(dev, &info))) return rc;     // configures every merge kernel once per device
         }
         it = h->dev.emplace(dev, d).first;
     }
@@ -187,11 +190,16 @@ struct BpeScratch {
     int32_t* counts;        // [n_rows] content tokens per row
     int32_t* class_count;   // [16]
     int32_t* work;          // [16]
+    unsigned long long* long_cursor;   // bytes of long_area handed out
     int32_t* class_list;    // [BPE_N_CLASSES * n_rows]
+    uint8_t* long_area;     // ranks and masks of the words of the long class
+    size_t long_bytes;
     size_t bytes;
 };
 
-BpeScratch bpe_scratch_layout(void* base, int64_t n_rows, int64_t total_bytes) {
+// The long class (words beyond the lanes kernel's capacity) needs extra working memory; it is left
+// out when no row of the batch can be that long (by the total size or by the caller's hint).
+BpeScratch bpe_scratch_layout(const dnatok_handle* h, void* base, int64_t n_rows, int64_t total_bytes) {
     BpeScratch s;
     size_t o = 0;
     uint8_t* b = (uint8_t*)base;
@@ -199,56 +207,87 @@ BpeScratch bpe_scratch_layout(void* base, int64_t n_rows, int64_t total_bytes) {
     s.counts = (int32_t*)(b + o);       o += align_up((size_t)n_rows * 4 + 4, 256);
     s.class_count = (int32_t*)(b + o);  o += 64;
     s.work = (int32_t*)(b + o);         o += 64;
+    s.long_cursor = (unsigned long long*)(b + o);   o += 64;
     o = align_up(o, 256);
     s.class_list = (int32_t*)(b + o);   o += align_up((size_t)n_rows * 4 * BPE_N_CLASSES + 4, 256);
+    int64_t longest = total_bytes;
+    if (h->hint_max_row > 0 && h->hint_max_row < longest) longest = h->hint_max_row;
+    s.long_area = (uint8_t*)(b + o);
+    s.long_bytes = 0;
+    if (longest > bpe_class_capacity(BPE_LONG_CLASS - 1)) {
+        const int64_t words = total_bytes / bpe_class_capacity(BPE_LONG_CLASS - 1) + 1;
+        s.long_bytes = align_up((size_t)(2 * total_bytes + total_bytes / 2 + 64 * words), 256);
+    }
+    o += s.long_bytes;
     s.bytes = o;
     return s;
 }
 
-template <int CLS, int W>
-int launch_bpe_team(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
-                    int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
-    constexpr int C = bpe_class_capacity(CLS);
+// Resident blocks per SM of every merge kernel on a device; filling it also sets the kernels'
+// shared-memory attribute, so a later launch does nothing but launch.
+struct BpeLaunchInfo { int lanes[BPE_LONG_CLASS]; };
+
+template <int W>
+int bpe_setup_lanes(int* bps) {
     constexpr int BW = bpe_block_warps(W);
-    constexpr int TEAMS = BW / W;                              // words in flight per block
-    const size_t smem = (size_t)TEAMS * bpe_slot_bytes(C);
-    static std::mutex mu;
-    static std::map<int, int> blocks_per_sm;         // device -> resident blocks (also marks the attribute as set)
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
-    int bps = 0;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        auto it = blocks_per_sm.find(dev);
-        if (it == blocks_per_sm.end()) {
-            CUDA_TRY(cudaFuncSetAttribute(bpe_rounds_kernel<C, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, bpe_rounds_kernel<C, W>, BW * 32, smem));
-            if (bps < 1) bps = 1;
-            blocks_per_sm[dev] = bps;
-        } else bps = it->second;
-    }
-    // Resident-size grid: every team pulls words from the class's shared counter.
-    int64_t grid = (int64_t)d.sm_count * bps;
-    const int64_t need = (n_rows + TEAMS - 1) / TEAMS;
-    if (grid > need) grid = need;
-    if (grid < 1) grid = 1;
-    bpe_rounds_kernel<C, W><<<(unsigned)grid, BW * 32, smem, st>>>(
-        bytes, offsets, s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
-        s.tokens, s.counts, status);
-    LAUNCH_CHECK("bpe_rounds_kernel");
+    const size_t smem = (size_t)(BW / W) * bpe_team_bytes(W);
+    CUDA_TRY(cudaFuncSetAttribute(bpe_lanes_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(bps, bpe_lanes_kernel<W>, BW * 32, smem));
+    if (*bps < 1) *bps = 1;
     return 0;
 }
 
-// A small batch cannot fill the GPU with one warp per word: give every word a whole block then, which
+int bpe_launch_info(int dev, const BpeLaunchInfo** out) {
+    static std::mutex mu;
+    static std::map<int, BpeLaunchInfo> info;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = info.find(dev);
+    if (it == info.end()) {
+        BpeLaunchInfo li{};
+        int rc;
+        if ((rc = bpe_setup_lanes<1>(&li.lanes[0])) || (rc = bpe_setup_lanes<2>(&li.lanes[1])) ||
+            (rc = bpe_setup_lanes<4>(&li.lanes[2])) || (rc = bpe_setup_lanes<8>(&li.lanes[3])) ||
+            (rc = bpe_setup_lanes<16>(&li.lanes[4])) || (rc = bpe_setup_lanes<32>(&li.lanes[5])))
+            return rc;
+        cudaFuncAttributes fa;
+        CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_long_kernel));      // loads the kernel's code now, not at its first launch
+        CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_classify_kernel));
+        it = info.emplace(dev, li).first;
+    }
+    *out = &it->second;
+    return 0;
+}
+
+// Class CLS's rows through teams of W warps (W >= 1 << CLS).
+template <int CLS, int W>
+int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDeviceTable& t, const uint8_t* bytes,
+                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+    constexpr int BW = bpe_block_warps(W);
+    constexpr int TEAMS = BW / W;                              // words in flight per block
+    constexpr int WI = W == 1 ? 0 : W == 2 ? 1 : W == 4 ? 2 : W == 8 ? 3 : W == 16 ? 4 : 5;
+    const size_t smem = (size_t)TEAMS * bpe_team_bytes(W);
+    // Resident-size grid: every team pulls words from the class's shared counter.
+    int64_t grid = (int64_t)d.sm_count * li.lanes[WI];
+    const int64_t need = (n_rows + TEAMS - 1) / TEAMS;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    bpe_lanes_kernel<W><<<(unsigned)grid, BW * 32, smem, st>>>(
+        bytes, offsets, s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
+        s.tokens, s.counts, status);
+    LAUNCH_CHECK("bpe_lanes_kernel");
+    return 0;
+}
+
+// A small batch cannot fill the GPU with one warp per word: give every word eight warps then, which
 // shortens each word's rounds instead.
 template <int CLS>
-int launch_bpe_class(const DeviceTables& d, const BpeDeviceTable& t, const uint8_t* bytes, const int64_t* offsets,
-                     int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
-    constexpr int W = bpe_class_team(CLS);
+int launch_bpe_class(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDeviceTable& t, const uint8_t* bytes,
+                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+    constexpr int W = 1 << CLS;
     const int64_t lim = g_bpe_block_team_rows.load();
-    if (W < BPE_BLOCK_WARPS && n_rows <= (lim < 0 ? (int64_t)d.sm_count * 8 : lim))
-        return launch_bpe_team<CLS, BPE_BLOCK_WARPS>(d, t, bytes, offsets, n_rows, s, status, st);
-    return launch_bpe_team<CLS, W>(d, t, bytes, offsets, n_rows, s, status, st);
+    if (W < 8 && n_rows <= (lim < 0 ? (int64_t)d.sm_count * 8 : lim))
+        return launch_bpe_lanes<CLS, 8>(d, li, t, bytes, offsets, n_rows, s, status, st);
+    return launch_bpe_lanes<CLS, W>(d, li, t, bytes, offsets, n_rows, s, status, st);
 }
 
 int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
@@ -256,31 +295,48 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
                   cudaStream_t st) {
     if (!scratch) return fail(DNATOK_ERR_SCRATCH, "BPE needs a scratch buffer (dnatok_scratch_bytes)");
     if (reinterpret_cast<uintptr_t>(scratch) & 255) return fail(DNATOK_ERR_SCRATCH, "scratch must be 256-byte aligned");
-    BpeScratch s = bpe_scratch_layout(scratch, n_rows, total_bytes);
+    BpeScratch s = bpe_scratch_layout(h, scratch, n_rows, total_bytes);
     if (s.bytes > scratch_bytes) return fail(DNATOK_ERR_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, s.bytes);
     if (n_rows == 0) return 0;
-    CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 128, st));   // class_count and work are adjacent
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    const BpeLaunchInfo* li;
+    if (int rc = bpe_launch_info(dev, &li)) return rc;
+    CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 192, st));   // class_count, work and long_cursor are adjacent
     // classes that can hold a row of this batch: bounded by the total size and by the caller's hint
     uint32_t class_mask = 0;
     {
         int64_t lo = 1, hi = total_bytes;
         if (h->hint_max_row > 0) { lo = h->hint_min_row > 1 ? h->hint_min_row : 1; if (h->hint_max_row < hi) hi = h->hint_max_row; }
         for (int c = 0; c < BPE_N_CLASSES; ++c) {
-            const int64_t c_lo = c == 0 ? 1 : bpe_class_capacity(c - 1) + 1, c_hi = bpe_class_capacity(c);
+            const int64_t c_lo = c == 0 ? 1 : bpe_class_capacity(c - 1) + 1;
+            const int64_t c_hi = c < BPE_LONG_CLASS ? bpe_class_capacity(c) : INT64_MAX;
             if (c_hi >= lo && c_lo <= hi) class_mask |= 1u << c;
         }
     }
+    if (((class_mask >> BPE_LONG_CLASS) & 1u) && !s.long_bytes) class_mask &= ~(1u << BPE_LONG_CLASS);
     bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
                                                                        s.class_list, s.counts, status, class_mask);
     LAUNCH_CHECK("bpe_classify_kernel");
-    BpeDeviceTable t{d.disp, d.slots, d.merge_out, d.future, d.hot, d.byte_tok, h->bpe.batch_safe ? 0 : 1};
+    BpeDeviceTable t{d.disp, reinterpret_cast<const uint2*>(d.slots), d.merge_out, reinterpret_cast<const uint2*>(d.hot),
+                     d.byte_tok, h->bpe.batch_safe ? 0 : 1};
     // Classes outside the mask are not launched; a row that falls into one is flagged by the classifier.
+    // Longest class first: its few, slow words start while nothing else competes for the SMs.
+    if ((class_mask >> BPE_LONG_CLASS) & 1u) {
+        int64_t grid = total_bytes / bpe_class_capacity(BPE_LONG_CLASS - 1);     // no more words than this can be that long
+        if (grid > n_rows) grid = n_rows;
+        if (grid > d.sm_count) grid = d.sm_count;
+        if (grid < 1) grid = 1;
+        bpe_long_kernel<<<(unsigned)grid, BPE_LONG_WARPS * 32, 0, st>>>(
+            bytes, offsets, s.class_list + (int64_t)BPE_LONG_CLASS * n_rows, s.class_count + BPE_LONG_CLASS,
+            s.work + BPE_LONG_CLASS, t, s.tokens, s.counts, status, s.long_area, s.long_cursor);
+        LAUNCH_CHECK("bpe_long_kernel");
+    }
     int rc;
-#define BPE_CLASS(CLS)                                                                                         \
-    if (((class_mask >> CLS) & 1u) && (rc = launch_bpe_class<CLS>(d, t, bytes, offsets, n_rows, s, status, st))) \
+#define BPE_CLASS(CLS)                                                                                              \
+    if (((class_mask >> CLS) & 1u) && (rc = launch_bpe_class<CLS>(d, *li, t, bytes, offsets, n_rows, s, status, st))) \
         return rc;
-    // longest class first: its few, slow words start while nothing else competes for the SMs
-    BPE_CLASS(8) BPE_CLASS(7) BPE_CLASS(6) BPE_CLASS(5) BPE_CLASS(4) BPE_CLASS(3) BPE_CLASS(2) BPE_CLASS(1) BPE_CLASS(0)
+    BPE_CLASS(5) BPE_CLASS(4) BPE_CLASS(3) BPE_CLASS(2) BPE_CLASS(1) BPE_CLASS(0)
 #undef BPE_CLASS
     return 0;
 }
@@ -640,7 +696,7 @@ void dnatok_destroy(dnatok_handle* h) {
         DeviceTables& d = kv.second;
         if (cudaSetDevice(kv.first) != cudaSuccess) continue;
         if (d.stream) cudaStreamSynchronize(d.stream);
-        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.future, d.hot, d.byte_tok, d.st_bytes, d.st_offsets,
+        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.hot, d.byte_tok, d.st_bytes, d.st_offsets,
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);
@@ -669,7 +725,7 @@ size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t tota
     if (!h || n_rows < 0 || total_bytes < 0) return 0;
     if (h->kind == DNATOK_KIND_KMER) return kmer_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
     if (h->kind != DNATOK_KIND_BPE) return 0;
-    return bpe_scratch_layout(nullptr, n_rows, total_bytes).bytes;
+    return bpe_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
 }
 
 int64_t dnatok_max_tokens(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes, const dnatok_format* f) {
@@ -705,7 +761,7 @@ int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_of
         default: {
             if (int rc = run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, st))
                 return rc;
-            BpeScratch s = bpe_scratch_layout(d_scratch, n_rows, total_bytes);
+            BpeScratch s = bpe_scratch_layout(h, d_scratch, n_rows, total_bytes);
             return launch_span_lengths(d_offsets, s.counts, n_rows, rf, d_lengths, d_status, st);
         }
     }
@@ -739,7 +795,7 @@ int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
                                       nullptr, d_out_offsets, d_status, d_scratch, scratch_bytes, st);
         default: {
             if (!d_scratch) return fail(DNATOK_ERR_SCRATCH, "BPE write needs the scratch filled by dnatok_prepare");
-            BpeScratch s = bpe_scratch_layout(d_scratch, n_rows, total_bytes);
+            BpeScratch s = bpe_scratch_layout(h, d_scratch, n_rows, total_bytes);
             if (s.bytes > scratch_bytes) return fail(DNATOK_ERR_SCRATCH, "scratch too small");
             return launch_emit<uint16_t, false>(*d, s.tokens, d_offsets, s.counts, n_rows, total_bytes, rf, fmt->id_bits,
                                                 d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
@@ -896,7 +952,7 @@ int dnatok_encode_bpe_builtin_scratch(dnatok_handle* h, const uint8_t* d_bytes, 
                                       dnatok_stream stream) {
     if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
     if (h->kind != DNATOK_KIND_BPE) return fail(DNATOK_ERR_INVALID, "only BPE handles use scratch memory");
-    const size_t need = bpe_scratch_layout(nullptr, n_rows, total_bytes).bytes;
+    const size_t need = bpe_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
     if (need > (size_t)DNATOK_BUILTIN_SCRATCH_BYTES)
         return fail(DNATOK_ERR_CAPACITY,
                     "batch of %lld rows / %lld bytes needs %zu bytes of scratch; the built-in array holds %zu "

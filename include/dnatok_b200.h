@@ -46,7 +46,7 @@ extern "C" {
 #define DNATOK_ERR_CAPACITY    (-5)   /* output buffer too small */
 
 /* per-row status bits written to d_status (0 = fine) */
-#define DNATOK_ROW_TOO_LONG       1   /* BPE word longer than the kernel's shared-memory slot; row left empty */
+#define DNATOK_ROW_TOO_LONG       1   /* BPE word longer than DNATOK_BPE_MAX_WORD; row left empty */
 #define DNATOK_ROW_NOT_CONVERGED  2   /* BPE pass limit reached (cannot happen for a consistent table) */
 #define DNATOK_ROW_CLIPPED        4   /* row had more tokens than out_stride and was cut to fit */
 #define DNATOK_ROW_OUTSIDE_HINT   8   /* BPE row length outside dnatok_set_row_bytes_hint; row left empty */
@@ -56,7 +56,8 @@ extern "C" {
 #define DNATOK_KIND_KMER 1
 #define DNATOK_KIND_BPE  2
 
-#define DNATOK_BPE_MAX_WORD 49152     /* longest BPE word (bytes) the merge kernel accepts */
+#define DNATOK_BPE_MAX_WORD (1 << 30) /* longest BPE word (bytes): words of up to 32,768 bytes are merged in shared
+                                         memory, longer ones in scratch memory (about 4.5 bytes of scratch per byte) */
 
 typedef struct dnatok_handle dnatok_handle;
 typedef void* dnatok_stream;          /* a cudaStream_t */

@@ -160,7 +160,8 @@ def test_ragged_lengths_truncation_dtypes(toks, name, ids_dtype, mask_dtype):
 def test_bpe_homopolymers_and_long_words(toks, name, bpe_team_mode):
     words = [b"A" * n for n in (1, 2, 3, 4, 5, 8, 9, 31, 32, 33, 64, 100, 255, 256, 257, 1024, 4097)]
     words += [b"AC" * 300, b"ACG" * 333, b"T" * 511 + b"A", b"N" * 70, b"ACGTNNNACGTnnacgt" * 40]
-    words += [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (255, 256, 257, 511, 513, 2047, 2049, 8191, 8193, 16384, 16385, 32769, 49152)]
+    words += [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (255, 256, 257, 1023, 1024, 1025, 2047, 2048, 2049, 4096, 4097, 8191, 8192, 8193, 16384,
+                                                                       16385, 32767, 32768, 32769, 49152)]
     flat, offs = H.pack_strs(words)
     enc = run_device(toks[name], flat, offs, padding=False, add_special_tokens=False)
     ids = enc["input_ids"].cpu().numpy()
@@ -170,10 +171,35 @@ def test_bpe_homopolymers_and_long_words(toks, name, bpe_team_mode):
         assert ids[oo[i]:oo[i + 1]].tolist() == want[i].tolist(), "word %d (len %d)" % (i, len(words[i]))
 
 
-def test_bpe_word_over_limit_raises(toks):
-    flat, offs = H.pack_strs([b"ACGT" * 13000])         # 52,000 bytes > 49,152
-    with pytest.raises(RuntimeError, match="word limit"):
-        run_device(toks["bpe4096"], flat, offs, padding=False)
+@pytest.mark.parametrize("name", ["bpe4096", "bpe32000"])
+def test_bpe_words_beyond_shared_memory(toks, name):
+    """Words longer than the 32,768 positions a block keeps in shared memory go through the
+    global-memory merge kernel (the reference has no per-input cap either:
+    src/dnatok_bpe_kernel/dnatok_bpe.cu:276-297, :890-892)."""
+    words = [bytes(synth.config3(batch=1, length=n, seed=n)[0]) for n in (32768, 32769, 49153, 100000)]
+    words += [b"A" * 200000, b"ACGT" * 13000, b"AC" * 20000 + b"N" + b"T" * 40001, b"ACG"]
+    flat, offs = H.pack_strs(words)
+    enc = run_device(toks[name], flat, offs, padding=False, add_special_tokens=False)
+    ids = enc["input_ids"].cpu().numpy()
+    oo = enc["offsets"].cpu().numpy()
+    want = H.oracle_rows(name, flat, offs)
+    for i in range(len(words)):
+        assert ids[oo[i]:oo[i + 1]].tolist() == want[i].tolist(), "word %d (len %d)" % (i, len(words[i]))
+
+
+def test_bpe_megabase_words(toks):
+    """Eight words of 1,048,576 bp (the byte-level shape's sizes) through a BPE tokenizer."""
+    rows = synth.config3(batch=8, length=1 << 20, seed=99)
+    flat, offs = synth.pack_rows(rows)
+    enc = run_device(toks["bpe4096"], flat, offs, padding=False, add_special_tokens=True)
+    ids = enc["input_ids"].cpu().numpy()
+    oo = enc["offsets"].cpu().numpy()
+    want = H.oracle_rows("bpe4096", flat, offs)
+    sp = toks["bpe4096"].spec.specials
+    for i in range(8):
+        got = ids[oo[i]:oo[i + 1]]
+        assert got[0] == sp.cls_id and got[-1] == sp.sep_id
+        assert np.array_equal(got[1:-1], want[i]), "word %d" % i
 
 
 def test_clipping_without_truncation_raises(toks):
