@@ -58,34 +58,36 @@ __host__ __device__ constexpr int bpe_class_capacity(int c) { return (32 * BPE_L
 __host__ __device__ constexpr int bpe_block_warps(int W) { return W < 8 ? 8 : W; }
 // shared memory of one team: two token buffers, and for teams of several warps the exchange arrays
 __host__ __device__ constexpr int bpe_team_bytes(int W) {
-    return 2 * BPE_LANE_SLOTS * (32 * W + 2) * 2 + (W > 1 ? 32 * W * 16 : 0);
+    return 2 * (BPE_LANE_SLOTS + 1) * (32 * W + 2) * 2 + (W > 1 ? 32 * W * 8 : 0);
 }
 // caller scratch of one word of the long class: ranks (2 bytes per position) and three mask words per 32 positions
 __host__ __device__ constexpr int64_t bpe_long_bytes(int64_t n) { return ((2 * n + 15) / 16 + 3 * ((n + 127) / 128)) * 16; }
 
 struct BpeDeviceTable {
     const uint32_t* disp;        // [n_tokens] row displacement of the left token
-    const uint2* slots;          // x = (left << 16) | rank, y = (created << 16) | F; all ones when empty
+    const uint2* slots;          // x = (rank << 16) | created, y = (left << 16) | F; all ones when empty
     const uint16_t* merge_out;   // [n_merges] token created by a rank
-    const uint2* hot;            // [32 * 32] pairs of ids < 32, slot format
+    const uint2* hot;            // [32 * 32] pairs of ids < 32: x as in slots, y = (F << 16) | rank; all ones when no merge
     const uint16_t* byte_tok;    // [256]
     int32_t single_step;
+    uint32_t hot_ranks;          // every rank below this creates an id < 32
 };
 
-// key = F << 16 | rank (its minimum over a word gives the bound B), val = created << 16 | rank;
-// both all ones when the pair does not merge.
-__device__ __forceinline__ void bpe_lookup(const BpeDeviceTable& t, const uint2* s_hot, uint32_t a, uint32_t b,
-                                           uint32_t& key, uint32_t& val) {
-    uint2 s;
-    if ((a | b) < 32u) {
-        s = s_hot[a * 32u + b];
-    } else {
-        s = __ldg(t.slots + __ldg(t.disp + a) + b);
-        if ((s.x >> 16) != a) s = make_uint2(BPE_FULL, BPE_FULL);
-    }
-    key = __byte_perm(s.x, s.y, 0x5410);        // low half of x, low half of y above it
-    val = __byte_perm(s.x, s.y, 0x7610);        // low half of x, high half of y above it
+// One table entry: x = (rank << 16) | created id, y = (left id << 16) | F.  Ranks compare like the x
+// words themselves (equal ranks create equal ids), so x is what the kernels keep per pair.  What
+// the kernels work with is the pair (x, key), key = (F << 16) | rank: the minimum of the keys over a
+// word gives the bound B (upper half) and tells whether any pair merges.  The table in shared
+// memory holds (x, key) directly; an entry from global memory is checked against its left id first.
+__device__ __forceinline__ uint2 bpe_cold_entry(const BpeDeviceTable& t, uint32_t a, uint32_t b) {
+    uint2 s = __ldg(t.slots + __ldg(t.disp + a) + b);
+    s.y = (s.y >> 16) == a ? __byte_perm(s.x, s.y, 0x5432) : BPE_FULL;
+    if (s.y == BPE_FULL) s.x = BPE_FULL;
+    return s;
 }
+
+constexpr int BPE_HOT_STRIDE = 36;              // row stride of the shared-memory table: the 16 pairs of four consecutive ids fall into 16 different banks
+constexpr int BPE_HOT_WORDS = 33 * BPE_HOT_STRIDE;   // row and column 32 stay empty: 32 is the filler token behind the end of a word
+constexpr uint32_t BPE_FILLER = 32;
 
 // odd(i) = c(i) & ~odd(i-1), odd(-1) = 0: parity of the length of the run of set bits ending at
 // each bit.
@@ -108,32 +110,57 @@ __device__ __forceinline__ uint32_t carry_then(uint32_t a, uint32_t b) {
 // Run parities of one mask word per lane, the runs continuing from lane to lane: upwards
 // (DOWN = false: bit `top` of lane l-1 precedes bit 0 of lane l) or downwards (DOWN = true: bit
 // `top` of lane l+1 precedes bit 0 of lane l).  Every word holds top + 1 bits; `full` is the word
-// with all of them set.  `carry` enters the first lane of the chain and leaves as the parity after
-// the last one, so blocks of 32 lanes chain through it.  A word passes its incoming parity on only
-// when all its bits are set; unless some lane has such a word the neighbour's own top bit is the
-// carry and one shuffle replaces the scan over carry functions.
+// with all of them set.  A word passes its incoming parity on only when all its bits are set;
+// unless some lane has such a word the neighbour's own top bit is the carry and one shuffle
+// replaces the scan over carry functions.
+//
+// chain_prepare does everything that does not depend on the parity entering the block of 32 lanes
+// and returns the block's carry function (what leaves the block as a function of what enters);
+// chain_finish takes the entering parity and gives the lane's parities.
+struct ChainPrep {
+    uint32_t odd0, fr;   // parities with nothing entering the word; the run they flip on when something does
+    uint32_t f;          // fast: parity leaving the word; else: carry function from the block's entry to this word's exit
+    bool fast;
+};
+
 template <bool DOWN>
-__device__ __forceinline__ uint32_t chain_parity(uint32_t c, int top, uint32_t full, bool& carry, int lane) {
-    const uint32_t odd0 = run_parity(c);
-    const uint32_t fr = first_run(c);
-    const uint32_t out0 = (odd0 >> top) & 1u;
-    bool cin;
-    if (__ballot_sync(BPE_FULL, c == full) == 0u) {
-        const uint32_t nb = DOWN ? __shfl_down_sync(BPE_FULL, out0, 1) : __shfl_up_sync(BPE_FULL, out0, 1);
-        cin = (DOWN ? lane == 31 : lane == 0) ? carry : nb != 0u;
-        carry = __shfl_sync(BPE_FULL, out0, DOWN ? 0 : 31) != 0u;
+__device__ __forceinline__ ChainPrep chain_prepare(uint32_t c, int top, uint32_t full, int lane, uint32_t& block_fn) {
+    ChainPrep p;
+    p.odd0 = run_parity(c);
+    p.fr = first_run(c);
+    const uint32_t out0 = (p.odd0 >> top) & 1u;
+    p.fast = __ballot_sync(BPE_FULL, c == full) == 0u;
+    if (p.fast) {
+        p.f = out0;
+        block_fn = __shfl_sync(BPE_FULL, out0, DOWN ? 0 : 31) * 3u;      // a constant function
     } else {
-        uint32_t f = out0 | ((((odd0 ^ fr) >> top) & 1u) << 1);
+        uint32_t f = out0 | ((((p.odd0 ^ p.fr) >> top) & 1u) << 1);
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const uint32_t other = DOWN ? __shfl_down_sync(BPE_FULL, f, d) : __shfl_up_sync(BPE_FULL, f, d);
             if (DOWN ? lane + d < 32 : lane >= d) f = carry_then(other, f);     // the lanes before this one apply first
         }
-        const uint32_t before = DOWN ? __shfl_down_sync(BPE_FULL, f, 1) : __shfl_up_sync(BPE_FULL, f, 1);
-        cin = (DOWN ? lane == 31 : lane == 0) ? carry : carry_apply(before, carry) != 0u;
-        carry = carry_apply(__shfl_sync(BPE_FULL, f, DOWN ? 0 : 31), carry) != 0u;
+        p.f = f;
+        block_fn = __shfl_sync(BPE_FULL, f, DOWN ? 0 : 31);
     }
-    return cin ? odd0 ^ fr : odd0;
+    return p;
+}
+
+template <bool DOWN>
+__device__ __forceinline__ uint32_t chain_finish(const ChainPrep& p, bool carry, int lane) {
+    const uint32_t before = DOWN ? __shfl_down_sync(BPE_FULL, p.f, 1) : __shfl_up_sync(BPE_FULL, p.f, 1);
+    const bool cin = (DOWN ? lane == 31 : lane == 0) ? carry : (p.fast ? before != 0u : carry_apply(before, carry) != 0u);
+    return cin ? p.odd0 ^ p.fr : p.odd0;
+}
+
+// Both steps for blocks visited one after the other: `carry` enters the block and leaves it updated.
+template <bool DOWN>
+__device__ __forceinline__ uint32_t chain_parity(uint32_t c, int top, uint32_t full, bool& carry, int lane) {
+    uint32_t fn;
+    const ChainPrep p = chain_prepare<DOWN>(c, top, full, lane, fn);
+    const uint32_t odd = chain_finish<DOWN>(p, carry, lane);
+    carry = carry_apply(fn, carry) != 0u;
+    return odd;
 }
 
 // Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].  One atomic per
@@ -175,13 +202,25 @@ __device__ __forceinline__ void team_sync(int team) {
     else asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(W * 32) : "memory");
 }
 
-// floor(x / d) for x * d < 2^32, d >= 1: inv = ceil(2^32 / d), or 0 for d = 1.
-__device__ __forceinline__ uint32_t bpe_inv(uint32_t d) { return d > 1u ? 0xFFFFFFFFu / d + 1u : 0u; }
-__device__ __forceinline__ uint32_t bpe_div(uint32_t x, uint32_t d, uint32_t inv) { return d > 1u ? __umulhi(x, inv) : x; }
+// floor(x / d) for 1 <= d <= 32, x < 2^16: __umulhi(2 x + 1, ceil(2^31 / d)).
+__device__ __forceinline__ uint32_t bpe_inv(uint32_t d) { return (0x80000000u + d - 1u) / d; }
+
+// The per-slot bodies of the lanes kernel run from the lane's last slot down to slot 0 through a
+// switch on the slot count with fall-through cases: one indirect jump instead of a guard per slot,
+// every slot index a compile-time constant (shared-memory offsets, register names, mask bits), and
+// no value handed from slot to slot except the accumulators.
+#define BPE_SLOTS_DOWN(X) \
+    X(31) X(30) X(29) X(28) X(27) X(26) X(25) X(24) X(23) X(22) X(21) X(20) X(19) X(18) X(17) X(16) \
+    X(15) X(14) X(13) X(12) X(11) X(10) X(9) X(8) X(7) X(6) X(5) X(4) X(3) X(2) X(1) X(0)
+
+#ifndef BPE_LANES_MIN_BLOCKS
+#define BPE_LANES_MIN_BLOCKS 4
+#endif
+__host__ __device__ constexpr int bpe_min_blocks(int W) { return W <= 8 ? BPE_LANES_MIN_BLOCKS : W == 16 ? 2 : 1; }
 
 // W: warps per word.
 template <int W>
-__global__ void __launch_bounds__(bpe_block_warps(W) * 32)
+__global__ void __launch_bounds__(bpe_block_warps(W) * 32, bpe_min_blocks(W))
 bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
                  const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
                  int32_t* __restrict__ work_counter, BpeDeviceTable t,
@@ -190,28 +229,38 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
     constexpr int P = BPE_LANE_SLOTS;
     constexpr int T = 32 * W;                    // lanes of a team
     constexpr int STRIDE = T + 2;                // elements between the slots of one lane
+    constexpr int BUF = (P + 1) * STRIDE;        // one token buffer: P slots and the copy of the next lane's first token
     constexpr int BW = bpe_block_warps(W);
     constexpr int TEAMS = BW / W;
     extern __shared__ uint4 bpe_dyn[];
-    __shared__ uint2 s_hot[32 * 32];             // direct table for pairs of small ids
+    __shared__ uint2 s_hot[BPE_HOT_WORDS];       // direct table for pairs of small ids, row stride BPE_HOT_STRIDE
     __shared__ uint16_t s_btok[256];
+    __shared__ uint32_t s_inv[P + 1];            // bpe_inv(d)
     __shared__ uint32_t s_red[BW];               // per-warp partial minima
-    __shared__ int32_t s_word[TEAMS][2];         // claimed word index, new length
-    for (int i = threadIdx.x; i < 32 * 32; i += BW * 32) s_hot[i] = __ldg(t.hot + i);
+    __shared__ uint32_t s_fn[BW];                // per-warp carry functions of the two walks
+    __shared__ uint32_t s_blk[BW];               // per-warp survivor count and border bits
+    __shared__ int32_t s_word[TEAMS];            // claimed word index
+    for (int i = threadIdx.x; i < BPE_HOT_WORDS; i += BW * 32) s_hot[i] = make_uint2(BPE_FULL, BPE_FULL);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * 32; i += BW * 32) s_hot[(i >> 5) * BPE_HOT_STRIDE + (i & 31)] = __ldg(t.hot + i);
     for (int i = threadIdx.x; i < 256; i += BW * 32) s_btok[i] = __ldg(t.byte_tok + i);
+    if (threadIdx.x >= 1 && threadIdx.x <= P) s_inv[threadIdx.x] = bpe_inv(threadIdx.x);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int team = warp / W, tw = warp % W;    // team, warp within team
     const int g = tw * 32 + lane;                // lane within team
-    uint8_t* area = reinterpret_cast<uint8_t*>(bpe_dyn) + (size_t)team * bpe_team_bytes(W);
-    uint16_t* cur = reinterpret_cast<uint16_t*>(area);           // [P][STRIDE] live tokens
-    uint16_t* nxt = cur + P * STRIDE;                            // [P][STRIDE] the next round's
-    uint16_t* xf = nxt + P * STRIDE;                             // [T] rank of every lane's first pair   (W > 1)
-    uint16_t* xl = xf + T;                                       // [T] rank of every lane's last pair    (W > 1)
-    uint32_t* m_a = reinterpret_cast<uint32_t*>(xl + T);         // [T] right-walk links, then selected pairs
-    uint32_t* m_b = m_a + T;                                     // [T] left-walk links, then survivors
-    uint32_t* m_c = m_b + T;                                     // [T] candidates, then output base
+    // All token traffic goes through one shared-memory array indexed with 32-bit element offsets.
+    uint16_t* const sm = reinterpret_cast<uint16_t*>(bpe_dyn);
+    const uint32_t team_base = (uint32_t)team * (bpe_team_bytes(W) / 2);
+    uint32_t cur = team_base + g;                // this lane's column in the buffer of live tokens
+    uint32_t nxt = cur + BUF;                    // ... and in the buffer the round writes
+    uint32_t* const xf = reinterpret_cast<uint32_t*>(sm + team_base + 2 * BUF);   // [T] entry of every lane's first pair (W > 1)
+    uint32_t* const xl = xf + T;                                                  // [T] entry of every lane's last pair  (W > 1)
     const int n_words = *list_count;
+    if (g == 0) {                                // what the last lane sees as "the next lane's first token"
+        sm[team_base + T] = (uint16_t)BPE_FILLER;
+        sm[team_base + BUF + T] = (uint16_t)BPE_FILLER;
+    }
 
     for (;;) {
         int wi;
@@ -220,79 +269,144 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             if (lane == 0) wi = atomicAdd(work_counter, 1);
             wi = __shfl_sync(BPE_FULL, wi, 0);
         } else {
-            if (g == 0) s_word[team][0] = atomicAdd(work_counter, 1);
+            if (g == 0) s_word[team] = atomicAdd(work_counter, 1);
             team_sync<W, BW>(team);
-            wi = s_word[team][0];
+            wi = s_word[team];
         }
         if (wi >= n_words) break;
         const int row = list[wi];
         const int64_t off = offsets[row];
         int n = (int)(offsets[row + 1] - off);               // 1 <= n <= T * P by classification
         uint32_t Pp = (uint32_t)(n + T - 1) / T;             // positions per lane: lane g owns [g Pp, (g + 1) Pp)
-        uint32_t inv = bpe_inv(Pp);
+        uint32_t inv = s_inv[Pp];
 
-        for (int i = g; i < n; i += T) {
-            const uint32_t l = bpe_div((uint32_t)i, Pp, inv);
-            cur[((uint32_t)i - l * Pp) * STRIDE + l] = s_btok[__ldg(bytes + off + i)];
+        // Every lane fetches its own chunk of the word as aligned 32-bit words (all requested before the
+        // first is used), maps the bytes to tokens and fills its column.  Positions behind the end of
+        // the word get the filler token, whose pairs never merge.
+        uint32_t tmax = 0;                                   // largest token id of the word
+        {
+            const uint32_t c0 = (uint32_t)g * Pp;            // first position of this lane
+            const uintptr_t a0 = reinterpret_cast<uintptr_t>(bytes + off + c0);
+            const uint32_t mis = (uint32_t)(a0 & 3u);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(a0 - mis);
+            const int first = (int)c0 - (int)mis;            // position of byte 0 of src[0]
+            uint32_t w[P / 4 + 1];
+#pragma unroll
+            for (int k = 0; k <= P / 4; ++k)                 // a word is read when it holds a byte of the word
+                w[k] = (4 * k < (int)(Pp + mis) && first + 4 * k < n && first + 4 * k + 3 >= 0) ? __ldg(src + k) : 0u;
+#pragma unroll
+            for (int k = 0; k < P / 4; ++k) {
+                if (4 * k < (int)Pp) {
+                    const uint32_t r = __funnelshift_r(w[k], w[k + 1], 8 * mis);
+#pragma unroll
+                    for (int bb = 0; bb < 4; ++bb) {
+                        const uint32_t tk = s_btok[(r >> (8 * bb)) & 0xFFu];
+                        const bool real = (int)c0 + 4 * k + bb < n;
+                        if (real) tmax = max(tmax, tk);
+                        sm[cur + (4 * k + bb) * STRIDE] = (uint16_t)(real ? tk : BPE_FILLER);
+                    }
+                }
+            }
         }
+        tmax = __reduce_max_sync(BPE_FULL, tmax);
+        if (W > 1 && lane == 0) s_red[warp] = tmax;
         team_sync<W, BW>(team);
+        if (W > 1) {
+#pragma unroll
+            for (int k = 0; k < W; ++k) tmax = max(tmax, s_red[team * W + k]);
+        }
+        bool all_hot = tmax < 32u;                           // stays true while the rounds create small ids only
 
         int round = 0;
         const int max_rounds = n + 2;
         for (; round < max_rounds; ++round) {
-            // ---- A: entries of the lane's pairs, the word's bound, "right neighbour ranks better" bits
-            const uint16_t* col = cur + g;
+            const int top = (int)Pp - 1, sh = 32 - (int)Pp;
             const int p0 = g * (int)Pp;
-            uint32_t val[P];
-            uint32_t emin = BPE_FULL, gt = 0, r_prev = BPE_NONE;
-            uint32_t a = col[0];
-            const uint32_t t_right = cur[g + 1];             // first token of the next lane (padding element after the last lane)
-#pragma unroll
-            for (int j = 0; j < P; ++j) {
-                if (j < (int)Pp) {
-                    uint32_t b = col[((j + 1) % P) * STRIDE];
-                    if (j + 1 == (int)Pp) b = t_right;
-                    uint32_t key = BPE_FULL, v = BPE_FULL;
-                    if (p0 + j + 1 < n) bpe_lookup(t, s_hot, a, b, key, v);
-                    const uint32_t r = v & 0xFFFFu;
-                    if (t.single_step) key = r == BPE_NONE ? BPE_FULL : (((r + 1u) << 16) | r);
-                    val[j] = v;
-                    emin = min(emin, key);
-                    if (j > 0) gt |= (r_prev > r ? 1u : 0u) << (j - 1);
-                    r_prev = r;
-                    a = b;
+            const int nv = n - 1 - p0;                       // pair j of this lane exists iff j < nv
+            // the next lane's first token becomes this lane's slot Pp, so that every slot finds its right neighbour one slot up
+            sm[cur + Pp * STRIDE] = sm[cur + 1];
+            team_sync<W, BW>(team);
+
+            // ---- A: entries of the lane's pairs, the word's bound, "right neighbour ranks better" bits.
+            // While every token of the word is a small id all pairs come from the shared-memory table and
+            // the slots are straight-line code; afterwards each lane takes the table its pair needs.
+            uint32_t val[P + 1];                             // x word of every pair's entry: (rank << 16) | created id
+            uint32_t gt = 0;                                 // bit j: the pair right of slot j's ranks better
+            uint32_t emin = BPE_FULL;
+#define BPE_A_TAIL(J)                                                                         \
+                    val[J] = e.x;                                                             \
+                    emin = min(emin, e.y);                                                    \
+                    if (e.x > val[J + 1]) gt |= 1u << J;
+            if (all_hot) {
+                switch (Pp) {
+#define BPE_A(J)                                                                              \
+                    case J + 1: {                                                             \
+                        const uint32_t a = sm[cur + J * STRIDE], b = sm[cur + (J + 1) * STRIDE]; \
+                        const uint2 e = s_hot[a * BPE_HOT_STRIDE + b];   /* the filler's pairs are empty */ \
+                        BPE_A_TAIL(J)                                                         \
+                    }
+                    BPE_SLOTS_DOWN(BPE_A)
+#undef BPE_A
+                    default: break;
+                }
+            } else {
+                switch (Pp) {
+#define BPE_A(J)                                                                              \
+                    case J + 1: {                                                             \
+                        const uint32_t a = sm[cur + J * STRIDE], b = sm[cur + (J + 1) * STRIDE]; \
+                        const bool hot = (a | b) < 32u;                                       \
+                        uint2 e = make_uint2(BPE_FULL, BPE_FULL);                             \
+                        if (J < nv && hot) e = s_hot[a * BPE_HOT_STRIDE + b];                 \
+                        if (J < nv && !hot) e = bpe_cold_entry(t, a, b);                      \
+                        BPE_A_TAIL(J)                                                         \
+                    }
+                    BPE_SLOTS_DOWN(BPE_A)
+#undef BPE_A
+                    default: break;
                 }
             }
-            const uint32_t r_first = val[0] & 0xFFFFu, r_last = r_prev;
+#undef BPE_A_TAIL
+            uint32_t v_top = val[0];                         // the entry of the last slot, whichever register holds it
+            switch (top) {
+#define BPE_T(J) case J: v_top = val[J]; break;
+                BPE_SLOTS_DOWN(BPE_T)
+#undef BPE_T
+                default: break;
+            }
+            gt &= (1u << top) - 1u;                          // the last slot was compared with nothing; set below
+            const uint32_t v_first = val[0];
             emin = __reduce_min_sync(BPE_FULL, emin);
-            uint32_t r_nf, r_pl;                             // the next lane's first rank, the previous lane's last rank
+            uint32_t v_nf, v_pl;                             // the next lane's first entry, the previous lane's last entry
             if (W == 1) {
-                r_nf = __shfl_down_sync(BPE_FULL, r_first, 1);
-                r_pl = __shfl_up_sync(BPE_FULL, r_last, 1);
-                if (lane == 31) r_nf = BPE_NONE;
-                if (lane == 0) r_pl = BPE_NONE;
+                v_nf = __shfl_down_sync(BPE_FULL, v_first, 1);
+                v_pl = __shfl_up_sync(BPE_FULL, v_top, 1);
+                if (lane == 31) v_nf = BPE_FULL;
+                if (lane == 0) v_pl = BPE_FULL;
             } else {
-                xf[g] = (uint16_t)r_first;
-                xl[g] = (uint16_t)r_last;
+                xf[g] = v_first;
+                xl[g] = v_top;
                 if (lane == 0) s_red[warp] = emin;
                 team_sync<W, BW>(team);
 #pragma unroll
                 for (int k = 0; k < W; ++k) emin = min(emin, s_red[team * W + k]);
-                r_nf = g + 1 < T ? (uint32_t)xf[g + 1] : BPE_NONE;
-                r_pl = g > 0 ? (uint32_t)xl[g - 1] : BPE_NONE;
+                v_nf = g + 1 < T ? xf[g + 1] : BPE_FULL;
+                v_pl = g > 0 ? xl[g - 1] : BPE_FULL;
             }
             if (emin == BPE_FULL) break;                     // no pair can merge: done (uniform over the team)
-            const uint32_t B = emin >> 16;
+            const uint32_t Bs = emin & 0xFFFF0000u;          // rank < B  <=>  entry < B << 16
+            all_hot = all_hot && (emin >> 16) <= t.hot_ranks;
 
             // ---- B: candidate and link masks of the lane's positions
-            const int top = (int)Pp - 1, sh = 32 - (int)Pp;
-            const uint32_t full = BPE_FULL >> sh;
-            gt |= (r_last > r_nf ? 1u : 0u) << top;
+            if (v_top > v_nf) gt |= 1u << top;
             uint32_t cand = 0;
-#pragma unroll
-            for (int j = 0; j < P; ++j)
-                if (j < (int)Pp) cand |= ((val[j] & 0xFFFFu) < B ? 1u : 0u) << j;
-            const uint32_t leq = (~(gt << 1) & ~1u) | (r_pl <= r_first ? 1u : 0u);   // bit j: rank(j-1) <= rank(j)
+            switch (Pp) {
+#define BPE_B(J) case J + 1: if (val[J] < Bs) cand |= 1u << J;
+                BPE_SLOTS_DOWN(BPE_B)
+#undef BPE_B
+                default: break;
+            }
+            const uint32_t full = BPE_FULL >> sh;
+            const uint32_t leq = (~(gt << 1) & ~1u) | (v_pl <= v_first ? 1u : 0u);   // bit j: rank(j-1) <= rank(j)
             const uint32_t link_r = cand & gt;               // the right neighbour is a candidate that goes first
             const uint32_t link_l = cand & leq;              // the left neighbour is a candidate that goes first
             const int len = min(max(n - p0, 0), (int)Pp);
@@ -311,7 +425,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                     const uint32_t any = __ballot_sync(BPE_FULL, sel != 0u);
                     sel = lane == __ffs(any) - 1 ? (sel & (0u - sel)) : 0u;
                 }
-                uint32_t prev = __shfl_up_sync(BPE_FULL, (sel >> top) & 1u, 1);
+                uint32_t prev = __shfl_up_sync(BPE_FULL, sel >> top, 1);
                 if (lane == 0) prev = 0u;
                 kept = valid & ~((sel << 1) | prev);
                 const int x = __popc(kept);
@@ -324,72 +438,92 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 q0 = incl - x;
                 n_new = __shfl_sync(BPE_FULL, incl, 31);
             } else {
-                m_a[g] = link_r; m_b[g] = link_l; m_c[g] = cand;
+                // every warp works on its own 32 lanes; what crosses warps are the blocks' carry functions
+                // (first barrier) and their survivor counts with the border bits (second barrier)
+                uint32_t fn_r, fn_l;
+                const ChainPrep pr = chain_prepare<true>(__brev(link_r) >> sh, top, full, lane, fn_r);
+                const ChainPrep pl = chain_prepare<false>(link_l, top, full, lane, fn_l);
+                const uint32_t any_cand = t.single_step ? __ballot_sync(BPE_FULL, cand != 0u) : 0u;
+                if (lane == 0) s_fn[warp] = fn_r | (fn_l << 2) | (any_cand ? 16u : 0u);
                 team_sync<W, BW>(team);
-                if (tw == 0) {
-                    bool carry = false;
-                    for (int b = W - 1; b >= 0; --b) {       // right walks, last lanes first
-                        const int gg = b * 32 + lane;
-                        m_a[gg] = __brev(chain_parity<true>(__brev(m_a[gg]) >> sh, top, full, carry, lane) << sh);
-                    }
-                    __syncwarp();
-                    carry = false;
-                    uint32_t sel_carry = 0;                  // was the last pair of the lane before the block selected
-                    int base = 0;
-                    bool took = false;
-                    for (int b = 0; b < W; ++b) {
-                        const int gg = b * 32 + lane;
-                        const uint32_t odd_l = chain_parity<false>(m_b[gg], top, full, carry, lane);
-                        uint32_t s = m_c[gg] & ~odd_l & ~m_a[gg];
-                        if (t.single_step) {
-                            const uint32_t any = __ballot_sync(BPE_FULL, s != 0u);
-                            s = (!took && lane == __ffs(any) - 1) ? (s & (0u - s)) : 0u;
-                            took = took || any != 0u;
-                        }
-                        uint32_t prev = __shfl_up_sync(BPE_FULL, (s >> top) & 1u, 1);
-                        if (lane == 0) prev = sel_carry;
-                        sel_carry = __shfl_sync(BPE_FULL, (s >> top) & 1u, 31);
-                        const int ln = min(max(n - gg * (int)Pp, 0), (int)Pp);
-                        const uint32_t vd = ln >= 32 ? BPE_FULL : ((1u << ln) - 1u);
-                        const uint32_t kp = vd & ~((s << 1) | prev);
-                        const int x = __popc(kp);
-                        int incl = x;
-#pragma unroll
-                        for (int d = 1; d < 32; d <<= 1) {
-                            const int y = __shfl_up_sync(BPE_FULL, incl, d);
-                            if (lane >= d) incl += y;
-                        }
-                        m_a[gg] = s; m_b[gg] = kp; m_c[gg] = (uint32_t)(base + incl - x);
-                        base += __shfl_sync(BPE_FULL, incl, 31);
-                    }
-                    if (lane == 0) s_word[team][1] = base;
+                bool carry_r = false, carry_l = false, earlier = false;
+                for (int k = W - 1; k > tw; --k) carry_r = carry_apply(s_fn[team * W + k] & 3u, carry_r) != 0u;
+                for (int k = 0; k < tw; ++k) {
+                    const uint32_t f = s_fn[team * W + k];
+                    carry_l = carry_apply((f >> 2) & 3u, carry_l) != 0u;
+                    earlier = earlier || (f & 16u);
                 }
+                const uint32_t odd_r = __brev(chain_finish<true>(pr, carry_r, lane) << sh);
+                const uint32_t odd_l = chain_finish<false>(pl, carry_l, lane);
+                sel = cand & ~odd_l & ~odd_r;
+                if (t.single_step)                           // only the leftmost pair of the lowest rank
+                    sel = (!earlier && lane == __ffs(any_cand) - 1) ? (cand & (0u - cand)) : 0u;
+                uint32_t prev = __shfl_up_sync(BPE_FULL, sel >> top, 1);
+                if (lane == 0) prev = 0u;                    // corrected below from the block before
+                kept = valid & ~((sel << 1) | prev);
+                const int x = __popc(kept);
+                int incl = x;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int y = __shfl_up_sync(BPE_FULL, incl, d);
+                    if (lane >= d) incl += y;
+                }
+                const uint32_t first_valid = __shfl_sync(BPE_FULL, valid & 1u, 0);
+                if (lane == 31) s_blk[warp] = (uint32_t)incl | ((sel >> top) << 16) | (first_valid << 17);
                 team_sync<W, BW>(team);
-                sel = m_a[g]; kept = m_b[g]; q0 = (int)m_c[g];
-                n_new = s_word[team][1];
+                // lane k looks at block k: its count drops by one when the block before it merged across the border
+                const uint32_t w = lane < W ? s_blk[team * W + lane] : 0u;
+                uint32_t lost = __shfl_up_sync(BPE_FULL, (w >> 16) & 1u, 1);
+                if (lane == 0) lost = 0u;
+                lost &= (w >> 17) & 1u;
+                const int tot = (int)(w & 0xFFFFu) - (int)lost;
+                int bincl = tot;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int y = __shfl_up_sync(BPE_FULL, bincl, d);
+                    if (lane >= d) bincl += y;
+                }
+                const int base = __shfl_sync(BPE_FULL, bincl - tot, tw);
+                n_new = __shfl_sync(BPE_FULL, bincl, 31);
+                const bool mine_lost = __shfl_sync(BPE_FULL, lost, tw) != 0u;
+                if (mine_lost && lane == 0) kept &= ~1u;
+                q0 = base + incl - x - ((mine_lost && lane > 0) ? 1 : 0);
             }
 
-            // ---- C: merge, and deal the survivors out again in the other buffer
-            const uint32_t Pn = (uint32_t)(n_new + T - 1) / T, inv_n = bpe_inv(Pn);
-            uint32_t q = (uint32_t)q0;
-#pragma unroll
-            for (int j = 0; j < P; ++j) {
-                if (j < (int)Pp && ((kept >> j) & 1u)) {
-                    uint32_t v = col[j * STRIDE];
-                    if ((sel >> j) & 1u) v = val[j] >> 16;
-                    const uint32_t l = bpe_div(q, Pn, inv_n);
-                    nxt[(q - l * Pn) * STRIDE + l] = (uint16_t)v;
-                    ++q;
+            // ---- C: merge, and deal the survivors out again in the other buffer, last slot first.
+            // Position q goes to lane l = q / Pn, slot q - l Pn: element q STRIDE - l (Pn STRIDE - 1).
+            const uint32_t Pn = (uint32_t)(n_new + T - 1) / T, inv_n = s_inv[Pn];
+            const uint32_t back = Pn * STRIDE - 1;
+            const uint32_t dst = nxt - g;                    // start of the buffer the round writes
+            uint32_t q = (uint32_t)q0 + (uint32_t)__popc(kept);
+            switch (Pp) {
+#define BPE_C(J)                                                                              \
+                case J + 1: {                                                                 \
+                    const bool keep_ = (kept & (1u << J)) != 0u;                              \
+                    if (keep_) --q;                                                           \
+                    const uint32_t l_ = __umulhi(2u * q + 1u, inv_n);                         \
+                    const uint16_t v_ = (sel & (1u << J)) ? (uint16_t)val[J] : sm[cur + J * STRIDE]; \
+                    if (keep_) sm[dst + q * STRIDE - l_ * back] = v_;                         \
+                }
+                BPE_SLOTS_DOWN(BPE_C)
+#undef BPE_C
+                default: break;
+            }
+            {                                                // filler behind the new end, up to the lanes' common slot count
+                const uint32_t pt = (uint32_t)n_new + (uint32_t)g;
+                if (pt < Pn * T) {
+                    const uint32_t l_ = __umulhi(2u * pt + 1u, inv_n);
+                    sm[dst + pt * STRIDE - l_ * back] = (uint16_t)BPE_FILLER;
                 }
             }
             team_sync<W, BW>(team);
-            uint16_t* sw = cur; cur = nxt; nxt = sw;
+            const uint32_t sw = cur; cur = nxt; nxt = sw;
             n = n_new; Pp = Pn; inv = inv_n;
         }
 
         for (int q = g; q < n; q += T) {
-            const uint32_t l = bpe_div((uint32_t)q, Pp, inv);
-            out_tok[off + q] = cur[((uint32_t)q - l * Pp) * STRIDE + l];
+            const uint32_t l = __umulhi(2u * (uint32_t)q + 1u, inv);
+            out_tok[off + q] = sm[cur - g + ((uint32_t)q - l * Pp) * STRIDE + l];
         }
         if (g == 0) {
             counts[row] = n;
@@ -398,6 +532,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
         team_sync<W, BW>(team);
     }
 }
+#undef BPE_SLOTS_DOWN
 
 // Words beyond the lanes kernel's capacity: one block per word, state in global memory.  The
 // tokens live in place in the output area (uint16 at the input offsets); ranks and the three mask
@@ -456,9 +591,9 @@ bpe_long_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ o
                 const int i = g * 32 + lane;
                 uint32_t r = BPE_NONE, fut = BPE_NONE;
                 if (i + 1 < n) {
-                    uint32_t key, v;
-                    bpe_lookup(t, s_hot, tok[i], tok[i + 1], key, v);
-                    r = key & 0xFFFFu; fut = key >> 16;
+                    const uint32_t a = tok[i], b = tok[i + 1];
+                    const uint2 e = (a | b) < 32u ? s_hot[a * 32u + b] : bpe_cold_entry(t, a, b);
+                    r = e.x >> 16; fut = e.y >> 16;
                 }
                 if (i < n) rk[i] = (uint16_t)r;
                 gmin = min(gmin, r);

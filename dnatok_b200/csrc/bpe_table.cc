@@ -80,8 +80,10 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
         }
     }
     auto entry = [&](int32_t r) {
-        const uint64_t lo = ((uint64_t)a[r] << 16) | (uint64_t)r;
-        const uint64_t hi = ((uint64_t)o[r] << 16) | (uint64_t)t->future[r];
+        // without usable future ranks (not batch-safe) the bound is "just above this rank": one rank per round
+        const uint64_t f = safe ? (uint64_t)t->future[r] : (uint64_t)r + 1;
+        const uint64_t lo = ((uint64_t)r << 16) | (uint64_t)o[r];
+        const uint64_t hi = ((uint64_t)a[r] << 16) | f;
         return lo | (hi << 32);
     };
     t->slots.assign(slots.size(), ~0ull);
@@ -91,7 +93,14 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
     // vocabulary): one shared-memory load answers the whole entry
     t->hot.assign(32 * 32, ~0ull);
     for (int32_t r = 0; r < n; ++r)
-        if (a[r] < 32 && b[r] < 32) t->hot[a[r] * 32 + b[r]] = entry(r);
+        if (a[r] < 32 && b[r] < 32) {
+            const uint64_t e = entry(r);
+            const uint64_t key = ((e >> 32) & 0xFFFFull) << 16 | (uint64_t)r;      // (F << 16) | rank
+            t->hot[a[r] * 32 + b[r]] = (e & 0xFFFFFFFFull) | (key << 32);
+        }
+    t->hot_ranks = (uint32_t)n;
+    for (int32_t r = n - 1; r >= 0; --r)
+        if (o[r] >= 32) t->hot_ranks = (uint32_t)r;
     t->byte_tok.resize(256);
     for (int i = 0; i < 256; ++i) t->byte_tok[i] = (uint16_t)byte_ids[i];
     t->n_tokens = n_tokens;

@@ -2,7 +2,7 @@
 //
 // The table is a perfect hash of the pair (left id, right id) by row displacement: every left
 // token `a` owns a row offset disp[a]; the pair (a, b) lives in slots[disp[a] + b], a 64-bit
-// entry: low word (a << 16) | rank, high word (created id << 16) | future rank.  A lookup is two
+// entry: low word (rank << 16) | created id, high word (a << 16) | future rank.  A lookup is two
 // dependent loads and an equality test, with no probing and no false positives, and brings
 // everything a merge needs.  Ids are Hugging Face ids, so the kernels emit final ids with no remap.
 // (The reference keeps a cuco::static_map keyed by a 64-bit pair and remaps kernel ids to HF
@@ -17,11 +17,12 @@ namespace dnatok {
 
 struct BpeHostTable {
     std::vector<uint32_t> disp;        // [n_tokens]
-    std::vector<uint64_t> slots;       // [max disp + n_tokens]; low 32 bits (a << 16) | rank, high 32 bits
-                                       // (created id << 16) | future rank; all ones when empty
+    std::vector<uint64_t> slots;       // [max disp + n_tokens]; low 32 bits (rank << 16) | created id, high 32 bits
+                                       // (a << 16) | future rank (rank + 1 when the table is not batch-safe); all ones when empty
     std::vector<uint16_t> merge_out;   // [n_merges] id created by each rank
     std::vector<uint16_t> future;      // [n_merges] lowest rank of any pair containing that id, 0xFFFF if none
-    std::vector<uint64_t> hot;         // [32 * 32] pairs of ids < 32 in the slot format, all ones if no merge
+    std::vector<uint64_t> hot;         // [32 * 32] pairs of ids < 32: low word as in slots, high word (future rank << 16) | rank; all ones if no merge
+    uint32_t hot_ranks = 0;            // every rank below this creates an id < 32
     std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
     uint32_t n_tokens = 0;
     uint32_t n_merges = 0;

@@ -15,13 +15,14 @@ tokenizer it cannot take), so it can be assigned to ``DNATok.bpe_backend`` uncha
 reference it never adds special tokens.
 
 ``DnatokBpeKernel`` mirrors the native slot (``src/dnatok_bpe_kernel/__init__.py:81-136``):
-``tokenize_batch(texts) -> (ids int32 [B, T_max], lengths int32 [B])`` on the GPU.  Ids are
-Hugging Face ids already (the reference returns kernel ids and remaps afterwards), the tail of
-each row is zero-filled as in the reference (``dnatok_bpe.cu:899``), and the returned tensors are
-freshly allocated rather than views into a workspace, so ``clone`` is accepted and ignored.
+``DnatokBpeKernel(merges_path, max_iters)``, ``vocab_size()``, ``id_to_token(i)`` and
+``tokenize_batch(texts) -> (ids int32 [B, T_max], lengths int32 [B])`` on the GPU, in the
+reference's internal id space when built from a merges file.  The tail of each row is zero-filled
+as in the reference (``dnatok_bpe.cu:899``), and the returned tensors are freshly allocated rather
+than views into a workspace, so ``clone`` is accepted and ignored.
 
 There is no length-based routing to a CPU tokenizer (reference ``:551-564``): every row goes
-through the GPU kernel; rows longer than the kernel's word limit raise.
+through the GPU kernel, whatever its length.
 """
 from __future__ import annotations
 
@@ -100,27 +101,88 @@ class GPUTokBPEBackend:
         return ids
 
 
-class DnatokBpeKernel:
-    """``DnatokBpeKernel(merges_path, max_iters=...)`` of the reference takes a merges.txt; here the
-    tables come from a tokenizer spec (``from_spec``) or from merges.txt plus the vocab that
-    names the tokens (``from_merges_file``)."""
+def _spec_from_merges_file(merges_path: str):
+    """Tables in the id space of the reference's native class: ids 0..255 are the byte symbols, then
+    every token named in merges.txt gets the next id at its first appearance (left operand, right
+    operand, result), line by line; a line's rank is its index among the merge lines
+    (``build_vocab_from_merges``, reference ``src/dnatok_bpe_kernel/dnatok_bpe.cu:761-791``).  The
+    first line is the ``#version`` header; blank lines and ``#`` lines are skipped."""
+    from .tables import Specials, TokenizerSpec
+    id_to_token: List[str] = [chr(b) for b in range(256)]
+    token_to_id = {t: i for i, t in enumerate(id_to_token)}
 
-    def __init__(self, spec, max_iters: int = 1024):
+    def add(t: str) -> int:
+        i = token_to_id.get(t)
+        if i is None:
+            i = token_to_id[t] = len(id_to_token)
+            id_to_token.append(t)
+        return i
+
+    a, b, o = [], [], []
+    with open(merges_path, "r", encoding="utf-8") as f:
+        lines = f.read().split("\n")
+    if not lines or (len(lines) == 1 and not lines[0]):
+        raise RuntimeError("Empty merges file")
+    for line in lines[1:]:
+        if not line or line[0] == "#":
+            continue
+        parts = line.split()
+        if len(parts) < 2:
+            continue
+        x, y = parts[0], parts[1]
+        a.append(add(x)); b.append(add(y)); o.append(add(x + y))
+    if not a:
+        raise RuntimeError("merges file holds no merges: %s" % merges_path)
+    spec = TokenizerSpec("bpe", Specials(pad_id=0, unk_id=0), len(id_to_token), np.arange(256, dtype=np.int32),
+                         merge_a=np.asarray(a, np.int32), merge_b=np.asarray(b, np.int32),
+                         merge_out=np.asarray(o, np.int32), vocab=dict(token_to_id))
+    return spec, id_to_token
+
+
+class DnatokBpeKernel:
+    """The native slot: ``DnatokBpeKernel(merges_path, max_iters=1024)`` as in the reference
+    (``src/dnatok_bpe_kernel/__init__.py:81-136`` over the pybind class
+    ``DNATokBPE(merges_path, byte_to_id_lut, max_iters)``, ``dnatok_bpe.cu:1042-1055``), with
+    ``vocab_size()``, ``id_to_token(i)`` and ``tokenize_batch(texts, clone=False)``.  Built from a
+    merges file the ids are the reference's internal ids (byte symbols, then tokens in file order),
+    which its callers remap to Hugging Face ids; ``from_spec`` builds the same object directly in
+    Hugging Face id space from a tokenizer spec."""
+
+    def __init__(self, merges_path, max_iters: int = 1024):
         import copy
         from .tokenizer import B200Tokenizer
-        spec = copy.copy(spec)
-        spec.specials = copy.copy(spec.specials)
-        spec.specials.pad_id = 0                      # the reference zero-fills the tail of each row
+        if isinstance(merges_path, (str, bytes)) or hasattr(merges_path, "__fspath__"):
+            import os
+            path = os.fspath(merges_path)
+            if not os.path.isfile(path):
+                raise RuntimeError("Failed to open merges file: %s" % path)
+            spec, self._id_to_token = _spec_from_merges_file(path)
+        else:
+            spec = copy.copy(merges_path)
+            spec.specials = copy.copy(spec.specials)
+            spec.specials.pad_id = 0                  # the reference zero-fills the tail of each row
+            inv = {i: t for t, i in spec.vocab.items()}
+            self._id_to_token = [inv.get(i, "") for i in range(spec.vocab_size)]
         self._tok = B200Tokenizer(spec)
         self._tok.padding_side = "right"
-        self.max_iters = max_iters        # accepted for signature parity; the pass bound is the word length
+        self.max_iters = int(max_iters)   # accepted for signature parity; the pass bound is the word length
 
     @classmethod
     def from_spec(cls, spec, max_iters: int = 1024) -> "DnatokBpeKernel":
         return cls(spec, max_iters)
 
+    @classmethod
+    def from_merges_file(cls, merges_path: str, max_iters: int = 1024) -> "DnatokBpeKernel":
+        return cls(merges_path, max_iters)
+
     def vocab_size(self) -> int:
-        return self._tok.vocab_size
+        return len(self._id_to_token)
+
+    def id_to_token(self, idx: int) -> str:
+        idx = int(idx)
+        if idx < 0 or idx >= len(self._id_to_token):
+            raise IndexError("token id %d outside the vocabulary" % idx)
+        return self._id_to_token[idx]
 
     def tokenize_batch(self, seqs: List[str], clone: bool = False):
         import torch

@@ -10,7 +10,7 @@ Writes ``tests/golden/golden.json`` (hashes + small literal cases) from three so
     (``NTv3Tokenizer``, ``Evo2ByteTokenizer``, ``CharTokenizer``);
   * the reference's normaliser known answers (``tests/test_gputok_bpe_backend.py:319-425``),
     re-derived by calling its ``_compile_normalizer_step``.
-The reference cannot travel to the GPU box; these vectors can.
+The reference is needed only here; the tests read the vectors.
 """
 import hashlib
 import json
@@ -158,6 +158,25 @@ def main():
                                              "mask_dtype": str(m2.dtype)})
             api["cases"].append(case)
     G["dnatok_api"] = api
+
+    # the reference's constructor flags normalize_case / handle_invalid_chars and its token_len
+    # attribute (its own tests: tests/test_benchmark_correctness.py:146-200), both padding sides
+    flag_seqs = ["AcGt", "acgt", "ACGT", "ACXGT", "AC$GT", "acgtnNRYkm", "TTTTTTTTTTTTT", "a", "ACGTACGTACGTNACGTACxACGTAC",
+                 "gattacaGATTACAgattacaN", "ACGTAC" * 3 + "acgtac" + "ACGTA"]
+    flags = {"seqs": flag_seqs, "cases": []}
+    for tname in ("char", "kmer6"):
+        for side in ("left", "right"):
+            for norm_case, handle in ((True, False), (False, True), (True, True)):
+                for token_len in (None, 40):
+                    hlp = DNATok(_Embedder(toks[tname]), padding_side=side, normalize_case=norm_case,
+                                 handle_invalid_chars=handle)
+                    hlp.discover()
+                    hlp.token_len = token_len
+                    ids = hlp.encode_batch_to_ids(flag_seqs)
+                    flags["cases"].append({"tokenizer": tname, "padding_side": side, "normalize_case": norm_case,
+                                           "handle_invalid_chars": handle, "token_len": token_len,
+                                           "ids": ids.tolist()})
+    G["dnatok_flags"] = flags
 
     # the reference's own tokenizer classes (src/dnatok_compat.py:135-238): the table this package
     # discovers from each by probing, and the class's own ids for every non-empty adversarial string
