@@ -71,6 +71,8 @@ struct BpeDeviceTable {
     const uint16_t* byte_tok;    // [256]
     int32_t single_step;
     uint32_t hot_ranks;          // every rank below this creates an id < 32
+    uint32_t bytes_hot;          // 1: every initial symbol is an id < 32
+    uint32_t filler;             // one past the largest token id: a token whose pairs never merge (disp and slots have room for it)
 };
 
 // One table entry: x = (rank << 16) | created id, y = (left id << 16) | F.  Ranks compare like the x
@@ -257,10 +259,6 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
     uint32_t* const xf = reinterpret_cast<uint32_t*>(sm + team_base + 2 * BUF);   // [T] entry of every lane's first pair (W > 1)
     uint32_t* const xl = xf + T;                                                  // [T] entry of every lane's last pair  (W > 1)
     const int n_words = *list_count;
-    if (g == 0) {                                // what the last lane sees as "the next lane's first token"
-        sm[team_base + T] = (uint16_t)BPE_FILLER;
-        sm[team_base + BUF + T] = (uint16_t)BPE_FILLER;
-    }
 
     for (;;) {
         int wi;
@@ -280,10 +278,14 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
         uint32_t Pp = (uint32_t)(n + T - 1) / T;             // positions per lane: lane g owns [g Pp, (g + 1) Pp)
         uint32_t inv = s_inv[Pp];
 
+        // While every token of the word is a small id (all_hot) the pairs come from the shared-memory
+        // table and the filler behind the end of the word is that table's empty row 32; afterwards they
+        // come from the table in global memory and the filler is the id one past the vocabulary.
+        bool all_hot = t.bytes_hot != 0u;
+        uint32_t filler = all_hot ? BPE_FILLER : t.filler;
+        if (g == 0) sm[cur + T] = (uint16_t)filler;          // what the last lane sees as "the next lane's first token"
         // Every lane fetches its own chunk of the word as aligned 32-bit words (all requested before the
-        // first is used), maps the bytes to tokens and fills its column.  Positions behind the end of
-        // the word get the filler token, whose pairs never merge.
-        uint32_t tmax = 0;                                   // largest token id of the word
+        // first is used), maps the bytes to tokens and fills its column.
         {
             const uint32_t c0 = (uint32_t)g * Pp;            // first position of this lane
             const uintptr_t a0 = reinterpret_cast<uintptr_t>(bytes + off + c0);
@@ -301,28 +303,18 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 #pragma unroll
                     for (int bb = 0; bb < 4; ++bb) {
                         const uint32_t tk = s_btok[(r >> (8 * bb)) & 0xFFu];
-                        const bool real = (int)c0 + 4 * k + bb < n;
-                        if (real) tmax = max(tmax, tk);
-                        sm[cur + (4 * k + bb) * STRIDE] = (uint16_t)(real ? tk : BPE_FILLER);
+                        sm[cur + (4 * k + bb) * STRIDE] = (uint16_t)((int)c0 + 4 * k + bb < n ? tk : filler);
                     }
                 }
             }
         }
-        tmax = __reduce_max_sync(BPE_FULL, tmax);
-        if (W > 1 && lane == 0) s_red[warp] = tmax;
         team_sync<W, BW>(team);
-        if (W > 1) {
-#pragma unroll
-            for (int k = 0; k < W; ++k) tmax = max(tmax, s_red[team * W + k]);
-        }
-        bool all_hot = tmax < 32u;                           // stays true while the rounds create small ids only
 
         int round = 0;
         const int max_rounds = n + 2;
         for (; round < max_rounds; ++round) {
             const int top = (int)Pp - 1, sh = 32 - (int)Pp;
             const int p0 = g * (int)Pp;
-            const int nv = n - 1 - p0;                       // pair j of this lane exists iff j < nv
             // the next lane's first token becomes this lane's slot Pp, so that every slot finds its right neighbour one slot up
             sm[cur + Pp * STRIDE] = sm[cur + 1];
             team_sync<W, BW>(team);
@@ -354,10 +346,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 #define BPE_A(J)                                                                              \
                     case J + 1: {                                                             \
                         const uint32_t a = sm[cur + J * STRIDE], b = sm[cur + (J + 1) * STRIDE]; \
-                        const bool hot = (a | b) < 32u;                                       \
-                        uint2 e = make_uint2(BPE_FULL, BPE_FULL);                             \
-                        if (J < nv && hot) e = s_hot[a * BPE_HOT_STRIDE + b];                 \
-                        if (J < nv && !hot) e = bpe_cold_entry(t, a, b);                      \
+                        const uint2 e = bpe_cold_entry(t, a, b);             /* the filler's pairs are empty */ \
                         BPE_A_TAIL(J)                                                         \
                     }
                     BPE_SLOTS_DOWN(BPE_A)
@@ -394,17 +383,18 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             }
             if (emin == BPE_FULL) break;                     // no pair can merge: done (uniform over the team)
             const uint32_t Bs = emin & 0xFFFF0000u;          // rank < B  <=>  entry < B << 16
-            all_hot = all_hot && (emin >> 16) <= t.hot_ranks;
 
             // ---- B: candidate and link masks of the lane's positions
             if (v_top > v_nf) gt |= 1u << top;
-            uint32_t cand = 0;
+            uint32_t cand = 0, vmax = 0;                     // vmax: the highest-ranking candidate's entry
             switch (Pp) {
-#define BPE_B(J) case J + 1: if (val[J] < Bs) cand |= 1u << J;
+#define BPE_B(J) case J + 1: if (val[J] < Bs) { cand |= 1u << J; vmax = max(vmax, val[J]); }
                 BPE_SLOTS_DOWN(BPE_B)
 #undef BPE_B
                 default: break;
             }
+            // the round creates small ids only if all its candidates rank below t.hot_ranks
+            const bool big = (vmax >> 16) >= t.hot_ranks && cand != 0u;
             const uint32_t full = BPE_FULL >> sh;
             const uint32_t leq = (~(gt << 1) & ~1u) | (v_pl <= v_first ? 1u : 0u);   // bit j: rank(j-1) <= rank(j)
             const uint32_t link_r = cand & gt;               // the right neighbour is a candidate that goes first
@@ -416,6 +406,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             uint32_t sel, kept;
             int q0, n_new;
             if (W == 1) {
+                all_hot = all_hot && !__any_sync(BPE_FULL, big);
                 bool carry = false;
                 const uint32_t odd_r = __brev(chain_parity<true>(__brev(link_r) >> sh, top, full, carry, lane) << sh);
                 carry = false;
@@ -444,9 +435,12 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 const ChainPrep pr = chain_prepare<true>(__brev(link_r) >> sh, top, full, lane, fn_r);
                 const ChainPrep pl = chain_prepare<false>(link_l, top, full, lane, fn_l);
                 const uint32_t any_cand = t.single_step ? __ballot_sync(BPE_FULL, cand != 0u) : 0u;
-                if (lane == 0) s_fn[warp] = fn_r | (fn_l << 2) | (any_cand ? 16u : 0u);
+                const bool any_big = __any_sync(BPE_FULL, big);
+                if (lane == 0) s_fn[warp] = fn_r | (fn_l << 2) | (any_cand ? 16u : 0u) | (any_big ? 32u : 0u);
                 team_sync<W, BW>(team);
                 bool carry_r = false, carry_l = false, earlier = false;
+#pragma unroll
+                for (int k = 0; k < W; ++k) all_hot = all_hot && !(s_fn[team * W + k] & 32u);
                 for (int k = W - 1; k > tw; --k) carry_r = carry_apply(s_fn[team * W + k] & 3u, carry_r) != 0u;
                 for (int k = 0; k < tw; ++k) {
                     const uint32_t f = s_fn[team * W + k];
@@ -510,11 +504,13 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 default: break;
             }
             {                                                // filler behind the new end, up to the lanes' common slot count
+                filler = all_hot ? BPE_FILLER : t.filler;
                 const uint32_t pt = (uint32_t)n_new + (uint32_t)g;
                 if (pt < Pn * T) {
                     const uint32_t l_ = __umulhi(2u * pt + 1u, inv_n);
-                    sm[dst + pt * STRIDE - l_ * back] = (uint16_t)BPE_FILLER;
+                    sm[dst + pt * STRIDE - l_ * back] = (uint16_t)filler;
                 }
+                if (g == 0) sm[dst + T] = (uint16_t)filler;  // the column behind the last lane
             }
             team_sync<W, BW>(team);
             const uint32_t sw = cur; cur = nxt; nxt = sw;

@@ -63,12 +63,14 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
             }
             if (ok) break;
         }
-        size_t need = d + n_tokens;           // any b < n_tokens must index inside the array
+        size_t need = d + n_tokens + 1;       // any b <= n_tokens (the kernels' filler id) must index inside the array
         if (need > slots.size()) slots.resize(need, 0xFFFFFFFFu);
         for (auto& e : row) slots[d + e.first] = (ai << 16) | e.second;
         disp[ai] = (uint32_t)d;
     }
 
+    disp.push_back(0);                        // the filler id: no slot carries it as left id
+    if (slots.size() < (size_t)n_tokens + 1) slots.resize((size_t)n_tokens + 1, 0xFFFFFFFFu);
     t->disp.swap(disp);
     t->merge_out.resize(n);
     for (int32_t r = 0; r < n; ++r) t->merge_out[r] = (uint16_t)o[r];
@@ -98,6 +100,8 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
             const uint64_t key = ((e >> 32) & 0xFFFFull) << 16 | (uint64_t)r;      // (F << 16) | rank
             t->hot[a[r] * 32 + b[r]] = (e & 0xFFFFFFFFull) | (key << 32);
         }
+    t->bytes_hot = true;
+    for (int i = 0; i < 256; ++i) t->bytes_hot = t->bytes_hot && byte_ids[i] < 32;
     t->hot_ranks = (uint32_t)n;
     for (int32_t r = n - 1; r >= 0; --r)
         if (o[r] >= 32) t->hot_ranks = (uint32_t)r;

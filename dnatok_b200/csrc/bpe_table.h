@@ -16,13 +16,14 @@
 namespace dnatok {
 
 struct BpeHostTable {
-    std::vector<uint32_t> disp;        // [n_tokens]
+    std::vector<uint32_t> disp;        // [n_tokens + 1]; the last entry belongs to the filler id n_tokens, which no pair contains
     std::vector<uint64_t> slots;       // [max disp + n_tokens]; low 32 bits (rank << 16) | created id, high 32 bits
                                        // (a << 16) | future rank (rank + 1 when the table is not batch-safe); all ones when empty
     std::vector<uint16_t> merge_out;   // [n_merges] id created by each rank
     std::vector<uint16_t> future;      // [n_merges] lowest rank of any pair containing that id, 0xFFFF if none
     std::vector<uint64_t> hot;         // [32 * 32] pairs of ids < 32: low word as in slots, high word (future rank << 16) | rank; all ones if no merge
     uint32_t hot_ranks = 0;            // every rank below this creates an id < 32
+    bool bytes_hot = false;            // every initial symbol is an id < 32
     std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
     uint32_t n_tokens = 0;
     uint32_t n_merges = 0;

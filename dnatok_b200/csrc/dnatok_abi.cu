@@ -319,7 +319,7 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
                                                                        s.class_list, s.counts, status, class_mask);
     LAUNCH_CHECK("bpe_classify_kernel");
     BpeDeviceTable t{d.disp, reinterpret_cast<const uint2*>(d.slots), d.merge_out, reinterpret_cast<const uint2*>(d.hot),
-                     d.byte_tok, h->bpe.batch_safe ? 0 : 1, h->bpe.hot_ranks};
+                     d.byte_tok, h->bpe.batch_safe ? 0 : 1, h->bpe.hot_ranks, h->bpe.bytes_hot ? 1u : 0u, h->bpe.n_tokens};
     // Classes outside the mask are not launched; a row that falls into one is flagged by the classifier.
     // Longest class first: its few, slow words start while nothing else competes for the SMs.
     if ((class_mask >> BPE_LONG_CLASS) & 1u) {
