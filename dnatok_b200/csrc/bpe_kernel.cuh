@@ -204,6 +204,23 @@ __device__ __forceinline__ void team_sync(int team) {
     else asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(W * 32) : "memory");
 }
 
+// Shared-memory accesses by 32-bit address in the shared window: the lanes kernel keeps its buffer
+// addresses in registers and reaches every slot with a compile-time offset.
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((uint16_t)v) : "memory");
+}
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+
 // floor(x / d) for 1 <= d <= 32, x < 2^16: __umulhi(2 x + 1, ceil(2^31 / d)).
 __device__ __forceinline__ uint32_t bpe_inv(uint32_t d) { return (0x80000000u + d - 1u) / d; }
 
@@ -251,11 +268,13 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int team = warp / W, tw = warp % W;    // team, warp within team
     const int g = tw * 32 + lane;                // lane within team
-    // All token traffic goes through one shared-memory array indexed with 32-bit element offsets.
+    // All token traffic goes through shared-memory byte addresses held in registers.
+    constexpr uint32_t S2 = 2 * STRIDE;          // bytes between the slots of one lane
     uint16_t* const sm = reinterpret_cast<uint16_t*>(bpe_dyn);
     const uint32_t team_base = (uint32_t)team * (bpe_team_bytes(W) / 2);
-    uint32_t cur = team_base + g;                // this lane's column in the buffer of live tokens
-    uint32_t nxt = cur + BUF;                    // ... and in the buffer the round writes
+    const uint32_t hot_base = smem_u32(s_hot);
+    uint32_t cur = smem_u32(sm + team_base + g); // this lane's column in the buffer of live tokens
+    uint32_t nxt = cur + 2 * BUF;                // ... and in the buffer the round writes
     uint32_t* const xf = reinterpret_cast<uint32_t*>(sm + team_base + 2 * BUF);   // [T] entry of every lane's first pair (W > 1)
     uint32_t* const xl = xf + T;                                                  // [T] entry of every lane's last pair  (W > 1)
     const int n_words = *list_count;
@@ -283,7 +302,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
         // come from the table in global memory and the filler is the id one past the vocabulary.
         bool all_hot = t.bytes_hot != 0u;
         uint32_t filler = all_hot ? BPE_FILLER : t.filler;
-        if (g == 0) sm[cur + T] = (uint16_t)filler;          // what the last lane sees as "the next lane's first token"
+        if (g == 0) sts_u16(cur + 2 * T, filler);            // what the last lane sees as "the next lane's first token"
         // Every lane fetches its own chunk of the word as aligned 32-bit words (all requested before the
         // first is used), maps the bytes to tokens and fills its column.
         {
@@ -303,7 +322,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 #pragma unroll
                     for (int bb = 0; bb < 4; ++bb) {
                         const uint32_t tk = s_btok[(r >> (8 * bb)) & 0xFFu];
-                        sm[cur + (4 * k + bb) * STRIDE] = (uint16_t)((int)c0 + 4 * k + bb < n ? tk : filler);
+                        sts_u16(cur + (4 * k + bb) * S2, (int)c0 + 4 * k + bb < n ? tk : filler);
                     }
                 }
             }
@@ -316,7 +335,8 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             const int top = (int)Pp - 1, sh = 32 - (int)Pp;
             const int p0 = g * (int)Pp;
             // the next lane's first token becomes this lane's slot Pp, so that every slot finds its right neighbour one slot up
-            sm[cur + Pp * STRIDE] = sm[cur + 1];
+            uint32_t t_up = lds_u16(cur + 2);                // handed from slot to slot: the token one slot up
+            sts_u16(cur + Pp * S2, t_up);
             team_sync<W, BW>(team);
 
             // ---- A: entries of the lane's pairs, the word's bound, "right neighbour ranks better" bits.
@@ -333,8 +353,9 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 switch (Pp) {
 #define BPE_A(J)                                                                              \
                     case J + 1: {                                                             \
-                        const uint32_t a = sm[cur + J * STRIDE], b = sm[cur + (J + 1) * STRIDE]; \
-                        const uint2 e = s_hot[a * BPE_HOT_STRIDE + b];   /* the filler's pairs are empty */ \
+                        const uint32_t a = lds_u16(cur + J * S2), b = t_up;                   \
+                        const uint2 e = lds_u64(hot_base + (a * BPE_HOT_STRIDE + b) * 8u);   /* the filler's pairs are empty */ \
+                        t_up = a;                                                             \
                         BPE_A_TAIL(J)                                                         \
                     }
                     BPE_SLOTS_DOWN(BPE_A)
@@ -345,8 +366,9 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 switch (Pp) {
 #define BPE_A(J)                                                                              \
                     case J + 1: {                                                             \
-                        const uint32_t a = sm[cur + J * STRIDE], b = sm[cur + (J + 1) * STRIDE]; \
+                        const uint32_t a = lds_u16(cur + J * S2), b = t_up;                   \
                         const uint2 e = bpe_cold_entry(t, a, b);             /* the filler's pairs are empty */ \
+                        t_up = a;                                                             \
                         BPE_A_TAIL(J)                                                         \
                     }
                     BPE_SLOTS_DOWN(BPE_A)
@@ -485,10 +507,10 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             }
 
             // ---- C: merge, and deal the survivors out again in the other buffer, last slot first.
-            // Position q goes to lane l = q / Pn, slot q - l Pn: element q STRIDE - l (Pn STRIDE - 1).
+            // Position q goes to lane l = q / Pn, slot q - l Pn: byte 2 (q STRIDE - l (Pn STRIDE - 1)) of the buffer.
             const uint32_t Pn = (uint32_t)(n_new + T - 1) / T, inv_n = s_inv[Pn];
-            const uint32_t back = Pn * STRIDE - 1;
-            const uint32_t dst = nxt - g;                    // start of the buffer the round writes
+            const uint32_t back = 2 * (Pn * STRIDE - 1);
+            const uint32_t dst = nxt - 2 * g;                // start of the buffer the round writes
             uint32_t q = (uint32_t)q0 + (uint32_t)__popc(kept);
             switch (Pp) {
 #define BPE_C(J)                                                                              \
@@ -496,8 +518,8 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                     const bool keep_ = (kept & (1u << J)) != 0u;                              \
                     if (keep_) --q;                                                           \
                     const uint32_t l_ = __umulhi(2u * q + 1u, inv_n);                         \
-                    const uint16_t v_ = (sel & (1u << J)) ? (uint16_t)val[J] : sm[cur + J * STRIDE]; \
-                    if (keep_) sm[dst + q * STRIDE - l_ * back] = v_;                         \
+                    const uint32_t tk_ = lds_u16(cur + J * S2);                               \
+                    if (keep_) sts_u16(dst + q * S2 - l_ * back, (sel & (1u << J)) ? val[J] : tk_); \
                 }
                 BPE_SLOTS_DOWN(BPE_C)
 #undef BPE_C
@@ -508,9 +530,9 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 const uint32_t pt = (uint32_t)n_new + (uint32_t)g;
                 if (pt < Pn * T) {
                     const uint32_t l_ = __umulhi(2u * pt + 1u, inv_n);
-                    sm[dst + pt * STRIDE - l_ * back] = (uint16_t)filler;
+                    sts_u16(dst + pt * S2 - l_ * back, filler);
                 }
-                if (g == 0) sm[dst + T] = (uint16_t)filler;  // the column behind the last lane
+                if (g == 0) sts_u16(dst + 2 * T, filler);    // the column behind the last lane
             }
             team_sync<W, BW>(team);
             const uint32_t sw = cur; cur = nxt; nxt = sw;
@@ -519,7 +541,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 
         for (int q = g; q < n; q += T) {
             const uint32_t l = __umulhi(2u * (uint32_t)q + 1u, inv);
-            out_tok[off + q] = sm[cur - g + ((uint32_t)q - l * Pp) * STRIDE + l];
+            out_tok[off + q] = (uint16_t)lds_u16(cur - 2 * g + 2 * (((uint32_t)q - l * Pp) * STRIDE + l));
         }
         if (g == 0) {
             counts[row] = n;
