@@ -311,6 +311,39 @@ def time_e2e(tok, flat, offsets, call, steps, warmup):
     return dt / steps, int(a.value), int(b.value)
 
 
+def pcie_probe(mb=256, reps=5):
+    """Host link measurement with pinned buffers and plain asynchronous copies: host->device alone,
+    device->host alone, and both at once on two streams.  Prints one JSON line."""
+    import torch
+    n = mb << 20
+    h_in = torch.empty(n, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(n, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(n, dtype=torch.uint8, device="cuda")
+    d_out = torch.empty(n, dtype=torch.uint8, device="cuda")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def run(h2d, d2h):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if h2d:
+                with torch.cuda.stream(s1):
+                    d_in.copy_(h_in, non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(s2):
+                    h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps
+
+    run(True, True)
+    t_in, t_out, t_both = run(True, False), run(False, True), run(True, True)
+    print(json.dumps({"probe": "pcie", "mb_each_way": mb, "h2d_GB/s": round(n / t_in / 1e9, 1),
+                      "d2h_GB/s": round(n / t_out / 1e9, 1), "both_ms": round(t_both * 1e3, 2),
+                      "serial_ms": round((t_in + t_out) * 1e3, 2),
+                      "duplex_GB/s_total": round(2 * n / t_both / 1e9, 1),
+                      "duplex_over_serial": round((t_in + t_out) / t_both, 2)}))
+
+
 def peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -636,6 +669,12 @@ def main():
                     help="k-mer: use the segment encoder whatever the batch shape (library option kmer_force_segments)")
     ap.add_argument("--gather", action="store_true",
                     help="multi-GPU: also time the optional NCCL gather of the padded ids to rank 0 (outside the timed region)")
+    ap.add_argument("--pcie-probe", action="store_true",
+                    help="measure the host link (h2d, d2h, both at once) with pinned buffers and exit")
+    ap.add_argument("--host-chunk-mb", type=int, default=None,
+                    help="library option host_chunk_bytes in MiB (0: never split a host batch into overlapping chunks)")
+    ap.add_argument("--host-chunk-threshold-mb", type=int, default=None,
+                    help="library option host_chunk_threshold in MiB: smaller host batches are not split")
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (no e2e, no CPU baseline): the form used under ncu")
     args = ap.parse_args()
@@ -645,6 +684,15 @@ def main():
         from dnatok_b200 import _cabi
         _cabi.check(_cabi.lib().dnatok_set_option(b"kmer_force_segments", 1))
     args.warmup = max(args.warmup, 3)
+    if args.pcie_probe:
+        pcie_probe()
+        return
+    if args.host_chunk_mb is not None or args.host_chunk_threshold_mb is not None:
+        from dnatok_b200 import _cabi
+        if args.host_chunk_mb is not None:
+            _cabi.check(_cabi.lib().dnatok_set_option(b"host_chunk_bytes", args.host_chunk_mb << 20))
+        if args.host_chunk_threshold_mb is not None:
+            _cabi.check(_cabi.lib().dnatok_set_option(b"host_chunk_threshold", args.host_chunk_threshold_mb << 20))
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -31,8 +31,8 @@ std::atomic<int64_t> g_host_mask_threads{-1};                 // -1: as many as 
 std::atomic<int64_t> g_host_mask_min_bytes{16ll << 20};      // smaller masks are not worth the threads
 thread_local int64_t g_last_h2d = 0, g_last_d2h = 0;          // bytes the last dnatok_encode_host of this thread copied
 std::atomic<int64_t> g_kmer_force_segments{0};                // 1: segment encoder whenever scratch is given
-std::atomic<int64_t> g_host_chunk_bytes{256ll << 20};        // bytes (in + out) per chunk of the host pipeline
-std::atomic<int64_t> g_host_chunk_threshold{4ll << 30};      // batches below this size are not chunked
+std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the host link (in + out) per chunk of the host pipeline
+std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
 
 int fail(int code, const char* fmt, ...) {
@@ -78,17 +78,11 @@ struct DeviceTables {
     void* st_scratch = nullptr;   size_t st_scratch_cap = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev_lengths = nullptr;  // marks the arrival of the row lengths in host memory
-    // chunked host pipeline: three independent slots (buffers + stream), grow only
-    struct PipeSlot {
-        cudaStream_t stream = nullptr;
-        void* bytes = nullptr;   size_t bytes_cap = 0;
-        void* offsets = nullptr; size_t offsets_cap = 0;
-        void* ids = nullptr;     size_t ids_cap = 0;
-        void* mask = nullptr;    size_t mask_cap = 0;
-        void* rows = nullptr;    size_t rows_cap = 0;      // lengths then status, int32 each
-        void* scratch = nullptr; size_t scratch_cap = 0;
-        int64_t* h_offsets = nullptr; size_t h_offsets_cap = 0;   // pinned, chunk-local offsets
-    } pipe[3];
+    // chunked host pipeline: three streams, one event per chunk, per-row words, pinned chunk-local offsets
+    cudaStream_t pipe_streams[3] = {nullptr, nullptr, nullptr};
+    std::vector<cudaEvent_t> pipe_events;
+    void* st_pipe_rows = nullptr; size_t st_pipe_rows_cap = 0;    // lengths then status, int32 each
+    int64_t* h_offsets = nullptr; size_t h_offsets_cap = 0;
 };
 
 }  // namespace
@@ -128,7 +122,18 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
     std::lock_guard<std::mutex> lock(h->mu);
     auto it = h->dev.find(dev);
     if (it == h->dev.end()) {
-        DeviceTables d;
+        it = h->dev.emplace(dev, DeviceTables()).first;
+        DeviceTables& d = it->second;
+        struct Undo {                                    // a failed upload leaves no half-built entry behind
+            dnatok_handle* h; int dev; bool keep;
+            ~Undo() {
+                if (keep) return;
+                DeviceTables& x = h->dev[dev];
+                void* ptrs[] = {x.lut256, x.kmer_ids, x.disp, x.slots, x.merge_out, x.hot, x.byte_tok};
+                for (void* p : ptrs) if (p) cudaFree(p);
+                h->dev.erase(dev);
+            }
+        } undo{h, dev, false};
         CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
         int rc = upload(&d.lut256, h->lut256);
         if (rc) return rc;
@@ -142,7 +147,7 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
             const BpeLaunchInfo* info;
             if ((rc = bpe_launch_info(dev, &info))) return rc;     // configures every merge kernel once per device
         }
-        it = h->dev.emplace(dev, d).first;
+        undo.keep = true;
     }
     *out = &it->second;
     return 0;
@@ -559,6 +564,20 @@ int launch_span_lengths(const int64_t* offsets, const int32_t* counts, int64_t n
 // Attention mask of a padded batch written by host threads from the row lengths the GPU produced:
 // ones on [shift, shift + T) of every row, zeros elsewhere.  The mask is a function of the lengths
 // alone, so a large one is cheaper to make where it is wanted than to carry over the host link.
+// The stores bypass the cache (the mask is written once and read by someone else later): an ordinary
+// store first reads the line it is about to overwrite, which doubles the memory traffic of a buffer
+// that the copies from the GPU are competing with.
+#if defined(__x86_64__) || defined(_M_X64)
+#include <emmintrin.h>
+inline void put_once(int64_t* p, int64_t v) { _mm_stream_si64(reinterpret_cast<long long*>(p), v); }
+inline void put_once(int32_t* p, int32_t v) { _mm_stream_si32(p, v); }
+inline void put_once(uint8_t* p, uint8_t v) { *p = v; }
+inline void put_once_done() { _mm_sfence(); }
+#else
+template <typename M> inline void put_once(M* p, M v) { *p = v; }
+inline void put_once_done() {}
+#endif
+
 template <typename M>
 void fill_mask_rows(M* mask, const int32_t* lengths, int64_t r0, int64_t r1, int64_t stride, bool pad_left) {
     for (int64_t r = r0; r < r1; ++r) {
@@ -567,10 +586,11 @@ void fill_mask_rows(M* mask, const int32_t* lengths, int64_t r0, int64_t r1, int
         if (T < 0) T = 0;
         if (T > stride) T = stride;
         const int64_t lo = pad_left ? stride - T : 0;
-        for (int64_t j = 0; j < lo; ++j) row[j] = 0;
-        for (int64_t j = lo; j < lo + T; ++j) row[j] = 1;
-        for (int64_t j = lo + T; j < stride; ++j) row[j] = 0;
+        for (int64_t j = 0; j < lo; ++j) put_once(row + j, (M)0);
+        for (int64_t j = lo; j < lo + T; ++j) put_once(row + j, (M)1);
+        for (int64_t j = lo + T; j < stride; ++j) put_once(row + j, (M)0);
     }
+    put_once_done();
 }
 
 // The attention mask of a large padded batch, written by n_threads host workers once the row lengths
@@ -701,11 +721,10 @@ void dnatok_destroy(dnatok_handle* h) {
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);
         if (d.ev_lengths) cudaEventDestroy(d.ev_lengths);
-        for (auto& ps : d.pipe) {
-            if (ps.stream) { cudaStreamSynchronize(ps.stream); cudaStreamDestroy(ps.stream); }
-            for (void* p : {ps.bytes, ps.offsets, ps.ids, ps.mask, ps.rows, ps.scratch}) if (p) cudaFree(p);
-            if (ps.h_offsets) cudaFreeHost(ps.h_offsets);
-        }
+        for (auto& st : d.pipe_streams) if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+        for (auto ev : d.pipe_events) cudaEventDestroy(ev);
+        if (d.st_pipe_rows) cudaFree(d.st_pipe_rows);
+        if (d.h_offsets) cudaFreeHost(d.h_offsets);
     }
     if (!h->dev.empty()) cudaSetDevice(cur);
     delete h;
@@ -996,57 +1015,116 @@ static int grow(void** p, size_t* cap, size_t need) {
     return 0;
 }
 
-// Fixed-stride output in row chunks over three slots: while chunk c is being encoded, chunk c+1 is
-// on its way in and chunk c-1 on its way out, so the two PCIe directions and the kernels overlap.
-// Every chunk is an independent sub-batch with chunk-local offsets, which also bounds the staging
-// memory by the chunk size instead of the batch size.
-static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, const uint8_t* h_bytes, const int64_t* h_offsets,
-                                 int64_t n_rows, const dnatok_format* f, int64_t rows_per_chunk, void* h_ids,
-                                 void* h_mask, int32_t* h_lengths, int32_t* h_status) {
+// Fixed-stride output in row chunks over three streams: while chunk c is being encoded, chunk c+1 is
+// on its way in and chunk c-1 on its way out, so the two directions of the host link (which carry
+// their copies at the same time) and the kernels overlap.  Every chunk is an independent sub-batch
+// with chunk-local offsets and its own piece of the device staging buffers and of the scratch, so
+// nothing is reused and the issuing thread never waits.  The row lengths of a chunk come back
+// before its ids; with host-written masks the worker threads wait for each chunk's lengths in turn
+// and fill its mask rows while later chunks are still moving.
+static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, const uint8_t* h_bytes,
+                                 const int64_t* h_offsets, int64_t n_rows, const dnatok_format* f,
+                                 int64_t rows_per_chunk, void* h_ids, void* h_mask, int32_t* h_lengths,
+                                 int32_t* h_status, int mask_threads) {
     const size_t id_sz = f->id_bits / 8, mask_sz = (f->mask_bits && h_mask) ? f->mask_bits / 8 : 0;
     const int64_t stride = f->out_stride;
+    const int64_t total = h_offsets[n_rows];
+    const int64_t n_chunks = (n_rows + rows_per_chunk - 1) / rows_per_chunk;
+    const bool host_mask = mask_sz && mask_threads > 0 &&
+                           (int64_t)((size_t)(n_rows * stride) * mask_sz) >= g_host_mask_min_bytes.load();
     dnatok_format cf = *f;
-    if (!mask_sz) cf.mask_bits = 0;
-    int64_t chunk = 0;
-    for (int64_t r0 = 0; r0 < n_rows; r0 += rows_per_chunk, ++chunk) {
-        const int64_t r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
-        const int64_t rows = r1 - r0;
-        const int64_t b0 = h_offsets[r0], nbytes = h_offsets[r1] - b0;
-        DeviceTables::PipeSlot& ps = d->pipe[chunk % 3];
-        if (!ps.stream) CUDA_TRY(cudaStreamCreateWithFlags(&ps.stream, cudaStreamNonBlocking));
-        CUDA_TRY(cudaStreamSynchronize(ps.stream));           // the slot's previous chunk has left
-        if (int rc = grow(&ps.bytes, &ps.bytes_cap, (size_t)nbytes + 64)) return rc;
-        if (int rc = grow(&ps.offsets, &ps.offsets_cap, (size_t)(rows + 1) * 8)) return rc;
-        if (int rc = grow(&ps.ids, &ps.ids_cap, (size_t)(rows * stride) * id_sz + 64)) return rc;
-        if (mask_sz) if (int rc = grow(&ps.mask, &ps.mask_cap, (size_t)(rows * stride) * mask_sz + 64)) return rc;
-        if (int rc = grow(&ps.rows, &ps.rows_cap, (size_t)rows * 8 + 64)) return rc;
-        const size_t sneed = dnatok_scratch_bytes(h, rows, nbytes);
-        if (sneed) if (int rc = grow(&ps.scratch, &ps.scratch_cap, sneed)) return rc;
-        if ((size_t)(rows + 1) * 8 > ps.h_offsets_cap) {
-            if (ps.h_offsets) CUDA_TRY(cudaFreeHost(ps.h_offsets));
-            ps.h_offsets = nullptr; ps.h_offsets_cap = 0;
-            const size_t cap = (size_t)(rows + 1) * 8 + 4096;
-            CUDA_TRY(cudaMallocHost((void**)&ps.h_offsets, cap));
-            ps.h_offsets_cap = cap;
-        }
-        for (int64_t i = 0; i <= rows; ++i) ps.h_offsets[i] = h_offsets[r0 + i] - b0;
-        int32_t* d_len = (int32_t*)ps.rows;
-        int32_t* d_st = d_len + rows;
-        if (nbytes) CUDA_TRY(cudaMemcpyAsync(ps.bytes, h_bytes + b0, (size_t)nbytes, cudaMemcpyHostToDevice, ps.stream));
-        CUDA_TRY(cudaMemcpyAsync(ps.offsets, ps.h_offsets, (size_t)(rows + 1) * 8, cudaMemcpyHostToDevice, ps.stream));
-        if (int rc = dnatok_encode(h, (const uint8_t*)ps.bytes, (const int64_t*)ps.offsets, rows, nbytes, &cf, ps.ids,
-                                   mask_sz ? ps.mask : nullptr, d_len, nullptr, d_st, ps.scratch, ps.scratch_cap, ps.stream))
-            return rc;
-        CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_ids + (size_t)(r0 * stride) * id_sz, ps.ids, (size_t)(rows * stride) * id_sz,
-                                 cudaMemcpyDeviceToHost, ps.stream));
-        if (mask_sz)
-            CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_mask + (size_t)(r0 * stride) * mask_sz, ps.mask,
-                                     (size_t)(rows * stride) * mask_sz, cudaMemcpyDeviceToHost, ps.stream));
-        if (h_lengths) CUDA_TRY(cudaMemcpyAsync(h_lengths + r0, d_len, (size_t)rows * 4, cudaMemcpyDeviceToHost, ps.stream));
-        if (h_status) CUDA_TRY(cudaMemcpyAsync(h_status + r0, d_st, (size_t)rows * 4, cudaMemcpyDeviceToHost, ps.stream));
+    if (!mask_sz || host_mask) cf.mask_bits = 0;
+
+    // staging for the whole batch (grow only), chunk-local offsets in pinned host memory
+    if (int rc = grow((void**)&d->st_bytes, &d->st_bytes_cap, (size_t)total + 64)) return rc;
+    if (int rc = grow((void**)&d->st_offsets, &d->st_offsets_cap, (size_t)(n_rows + n_chunks) * 8)) return rc;
+    if (int rc = grow(&d->st_ids, &d->st_ids_cap, (size_t)(n_rows * stride) * id_sz + 64)) return rc;
+    if (mask_sz && !host_mask)
+        if (int rc = grow(&d->st_mask, &d->st_mask_cap, (size_t)(n_rows * stride) * mask_sz + 64)) return rc;
+    if (int rc = grow(&d->st_pipe_rows, &d->st_pipe_rows_cap, (size_t)n_rows * 8 + 64)) return rc;
+    if ((size_t)(n_rows + n_chunks) * 8 > d->h_offsets_cap) {
+        if (d->h_offsets) CUDA_TRY(cudaFreeHost(d->h_offsets));
+        d->h_offsets = nullptr; d->h_offsets_cap = 0;
+        const size_t cap = (size_t)(n_rows + n_chunks) * 8 + 65536;
+        CUDA_TRY(cudaMallocHost((void**)&d->h_offsets, cap));
+        d->h_offsets_cap = cap;
     }
-    for (auto& ps : d->pipe) if (ps.stream) CUDA_TRY(cudaStreamSynchronize(ps.stream));
-    return DNATOK_OK;
+    // k-mer chunks run one warp per row: several chunks are on the GPU at once, and the segment encoder
+    // counts on having its whole grid resident
+    size_t scratch_total = 0;
+    std::vector<size_t> scratch_at((size_t)n_chunks + 1, 0);
+    for (int64_t c = 0; c < n_chunks; ++c) {
+        const int64_t r0 = c * rows_per_chunk, r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
+        scratch_at[(size_t)c] = scratch_total;
+        if (h->kind == DNATOK_KIND_BPE)
+            scratch_total += align_up(dnatok_scratch_bytes(h, r1 - r0, h_offsets[r1] - h_offsets[r0]), 256);
+    }
+    scratch_at[(size_t)n_chunks] = scratch_total;
+    if (scratch_total) if (int rc = grow(&d->st_scratch, &d->st_scratch_cap, scratch_total)) return rc;
+    while ((int64_t)d->pipe_events.size() < n_chunks) {
+        cudaEvent_t ev;
+        CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        d->pipe_events.push_back(ev);
+    }
+    for (auto& st : d->pipe_streams) if (!st) CUDA_TRY(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+
+    int32_t* d_len_all = (int32_t*)d->st_pipe_rows;
+    int32_t* d_st_all = d_len_all + n_rows;
+    std::vector<int32_t> tmp_len;
+    int32_t* hl = h_lengths;
+    if (host_mask && !hl) { tmp_len.resize((size_t)n_rows); hl = tmp_len.data(); }
+    for (int64_t c = 0; c < n_chunks; ++c) {
+        const int64_t r0 = c * rows_per_chunk, r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
+        const int64_t rows = r1 - r0, b0 = h_offsets[r0], nbytes = h_offsets[r1] - b0;
+        cudaStream_t st = d->pipe_streams[c % 3];
+        int64_t* ho = d->h_offsets + r0 + c;                   // rows + 1 entries of this chunk
+        for (int64_t i = 0; i <= rows; ++i) ho[i] = h_offsets[r0 + i] - b0;
+        uint8_t* db = d->st_bytes + b0;
+        int64_t* dof = d->st_offsets + r0 + c;
+        if (nbytes) CUDA_TRY(cudaMemcpyAsync(db, h_bytes + b0, (size_t)nbytes, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(dof, ho, (size_t)(rows + 1) * 8, cudaMemcpyHostToDevice, st));
+        uint8_t* dids = (uint8_t*)d->st_ids + (size_t)(r0 * stride) * id_sz;
+        uint8_t* dmask = (mask_sz && !host_mask) ? (uint8_t*)d->st_mask + (size_t)(r0 * stride) * mask_sz : nullptr;
+        if (int rc = dnatok_encode(h, db, dof, rows, nbytes, &cf, dids, dmask, d_len_all + r0, nullptr, d_st_all + r0,
+                                   scratch_total ? (uint8_t*)d->st_scratch + scratch_at[(size_t)c] : nullptr,
+                                   scratch_at[(size_t)c + 1] - scratch_at[(size_t)c], st))
+            return rc;
+        if (hl) CUDA_TRY(cudaMemcpyAsync(hl + r0, d_len_all + r0, (size_t)rows * 4, cudaMemcpyDeviceToHost, st));
+        if (h_status) CUDA_TRY(cudaMemcpyAsync(h_status + r0, d_st_all + r0, (size_t)rows * 4, cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaEventRecord(d->pipe_events[(size_t)c], st));
+        CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_ids + (size_t)(r0 * stride) * id_sz, dids, (size_t)(rows * stride) * id_sz,
+                                 cudaMemcpyDeviceToHost, st));
+        if (dmask)
+            CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_mask + (size_t)(r0 * stride) * mask_sz, dmask,
+                                     (size_t)(rows * stride) * mask_sz, cudaMemcpyDeviceToHost, st));
+    }
+    g_last_h2d = total + (n_rows + n_chunks) * 8;
+    g_last_d2h = n_rows * stride * (int64_t)(id_sz + (host_mask ? 0 : mask_sz)) + (hl ? n_rows * 4 : 0) + (h_status ? n_rows * 4 : 0);
+    int rc_mask = 0;
+    if (host_mask) {
+        // every worker takes its stripe of each chunk once that chunk's lengths have arrived
+        const int nt = mask_threads;
+        std::vector<int> errs((size_t)nt, 0);
+        auto work = [&](int t) {
+            if (cudaSetDevice(device) != cudaSuccess) { errs[(size_t)t] = 1; return; }
+            for (int64_t c = 0; c < n_chunks; ++c) {
+                if (cudaEventSynchronize(d->pipe_events[(size_t)c]) != cudaSuccess) { errs[(size_t)t] = 1; return; }
+                const int64_t r0 = c * rows_per_chunk, r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
+                const int64_t a = r0 + (r1 - r0) * t / nt, b = r0 + (r1 - r0) * (t + 1) / nt;
+                if (f->mask_bits == 64) fill_mask_rows<int64_t>((int64_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
+                else if (f->mask_bits == 32) fill_mask_rows<int32_t>((int32_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
+                else fill_mask_rows<uint8_t>((uint8_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
+            }
+        };
+        std::vector<std::thread> pool;
+        pool.reserve((size_t)nt);
+        for (int t = 1; t < nt; ++t) pool.emplace_back(work, t);
+        work(0);
+        for (auto& th : pool) th.join();
+        for (int e : errs) if (e) rc_mask = fail(DNATOK_ERR_CUDA, "a host worker could not wait for the row lengths");
+    }
+    for (auto& st : d->pipe_streams) if (st) CUDA_TRY(cudaStreamSynchronize(st));
+    return rc_mask;
 }
 
 int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, const int64_t* h_offsets,
@@ -1093,22 +1171,32 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
             }
         }
         if (pstride > 0 && n_rows >= 2) {
-            const size_t row_out = (size_t)pstride * (id_sz + ((mask_sz && h_mask) ? mask_sz : 0));
-            const size_t out_total = row_out * (size_t)n_rows;
-            // Chunking bounds the staging memory; on a link whose two directions share one budget it
-            // does not shorten the call, so by default only batches of 4 GiB and more are split.
+            int mask_threads = (int)g_host_mask_threads.load();
+            if (mask_threads < 0) {
+                const unsigned hc = std::thread::hardware_concurrency();
+                mask_threads = hc == 0 ? 1 : (hc > 16 ? 16 : (int)hc);
+            }
+            const bool want_mask = mask_sz && h_mask;
+            const bool host_mask = want_mask && mask_threads > 0 &&
+                                   (int64_t)((size_t)(n_rows * pstride) * mask_sz) >= g_host_mask_min_bytes.load();
+            // bytes that cross the link per row: the input, the ids, and the mask unless host threads write it
+            const size_t row_link = (size_t)pstride * (id_sz + ((want_mask && !host_mask) ? mask_sz : 0)) + (size_t)(total / n_rows) + 1;
+            const size_t link_total = row_link * (size_t)n_rows;
+            // The two directions of the host link carry copies at the same time (measured: both at once take
+            // 0.57 of one after the other), so batches from 128 MiB up are split into chunks of about 64 MiB.
             const size_t CHUNK_BYTES = (size_t)g_host_chunk_bytes.load();
             const size_t threshold = (size_t)g_host_chunk_threshold.load();
-            if (CHUNK_BYTES && out_total + (size_t)total >= threshold && out_total + (size_t)total >= 2 * CHUNK_BYTES) {
-                if ((int64_t)(out_total / (id_sz + ((mask_sz && h_mask) ? mask_sz : 0))) > ids_capacity)
+            if (CHUNK_BYTES && link_total >= threshold && link_total >= 2 * CHUNK_BYTES) {
+                if (n_rows * pstride > ids_capacity)
                     return fail(DNATOK_ERR_CAPACITY, "ids buffer holds %lld elements, %lld needed", (long long)ids_capacity,
                                 (long long)(n_rows * pstride));
-                const size_t per_row = row_out + (size_t)(total / n_rows) + 1;
-                int64_t rpc = (int64_t)(CHUNK_BYTES / per_row);
+                int64_t rpc = (int64_t)(CHUNK_BYTES / row_link);
                 if (rpc < 1) rpc = 1;
+                if ((n_rows + rpc - 1) / rpc > 256) rpc = (n_rows + 255) / 256;      // at most 256 chunks
                 dnatok_format pf = *fmt;
                 pf.out_stride = pstride;
-                if (int rc = encode_host_pipelined(h, d, h_bytes, h_offsets, n_rows, &pf, rpc, h_ids, h_mask, h_lengths, h_status))
+                if (int rc = encode_host_pipelined(h, d, device, h_bytes, h_offsets, n_rows, &pf, rpc, h_ids, h_mask, h_lengths,
+                                                   h_status, mask_threads))
                     return rc;
                 if (out_stride_used) *out_stride_used = pstride;
                 return DNATOK_OK;
@@ -1120,10 +1208,16 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
     if ((size_t)n_rows + 1 > d->st_rows_cap) {
         for (void** p : {(void**)&d->st_lengths, (void**)&d->st_status, (void**)&d->st_out_offsets})
             if (*p) { CUDA_TRY(cudaFree(*p)); *p = nullptr; }
+        d->st_rows_cap = 0;
         const size_t cap = (size_t)n_rows + n_rows / 8 + 1024;
-        CUDA_TRY(cudaMalloc((void**)&d->st_lengths, cap * 4));
-        CUDA_TRY(cudaMalloc((void**)&d->st_status, cap * 4));
-        CUDA_TRY(cudaMalloc((void**)&d->st_out_offsets, cap * 8));
+        cudaError_t e1 = cudaMalloc((void**)&d->st_lengths, cap * 4);
+        cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc((void**)&d->st_status, cap * 4) : e1;
+        cudaError_t e3 = e2 == cudaSuccess ? cudaMalloc((void**)&d->st_out_offsets, cap * 8) : e2;
+        if (e3 != cudaSuccess) {
+            for (void** p : {(void**)&d->st_lengths, (void**)&d->st_status, (void**)&d->st_out_offsets})
+                if (*p) { cudaFree(*p); *p = nullptr; }
+            return fail(DNATOK_ERR_CUDA, "staging allocation: %s", cudaGetErrorString(e3));
+        }
         d->st_rows_cap = cap;
     }
     const size_t scratch_need = dnatok_scratch_bytes(h, n_rows, total);
@@ -1159,7 +1253,15 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
             prepared = true;
         }
         stride = longest;
-        if (stride == 0) { if (out_stride_used) *out_stride_used = 0; CUDA_TRY(cudaStreamSynchronize(st)); return DNATOK_OK; }
+        if (stride == 0) {                               // every row is empty: nothing to write but the row words
+            CUDA_TRY(cudaStreamSynchronize(st));
+            if (h_lengths) for (int64_t i = 0; i < n_rows; ++i) h_lengths[i] = 0;
+            if (h_status) for (int64_t i = 0; i < n_rows; ++i) h_status[i] = 0;
+            g_last_h2d = total + (n_rows + 1) * 8;
+            g_last_d2h = 0;
+            if (out_stride_used) *out_stride_used = 0;
+            return DNATOK_OK;
+        }
     }
     f.out_stride = stride;
     const bool ragged = stride == 0;

@@ -198,9 +198,10 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
                       int64_t* out_offsets, int64_t offsets_capacity, int64_t* n_records, int64_t* n_bytes);
 
 /* Process-wide tuning knobs (no reference counterpart):
- *   "host_chunk_bytes"      bytes (input + output) per chunk when dnatok_encode_host splits a
- *                           fixed-stride batch into overlapping chunks; 0 disables splitting (default 256 MiB)
- *   "host_chunk_threshold"  only batches at least this large are split (default 4 GiB)
+ *   "host_chunk_bytes"      bytes over the host link (input + output) per chunk when dnatok_encode_host splits a
+ *                           fixed-stride batch into chunks whose copies in the two directions and kernels overlap;
+ *                           0 disables splitting (default 64 MiB)
+ *   "host_chunk_threshold"  only batches at least this large are split (default 128 MiB)
  *   "host_mask_threads"     dnatok_encode_host, padded output with a mask of 16 MiB or more: the mask is written by
  *                           this many host threads from the row lengths while the ids are copied back, instead of
  *                           being produced on the GPU and copied too (-1, default: one per core, at most 16;
@@ -215,7 +216,7 @@ int dnatok_set_option(const char* name, int64_t value);
 /* Number of kernels this library has launched from the calling process (for accounting). */
 int64_t dnatok_launch_count(void);
 
-/* Bytes the calling thread's last dnatok_encode_host (unchunked) copied host -> device and device ->
+/* Bytes the calling thread's last dnatok_encode_host copied host -> device and device ->
  * host.  With "host_mask_threads" active the mask of a large padded batch is not among them: host
  * threads write it from the row lengths the GPU returned.  No reference counterpart. */
 void dnatok_host_copy_bytes(int64_t* h2d, int64_t* d2h);

@@ -406,8 +406,10 @@ def test_bpe_table_with_late_created_operands_single_step(bpe_team_mode):
     ("kmer6", 4096, 6000, dict(padding="max_length", max_length=1000, truncation=True, add_special_tokens=False)),
     ("bpe4096", 6144, 1024, dict(padding="max_length", max_length=768)),
 ])
-def test_host_entry_chunked_pipeline(toks, name, rows, length, kw):
-    """Batches large enough for dnatok_encode_host to split into overlapping chunks (several slots reused)."""
+@pytest.mark.parametrize("mask_threads", [-1, 0])
+def test_host_entry_chunked_pipeline(toks, name, rows, length, kw, mask_threads):
+    """Batches large enough for dnatok_encode_host to split into chunks whose copies and kernels overlap,
+    with the mask written by host threads chunk by chunk (-1) or copied from the device (0)."""
     gen = {"char": synth.config1, "kmer6": synth.config2, "bpe4096": synth.config3}[name]
     flat, offs = synth.pack_rows(gen(batch=rows, length=length, seed=1234))
     # ragged tail so the chunks differ in size
@@ -418,13 +420,15 @@ def test_host_entry_chunked_pipeline(toks, name, rows, length, kw):
     flat = np.concatenate([flat[:offs[rows - 7]], flat2])
     from dnatok_b200 import _cabi
     L = _cabi.lib()
-    _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 16 << 20))
+    _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 4 << 20))
     _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 0))
+    _cabi.check(L.dnatok_set_option(b"host_mask_threads", mask_threads))
     try:
         enc = toks[name].encode_host((flat, offs2), **kw)
     finally:
-        _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 256 << 20))
-        _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 4 << 30))
+        _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 64 << 20))
+        _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 128 << 20))
+        _cabi.check(L.dnatok_set_option(b"host_mask_threads", -1))
     okw = dict(kw)
     okw["add_special"] = okw.pop("add_special_tokens", True)
     o_ids, o_mask = H.oracle_batch(name, flat, offs2, **okw)
