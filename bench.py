@@ -503,7 +503,35 @@ def per_config(local, peak, args):
             del d_bytes, d_off, enc
             torch.cuda.empty_cache()
     out["embed_char/scaled"] = embed_line(local, peak)
+    out["kmer6/list_str"] = list_str_line(local)
     return out
+
+
+def list_str_line(local):
+    """From a Python list of str to ids + mask tensors on the device through the call a user makes
+    (``tok(seqs, ...)``): native packing into pinned memory, one copy in, the kernel.  Wall clock."""
+    import torch
+    from dnatok_b200.tokenizer import B200Tokenizer
+    tok = B200Tokenizer(spec_for("kmer6"), device=local)
+    flat, offsets, call, desc = make_workload("kmer6", 32)
+    strs = synth.rows_to_strings(flat, offsets)
+    kw = dict(padding="max_length", max_length=1000, truncation=True, add_special_tokens=False, return_tensors="pt")
+    for _ in range(3):
+        tok(strs, **kw)
+    torch.cuda.synchronize()
+    steps = 10
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        enc = tok(strs, **kw)
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    t0 = time.perf_counter()
+    "".join(strs).encode("ascii")
+    t_join = time.perf_counter() - t0
+    return {"workload": "list of %d str x 6000 bp -> int64 ids + mask on the device (tok(seqs, ...))" % len(strs),
+            "ms_per_step": round(dt * 1e3, 3), "Mbp/s": round(int(offsets[-1]) / dt / 1e6, 1),
+            "python_join_encode_ms": round(t_join * 1e3, 3),
+            "note": "python_join_encode_ms is the packing step alone as the reference does it (\"\".join(seqs).encode)"}
 
 
 def embed_line(local, peak):

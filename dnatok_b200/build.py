@@ -1,4 +1,4 @@
-"""Build ``libdnatok_b200.so`` in-tree with nvcc for sm_100a.
+"""Build ``libdnatok_b200.so`` (nvcc, sm_100a) and the host packer ``_pack.so`` (gcc, CPython API) in-tree.
 
     python -m dnatok_b200.build [--force] [--verbose]
 """
@@ -28,7 +28,24 @@ def stale() -> bool:
     return any(os.path.getmtime(os.path.join(CSRC, d)) > t for d in DEPS)
 
 
+PACK_SRC = os.path.join(CSRC, "pack_module.c")
+PACK_OUT = os.path.join(HERE, "_pack.so")
+
+
+def build_packer(force: bool = False, verbose: bool = False) -> str:
+    if not force and os.path.exists(PACK_OUT) and os.path.getmtime(PACK_OUT) >= os.path.getmtime(PACK_SRC):
+        return PACK_OUT
+    import sysconfig
+    cmd = [os.environ.get("CC", "gcc"), "-O3", "-shared", "-fPIC", "-pthread", "-I", sysconfig.get_paths()["include"],
+           "-o", PACK_OUT, PACK_SRC]
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.check_call(cmd)
+    return PACK_OUT
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
+    build_packer(force, verbose)
     if not force and not stale():
         return OUT
     cmd = [nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,210 +1,233 @@
-"""Command line front end: ``python -m dnatok_b200.cli info | encode | validate | bench``.
+"""``python -m dnatok_b200.cli <command> --tokenizer T [...]`` - a small front end over ``B200Tokenizer``.
 
-Same four commands, payload keys and exit codes as the reference's ``dnatok`` CLI
-(``src/dnatok_cli.py:162-307``): ``info`` reports the selected path, ``encode`` prints the ids of one
-sequence with padding stripped, ``validate`` compares n random ACGT windows with the Hugging Face
-tokenizer (``add_special_tokens=False``) and exits 1 on any mismatch, ``bench`` measures
-Mbp/s = sum(bp) / wall time for both.  The reference resolves a model name on the Hugging Face hub;
-here ``--tokenizer`` is a ``tokenizer.json`` file, a local directory ``AutoTokenizer`` can load, or
-one of the built-in synthetic tokenizers ``char``, ``byte``, ``kmer<k>``.
+Commands and the keys they print follow the reference's ``dnatok`` tool (``src/dnatok_cli.py:162-307``:
+``info``, ``encode``, ``validate``, ``bench``; exit code 1 when ``validate`` finds a mismatch, 2 on an
+error) so that scripts written against it keep working; ``scenarios`` runs the eight read-length
+workloads of its realistic benchmark (``benchmarks/run_realistic_benchmark.py:184-272``).  ``--tokenizer``
+is a ``tokenizer.json`` (optionally gzipped), a local directory ``AutoTokenizer`` can load, or one of the
+built-in synthetic tokenizers ``char``, ``byte``, ``kmer<k>`` (the reference resolves model names on the
+Hugging Face hub, which is not reachable offline).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
-import random
 import sys
 import time
-from typing import Any, List
+
+import numpy as np
+
+PATH_NAME = {"char": "ascii_lut", "kmer": "kmer_lut", "bpe": "gpu_bpe"}
 
 
-def _builtin(name: str):
-    """Synthetic tokenizers with the vocabularies of the benchmark shapes, built with `tokenizers`."""
+def builtin_tokenizer(name: str):
+    """Hugging Face tokenizers with the vocabularies of the benchmark shapes (None for other names)."""
     import itertools
-    from tokenizers import Regex, Tokenizer
-    from tokenizers.models import WordLevel
-    from tokenizers.pre_tokenizers import Sequence, Split
+    from tokenizers import Regex, Tokenizer, models, pre_tokenizers
     from transformers import PreTrainedTokenizerFast
-    specials = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"]
     if name == "byte":
-        tok = Tokenizer(WordLevel({chr(i): i for i in range(512)}, unk_token=chr(0)))
-        tok.pre_tokenizer = Split(Regex("[\\s\\S]"), "isolated")
-        return PreTrainedTokenizerFast(tokenizer_object=tok, pad_token=chr(1), unk_token=chr(0))
-    vocab = {s: i for i, s in enumerate(specials)}
-    if name == "char":
-        for c in "ACGTN":
-            vocab[c] = len(vocab)
-        tok = Tokenizer(WordLevel(vocab, unk_token="[UNK]"))
-        tok.pre_tokenizer = Split(Regex("."), "isolated")
-    elif name.startswith("kmer") and name[4:].isdigit():
-        k = int(name[4:])
-        for t in itertools.product("ACGT", repeat=k):
-            vocab["".join(t)] = len(vocab)
-        for c in "ACGTN":
-            vocab[c] = len(vocab)
-        tok = Tokenizer(WordLevel(vocab, unk_token="[UNK]"))
-        tok.pre_tokenizer = Sequence([Split(Regex(".{1,%d}" % k), "isolated"), Split(Regex("[ACGT]{%d}|." % k), "isolated")])
-    else:
+        core = Tokenizer(models.WordLevel({chr(i): i for i in range(512)}, unk_token=chr(0)))
+        core.pre_tokenizer = pre_tokenizers.Split(Regex("[\\s\\S]"), "isolated")
+        return PreTrainedTokenizerFast(tokenizer_object=core, pad_token=chr(1), unk_token=chr(0))
+    k = int(name[4:]) if name.startswith("kmer") and name[4:].isdigit() else 0
+    if name != "char" and not k:
         return None
-    return PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="[PAD]", unk_token="[UNK]")
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"]
+    if k:
+        words += ["".join(t) for t in itertools.product("ACGT", repeat=k)]
+    words += list("ACGTN")
+    core = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="[UNK]"))
+    splits = [pre_tokenizers.Split(Regex("."), "isolated")] if not k else \
+        [pre_tokenizers.Split(Regex(".{1,%d}" % k), "isolated"), pre_tokenizers.Split(Regex("[ACGT]{%d}|." % k), "isolated")]
+    core.pre_tokenizer = pre_tokenizers.Sequence(splits)
+    return PreTrainedTokenizerFast(tokenizer_object=core, pad_token="[PAD]", unk_token="[UNK]")
 
 
-def load_hf(spec: str):
-    tok = _builtin(spec)
+def load_hf(where: str):
+    tok = builtin_tokenizer(where)
     if tok is not None:
         return tok
-    if os.path.isfile(spec):
+    if os.path.isfile(where):
+        from tokenizers import Tokenizer
         from transformers import PreTrainedTokenizerFast
-        if spec.endswith(".gz"):
+        if where.endswith(".gz"):
             import gzip
-            from tokenizers import Tokenizer
-            with gzip.open(spec, "rt") as f:
-                obj = Tokenizer.from_str(f.read())
-            tok = PreTrainedTokenizerFast(tokenizer_object=obj)
+            with gzip.open(where, "rt") as f:
+                core = Tokenizer.from_str(f.read())
         else:
-            tok = PreTrainedTokenizerFast(tokenizer_file=spec)
-        vocab = tok.get_vocab()
-        for attr, names in (("pad_token", ("[PAD]", "<pad>")), ("unk_token", ("[UNK]", "<unk>"))):
-            for n in names:
-                if getattr(tok, attr) is None and n in vocab:
-                    setattr(tok, attr, n)
+            core = Tokenizer.from_file(where)
+        tok = PreTrainedTokenizerFast(tokenizer_object=core)
+        have = tok.get_vocab()
+        for attr, names in {"pad_token": ("[PAD]", "<pad>"), "unk_token": ("[UNK]", "<unk>")}.items():
+            if getattr(tok, attr) is None:
+                hit = next((n for n in names if n in have), None)
+                if hit:
+                    setattr(tok, attr, hit)
         return tok
     from transformers import AutoTokenizer
-    return AutoTokenizer.from_pretrained(spec, trust_remote_code=False)
+    return AutoTokenizer.from_pretrained(where, trust_remote_code=False)
 
 
-class _Embedder:
-    def __init__(self, tokenizer):
-        self.tokenizer = tokenizer
+class Session:
+    """One Hugging Face tokenizer and the GPU tokenizer built from it."""
 
-    def embed_tokens(self, ids):
-        return ids
+    def __init__(self, where: str):
+        from .tokenizer import B200Tokenizer
+        self.where = where
+        self.hf = load_hf(where)
+        self.gpu = B200Tokenizer.from_hf(self.hf)
+        self.path = PATH_NAME[self.gpu.spec.kind]
 
+    def rows(self, seqs):
+        """Content ids of every sequence (no special tokens, no padding) as lists."""
+        enc = self.gpu(seqs, add_special_tokens=False, return_attention_mask=False)
+        return enc["input_ids"]
 
-def _build(spec: str, padding_side: str = "right"):
-    from .dna_tokenizer import DNATok
-    hf = load_hf(spec)
-    dn = DNATok(_Embedder(hf), padding_side=padding_side)
-    dn.discover()
-    return hf, dn
+    def encode_timed(self, seqs, chunk):
+        import torch
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(0, len(seqs), chunk):
+            self.gpu(seqs[i:i + chunk], padding=True, add_special_tokens=False, return_tensors="pt")
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0
 
-
-def _path(dn) -> str:
-    if dn.bpe_backend is not None:
-        return "gpu_bpe"
-    return "kmer_lut" if dn.kmer_k else "ascii_lut"
-
-
-def _strip(row: List[int], pad: int, side: str) -> List[int]:
-    if side == "left":
-        j = 0
-        while j < len(row) and row[j] == pad:
-            j += 1
-        return row[j:]
-    j = len(row)
-    while j > 0 and row[j - 1] == pad:
-        j -= 1
-    return row[:j]
+    def hf_timed(self, seqs, chunk):
+        t0 = time.perf_counter()
+        for i in range(0, len(seqs), chunk):
+            self.hf(seqs[i:i + chunk], add_special_tokens=False)
+        return time.perf_counter() - t0
 
 
-def _emit(payload: Any, as_json: bool) -> None:
-    if as_json:
-        print(json.dumps(payload))
-    else:
-        for k, v in payload.items():
-            print("%-24s %s" % (k, v))
+def random_windows(n, width, seed):
+    rng = np.random.default_rng(seed)
+    letters = np.frombuffer(b"ACGT", dtype=np.uint8)[rng.integers(0, 4, size=(n, width))]
+    return [row.tobytes().decode("ascii") for row in letters]
 
 
-def cmd_info(a) -> int:
-    hf, dn = _build(a.tokenizer)
-    _emit({"tokenizer": a.tokenizer, "tokenizer_class": type(hf).__name__,
-           "vocab_size": int(getattr(hf, "vocab_size", 0)) or len(hf.get_vocab()), "selected_path": _path(dn),
-           "device": "cuda", "kmer_k": dn.kmer_k, "has_ascii_lut": dn.use_ids_path and not dn.kmer_k,
-           "has_gpu_bpe_backend": dn.bpe_backend is not None, "padding_side": dn.padding_side,
-           "id_pad": int(dn.id_pad)}, a.json)
-    return 0
+def run_info(s: Session, a):
+    sp = s.gpu.spec
+    return 0, {"tokenizer": s.where, "tokenizer_class": type(s.hf).__name__, "vocab_size": int(s.gpu.vocab_size),
+               "selected_path": s.path, "device": str(s.gpu.device), "kmer_k": sp.k or None,
+               "has_ascii_lut": sp.kind == "char", "has_gpu_bpe_backend": sp.kind == "bpe",
+               "padding_side": s.gpu.padding_side, "id_pad": int(s.gpu.pad_token_id)}
 
 
-def cmd_encode(a) -> int:
-    hf, dn = _build(a.tokenizer)
-    ids = _strip(dn.encode_batch_to_ids([a.seq])[0].tolist(), int(dn.id_pad), dn.padding_side)
-    _emit({"tokenizer": a.tokenizer, "sequence": a.seq[:80] + ("..." if len(a.seq) > 80 else ""),
-           "sequence_length_bp": len(a.seq), "n_tokens": len(ids),
-           "token_ids": ids if a.json else ids[:32] + (["..."] if len(ids) > 32 else []),
-           "selected_path": _path(dn)}, a.json)
-    return 0
+def run_encode(s: Session, a):
+    ids = s.rows([a.seq])[0]
+    shown = ids if a.json or len(ids) <= 32 else ids[:32] + ["..."]
+    return 0, {"tokenizer": s.where, "sequence": a.seq if len(a.seq) <= 80 else a.seq[:80] + "...",
+               "sequence_length_bp": len(a.seq), "n_tokens": len(ids), "token_ids": shown, "selected_path": s.path}
 
 
-def cmd_validate(a) -> int:
-    hf, dn = _build(a.tokenizer)
-    rng = random.Random(a.seed)
-    seqs = ["".join(rng.choices("ACGT", k=a.window)) for _ in range(a.n)]
-    mine = dn.encode_batch_to_ids(seqs).tolist()
-    want = hf(seqs, add_special_tokens=False, padding=False, truncation=False)["input_ids"]
-    pad = int(dn.id_pad)
-    n_match, first = 0, None
-    for i, s in enumerate(seqs):
-        got = _strip(mine[i], pad, dn.padding_side)
-        if got == list(want[i]):
-            n_match += 1
-        elif first is None:
-            first = {"i": i, "seq_head": s[:40], "dnatok_head": got[:8], "hf_head": list(want[i])[:8]}
-    _emit({"tokenizer": a.tokenizer, "n_sequences": a.n, "n_match": n_match, "n_mismatch": a.n - n_match,
-           "match_rate": n_match / a.n, "selected_path": _path(dn), "first_mismatch": first}, a.json)
-    return 0 if n_match == a.n else 1
+def run_validate(s: Session, a):
+    seqs = random_windows(a.n, a.window, a.seed)
+    want = s.hf(seqs, add_special_tokens=False, padding=False, truncation=False)["input_ids"]
+    got = s.rows(seqs)
+    bad = [i for i in range(a.n) if list(got[i]) != list(want[i])]
+    first = None
+    if bad:
+        i = bad[0]
+        first = {"i": i, "seq_head": seqs[i][:40], "dnatok_head": list(got[i])[:8], "hf_head": list(want[i])[:8]}
+    return (1 if bad else 0), {"tokenizer": s.where, "n_sequences": a.n, "n_match": a.n - len(bad), "n_mismatch": len(bad),
+                               "match_rate": (a.n - len(bad)) / max(a.n, 1), "selected_path": s.path, "first_mismatch": first}
 
 
-def cmd_bench(a) -> int:
-    import torch
-    os.environ["RAYON_NUM_THREADS"] = str(a.hf_threads)
-    os.environ["TOKENIZERS_PARALLELISM"] = "true" if a.hf_threads > 1 else "false"
-    hf, dn = _build(a.tokenizer)
-    rng = random.Random(a.seed)
-    seqs = ["".join(rng.choices("ACGT", k=a.window)) for _ in range(a.n)]
-    bp = sum(map(len, seqs))
-    hf(seqs[:min(a.chunk, a.n)], add_special_tokens=False)
-    dn.encode_batch_to_ids(seqs[:min(a.chunk, a.n)])
-    t0 = time.perf_counter()
-    for i in range(0, a.n, a.chunk):
-        hf(seqs[i:i + a.chunk], add_special_tokens=False)
-    t_hf = time.perf_counter() - t0
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for i in range(0, a.n, a.chunk):
-        dn.encode_batch_to_ids(seqs[i:i + a.chunk])
-    torch.cuda.synchronize()
-    t_dn = time.perf_counter() - t0
-    _emit({"tokenizer": a.tokenizer, "n_sequences": a.n, "window_bp": a.window, "chunk": a.chunk, "total_bp": bp,
-           "hf_threads": a.hf_threads, "hf_time_s": round(t_hf, 4), "hf_mbp_per_s": round(bp / t_hf / 1e6, 2),
-           "dnatok_time_s": round(t_dn, 4), "dnatok_mbp_per_s": round(bp / t_dn / 1e6, 2),
-           "speedup_dnatok_vs_hf": round(t_hf / t_dn, 2), "selected_path": _path(dn), "device": "cuda"}, a.json)
-    return 0
+def run_bench(s: Session, a):
+    seqs = random_windows(a.n, a.window, a.seed)
+    bp = a.n * a.window
+    head = seqs[:min(a.chunk, a.n)]
+    s.hf(head, add_special_tokens=False)
+    s.gpu(head, padding=True, add_special_tokens=False, return_tensors="pt")
+    t_hf, t_gpu = s.hf_timed(seqs, a.chunk), s.encode_timed(seqs, a.chunk)
+    return 0, {"tokenizer": s.where, "n_sequences": a.n, "window_bp": a.window, "chunk": a.chunk, "total_bp": bp,
+               "hf_threads": a.hf_threads, "hf_time_s": round(t_hf, 4), "hf_mbp_per_s": round(bp / t_hf / 1e6, 2),
+               "dnatok_time_s": round(t_gpu, 4), "dnatok_mbp_per_s": round(bp / t_gpu / 1e6, 2),
+               "speedup_dnatok_vs_hf": round(t_hf / t_gpu, 2), "selected_path": s.path, "device": str(s.gpu.device)}
 
 
-def main(argv=None) -> int:
+def run_scenarios(s: Session, a):
+    """Every read-length scenario: ids checked against Hugging Face on a sample of the reads, then the whole
+    workload timed in chunks through both."""
+    from . import synth
+    out, code = {}, 0
+    names = a.only.split(",") if a.only else list(synth.SCENARIOS)
+    for name in names:
+        reads = None if a.reads <= 0 else a.reads
+        flat, offsets = synth.scenario(name, reads, a.seed)
+        seqs = synth.rows_to_strings(flat, offsets)
+        sample = seqs[:: max(1, len(seqs) // max(a.check, 1))][:a.check]
+        want = s.hf(sample, add_special_tokens=False)["input_ids"]
+        got = s.rows(sample)
+        n_bad = sum(list(g) != list(w) for g, w in zip(got, want))
+        code = code or (1 if n_bad else 0)
+        s.gpu(seqs[:min(a.chunk, len(seqs))], padding=True, add_special_tokens=False, return_tensors="pt")
+        t_gpu = s.encode_timed(seqs, a.chunk)
+        t_hf = s.hf_timed(seqs, a.chunk) if not a.no_hf else float("nan")
+        bp = int(offsets[-1])
+        lens = np.diff(offsets)
+        out[name] = {"description": synth.SCENARIOS[name][1], "n_reads": len(seqs), "total_bp": bp,
+                     "length_min": int(lens.min()), "length_p50": int(np.median(lens)), "length_max": int(lens.max()),
+                     "checked": len(sample), "mismatches": int(n_bad), "dnatok_mbp_per_s": round(bp / t_gpu / 1e6, 2),
+                     "hf_mbp_per_s": None if a.no_hf else round(bp / t_hf / 1e6, 2),
+                     "speedup_dnatok_vs_hf": None if a.no_hf else round(t_hf / t_gpu, 2)}
+    return code, {"tokenizer": s.where, "selected_path": s.path, "chunk": a.chunk, "hf_threads": a.hf_threads, "scenarios": out}
+
+
+COMMANDS = {"info": run_info, "encode": run_encode, "validate": run_validate, "bench": run_bench, "scenarios": run_scenarios}
+
+
+def parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="dnatok_b200")
-    sub = ap.add_subparsers(dest="cmd", required=True)
-    for name, fn in (("info", cmd_info), ("encode", cmd_encode), ("validate", cmd_validate), ("bench", cmd_bench)):
+    sub = ap.add_subparsers(dest="command", required=True)
+    for name in COMMANDS:
         p = sub.add_parser(name)
         p.add_argument("--tokenizer", "--model", dest="tokenizer", required=True)
         p.add_argument("--json", action="store_true")
         if name == "encode":
             p.add_argument("--seq", required=True)
-        if name in ("validate", "bench"):
-            p.add_argument("--n", type=int, default=100 if name == "validate" else 1000)
-            p.add_argument("--window", type=int, default=1024 if name == "validate" else 4096)
+        if name in ("validate", "bench", "scenarios"):
             p.add_argument("--seed", type=int, default=0)
-        if name == "bench":
+        if name in ("validate", "bench"):
+            p.add_argument("--n", type=int, default={"validate": 100, "bench": 1000}[name])
+            p.add_argument("--window", type=int, default={"validate": 1024, "bench": 4096}[name])
+        if name in ("bench", "scenarios"):
             p.add_argument("--chunk", type=int, default=32)
             p.add_argument("--hf-threads", type=int, default=os.cpu_count() or 1)
-        p.set_defaults(fn=fn)
-    a = ap.parse_args(argv)
+        if name == "scenarios":
+            p.add_argument("--only", default="", help="comma-separated scenario names (default: all eight)")
+            p.add_argument("--reads", type=int, default=0, help="reads per scenario (0: the scenario's own count)")
+            p.add_argument("--check", type=int, default=64, help="reads per scenario compared with Hugging Face")
+            p.add_argument("--no-hf", action="store_true", help="skip timing the Hugging Face tokenizer")
+    return ap
+
+
+def show(payload, as_json: bool) -> None:
+    if as_json:
+        print(json.dumps(payload))
+        return
+    for key, value in payload.items():
+        if isinstance(value, dict):
+            print(key)
+            for k2, v2 in value.items():
+                print("  %-18s %s" % (k2, v2))
+        else:
+            print("%-24s %s" % (key, value))
+
+
+def main(argv=None) -> int:
+    a = parser().parse_args(argv)
+    if getattr(a, "hf_threads", None):
+        os.environ["RAYON_NUM_THREADS"] = str(a.hf_threads)
+        os.environ["TOKENIZERS_PARALLELISM"] = "true" if a.hf_threads > 1 else "false"
     try:
-        return a.fn(a)
-    except Exception as e:                                   # same contract as the reference CLI: message + non-zero exit
+        code, payload = COMMANDS[a.command](Session(a.tokenizer), a)
+    except Exception as e:                                   # message and a non-zero exit, like the reference tool
         print("error: %s: %s" % (type(e).__name__, e), file=sys.stderr)
         return 2
+    show(payload, a.json)
+    return code
 
 
 if __name__ == "__main__":

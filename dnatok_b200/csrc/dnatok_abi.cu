@@ -31,6 +31,8 @@ std::atomic<int64_t> g_host_mask_threads{-1};                 // -1: as many as 
 std::atomic<int64_t> g_host_mask_min_bytes{16ll << 20};      // smaller masks are not worth the threads
 thread_local int64_t g_last_h2d = 0, g_last_d2h = 0;          // bytes the last dnatok_encode_host of this thread copied
 std::atomic<int64_t> g_kmer_force_segments{0};                // 1: segment encoder whenever scratch is given
+std::atomic<int64_t> g_kmer_poll_limit{1 << 20};              // polls before a segment gives up waiting for the one before it
+std::atomic<int64_t> g_kmer_test_withhold{-1};                // tests: the ticket whose segment publishes nothing
 std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the host link (in + out) per chunk of the host pipeline
 std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
@@ -257,6 +259,13 @@ int bpe_launch_info(int dev, const BpeLaunchInfo** out) {
         cudaFuncAttributes fa;
         CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_long_kernel));      // loads the kernel's code now, not at its first launch
         CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_classify_kernel));
+        // ... and the kernels of the output stage, for both id widths
+        CUDA_TRY(cudaFuncGetAttributes(&fa, span_lengths_kernel));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, scan_lengths_kernel));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, emit_padded_kernel<uint16_t, int64_t, false, EMIT_SPAN>));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, emit_padded_kernel<uint16_t, int32_t, false, EMIT_SPAN>));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, emit_ragged_kernel<uint16_t, int64_t, false>));
+        CUDA_TRY(cudaFuncGetAttributes(&fa, emit_ragged_kernel<uint16_t, int32_t, false>));
         it = info.emplace(dev, li).first;
     }
     *out = &it->second;
@@ -409,7 +418,7 @@ void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_
 // Scratch of the segmented k-mer kernel: one flag per (segment, row).  The number of segments follows
 // the average row (or the caller's row-length hint, when that is larger); longer rows finish inside
 // the last segment.
-struct KmerScratch { uint32_t* flags; int n_seg; size_t bytes; };
+struct KmerScratch { unsigned long long* tickets; uint32_t* flags; int n_seg; size_t bytes; };
 
 KmerScratch kmer_scratch_layout(const dnatok_handle* h, void* base, int64_t n_rows, int64_t total_bytes) {
     KmerScratch s{};
@@ -426,7 +435,8 @@ KmerScratch kmer_scratch_layout(const dnatok_handle* h, void* base, int64_t n_ro
     if (n_seg < 1) n_seg = 1;
     if (n_seg > (1 << 20)) n_seg = 1 << 20;
     s.n_seg = (int)n_seg;
-    s.flags = (uint32_t*)base;
+    s.tickets = (unsigned long long*)base;                       // the ticket counter has the first 256 bytes to itself
+    s.flags = (uint32_t*)((uint8_t*)base + 256);
     s.bytes = 256 + (size_t)n_seg * (size_t)n_rows * 4;
     return s;
 }
@@ -437,13 +447,26 @@ void launch_kmer_seg_k(const DeviceTables& d, int32_t affine_base, const uint8_t
                        const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets, int32_t* status,
                        const KmerScratch& ks, cudaStream_t st) {
     const int64_t tickets = n_rows * ks.n_seg;
-    const int64_t want = (tickets + KW_WARPS - 1) / KW_WARPS, resident = (int64_t)d.sm_count * KSEG_BLOCKS_PER_SM;
-    const unsigned grid = (unsigned)(want < resident ? want : resident);
     const bool fuse = mask && rf.mask_bits == (int)sizeof(IdT) * 8;
     const bool affine = affine_base >= 0;
+    // as many blocks as the GPU keeps resident (the warps draw tickets from a counter, so a smaller or a
+    // larger grid would also finish; this size keeps every SM busy without idle blocks queued behind)
+    int bps = KSEG_BLOCKS_PER_SM;
+    {
+        int q = 0;
+        cudaError_t e = affine && fuse ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kmer_seg_rows_kernel<IdT, K, true, true>, KW_WARPS * 32, 0)
+                        : affine       ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kmer_seg_rows_kernel<IdT, K, true, false>, KW_WARPS * 32, 0)
+                        : fuse         ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kmer_seg_rows_kernel<IdT, K, false, true>, KW_WARPS * 32, 0)
+                                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kmer_seg_rows_kernel<IdT, K, false, false>, KW_WARPS * 32, 0);
+        if (e == cudaSuccess && q >= 1) bps = q;
+    }
+    const int64_t want = (tickets + KW_WARPS - 1) / KW_WARPS, resident = (int64_t)d.sm_count * bps;
+    const unsigned grid = (unsigned)(want < resident ? want : resident);
+    const int poll_limit = (int)g_kmer_poll_limit.load();
+    const long long withhold = (long long)g_kmer_test_withhold.load();
 #define KLAUNCH(A, F) kmer_seg_rows_kernel<IdT, K, A, F><<<grid, KW_WARPS * 32, 0, st>>>(                           \
         bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
-        lengths_out, out_offsets, status, ks.n_seg, ks.flags)
+        lengths_out, out_offsets, status, ks.n_seg, ks.flags, ks.tickets, poll_limit, withhold)
     if (affine && fuse) KLAUNCH(true, true);
     else if (affine) KLAUNCH(true, false);
     else if (fuse) KLAUNCH(false, true);
@@ -496,7 +519,8 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
     const bool long_rows = total_bytes / n_rows > KMER_WARP_MAX_AVG_LEN;
     // the flags carry 30-bit token counts: a row that might hold 2^30 tokens stays with the other kernels
     const int64_t longest = h->hint_max_row > 0 && h->hint_max_row < total_bytes ? h->hint_max_row : total_bytes;
-    if (!COUNT_ONLY && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && longest < (1ll << 30) &&
+    // a row that gave up is reported through the status array only: without one the segment encoder is not used
+    if (!COUNT_ONLY && status && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && longest < (1ll << 30) &&
         (few_rows || long_rows || g_kmer_force_segments)) {
         const KmerScratch ks = kmer_scratch_layout(h, scratch, n_rows, total_bytes);
         if (ks.bytes <= scratch_bytes && (ks.n_seg > 1 || g_kmer_force_segments)) {
@@ -648,9 +672,11 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_min_bytes")) { g_host_mask_min_bytes = value < 0 ? 0 : value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_threads")) { g_host_mask_threads = value < -1 ? -1 : value; return DNATOK_OK; }
+    if (!strcmp(name, "kmer_test_withhold_ticket")) { g_kmer_test_withhold = value < 0 ? -1 : value; return DNATOK_OK; }
     if (value < 0) return fail(DNATOK_ERR_INVALID, "bad option value");
     if (!strcmp(name, "host_chunk_bytes")) { g_host_chunk_bytes = value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_force_segments")) { g_kmer_force_segments = value ? 1 : 0; return DNATOK_OK; }
+    if (!strcmp(name, "kmer_poll_limit")) { g_kmer_poll_limit = value < 1 ? 1 : (value > (1 << 30) ? (1 << 30) : value); return DNATOK_OK; }
     if (!strcmp(name, "host_chunk_threshold")) { g_host_chunk_threshold = value; return DNATOK_OK; }
     return fail(DNATOK_ERR_INVALID, "unknown option %s", name);
 }

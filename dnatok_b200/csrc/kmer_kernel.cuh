@@ -614,9 +614,8 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
     kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
 }
 
-// Rows cut into segments of KSEG_WINDOWS windows, dealt round-robin to a grid of resident warps:
-// ticket t stands for segment t / n_rows of row t % n_rows, warp g of G takes tickets g, g + G, ...
-// (a shared ticket counter was tried: one atomic per segment caps the rate near 400 M segments/s).
+// Rows cut into segments of KSEG_WINDOWS windows.  Ticket t stands for segment t / n_rows of row
+// t % n_rows; the warps draw tickets in rising order from a counter in the scratch buffer.
 // A segment's place in the output depends on the tokens all earlier segments of its row produce
 // (a window with an N yields K tokens, not one), which is settled by a decoupled look-back:
 //   1. the warp loads and decodes its 256 windows into registers and counts their tokens;
@@ -625,16 +624,18 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
 //      already published a "total" (its own count plus everything before it) or to the row start;
 //   4. it publishes its "total" and stores its tokens.
 // Nothing is awaited before step 2, so the segments of one row run in parallel, and step 3 only
-// waits for flags of earlier tickets, whose holders are running warps (the grid never exceeds what
-// the GPU keeps resident, and every warp takes its tickets in rising order) that reach their own
-// step 2 without waiting for anybody.  The waits are bounded
-// all the same: a row whose wait ran out is reported with DNATOK_ROW_STALLED instead of tokens.
+// waits for flags of earlier tickets.  A ticket is drawn by a warp that is running, and the warp
+// reaches step 2 of that ticket without waiting for anybody, so the holders of the flags a warp
+// waits for always make progress, however much of the grid the GPU keeps resident.  The waits are
+// bounded all the same (poll_limit polls): a row whose wait ran out is reported with
+// DNATOK_ROW_STALLED instead of tokens.  `withhold` (tests only, -1 otherwise) names a ticket whose
+// holder publishes nothing, which is how the tests make a wait run out.
 // The last segment of a row (short windows, the len % K tail) and segments that hold anything but
 // clean k-mers place their tokens through kmer_encode_windows; clean ones store straight from
 // registers, as 16-byte pairs whatever the parity of their output offset.
 constexpr int KSEG_WINDOWS = 256;        // four chunks of 64 windows
 constexpr int KSEG_BLOCKS_PER_SM = 4;    // 64 registers per thread: the decoded segment stays in registers
-constexpr int KSEG_POLL_LIMIT = 1 << 20;
+constexpr int KSEG_POLL_LIMIT = 1 << 20;    // default bound on the polls of one wait
 constexpr uint32_t KSEG_OWN = 1u << 30, KSEG_TOTAL = 2u << 30, KSEG_POISON = 3u << 30, KSEG_VALUE = (1u << 30) - 1u;
 
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
@@ -644,7 +645,8 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
                      const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
                      void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
                      int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
-                     int32_t* __restrict__ status, int n_seg, uint32_t* __restrict__ flags) {
+                     int32_t* __restrict__ status, int n_seg, uint32_t* __restrict__ flags,
+                     unsigned long long* __restrict__ ticket_counter, int poll_limit, long long withhold) {
     constexpr int NW = (2 * K + 3 + 3) / 4;
     constexpr uint32_t IDX_MASK = (1u << (2 * K)) - 1u;
     constexpr int NCH = KSEG_WINDOWS / 64;
@@ -653,23 +655,15 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
     const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
     const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
     const int64_t n_tickets = n_rows * (int64_t)n_seg;
-    const int64_t n_warps = (int64_t)gridDim.x * KW_WARPS;
-    // (segment, row) of the ticket after this warp's current one, kept in step without dividing; its
-    // row bounds are fetched while the current ticket is being worked on
-    const int64_t t0 = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
-    if (t0 >= n_tickets) return;
-    int seg2 = (int)(t0 / n_rows);
-    int64_t row2 = t0 - (int64_t)seg2 * n_rows;
-    const int step_seg = (int)(n_warps / n_rows);
-    const int64_t step_row = n_warps - (int64_t)step_seg * n_rows;
-    int64_t off2 = offsets[row2], end2 = offsets[row2 + 1];
-    for (int64_t t = t0; t < n_tickets; t += n_warps) {
-        const int seg = seg2;
-        const int64_t row = row2, off = off2, end = end2;
-        seg2 += step_seg;
-        row2 += step_row;
-        if (row2 >= n_rows) { row2 -= n_rows; ++seg2; }
-        if (t + n_warps < n_tickets) { off2 = offsets[row2]; end2 = offsets[row2 + 1]; }
+    for (;;) {
+        unsigned long long drawn = 0;
+        if (lane == 0) drawn = atomicAdd(ticket_counter, 1ull);
+        const int64_t t = (int64_t)__shfl_sync(0xffffffffu, drawn, 0);
+        if (t >= n_tickets) break;
+        const int seg = (int)(t / n_rows);
+        const int64_t row = t - (int64_t)seg * n_rows;
+        const int64_t off = offsets[row], end = offsets[row + 1];
+        const bool publish = t != (int64_t)withhold;
 
         const KmerRow<IdT> r = kmer_row_setup<IdT, K>(bytes, off, end, row, total_bytes, f, ids, lengths_in, out_offsets);
         const int64_t w0 = (int64_t)seg * KSEG_WINDOWS;
@@ -734,7 +728,7 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
                 count = __reduce_add_sync(0xffffffffu, cnt);
             }
             // ---- 2. publish the own count (segment 0 knows its total already)
-            if (lane == 0) *(volatile uint32_t*)my_flag = (seg == 0 ? KSEG_TOTAL : KSEG_OWN) | (uint32_t)count;
+            if (lane == 0 && publish) *(volatile uint32_t*)my_flag = (seg == 0 ? KSEG_TOTAL : KSEG_OWN) | (uint32_t)count;
         }
 
         // ---- 3. tokens before this segment
@@ -752,7 +746,7 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
                 const int first_total = totals ? __ffs(totals) - 1 : 32;
                 const unsigned wanted = first_total >= 31 ? 0xffffffffu : ((2u << first_total) - 1u);
                 if (empties & wanted) {
-                    if (++polls > KSEG_POLL_LIMIT) { stalled = true; break; }
+                    if (++polls > poll_limit) { stalled = true; break; }
                     __nanosleep(64);
                 } else {
                     sum += __reduce_add_sync(0xffffffffu, lane <= first_total ? (look & KSEG_VALUE) : 0u);
@@ -773,7 +767,7 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
             continue;
         }
         // ---- 4. publish the total, place the tokens
-        if (!last && seg > 0 && lane == 0) *(volatile uint32_t*)my_flag = KSEG_TOTAL | (uint32_t)(base + count);
+        if (!last && seg > 0 && lane == 0 && publish) *(volatile uint32_t*)my_flag = KSEG_TOTAL | (uint32_t)(base + count);
 
         if (in_regs && clean && base + KSEG_WINDOWS <= cap) {
             IdT* d = r.dst + base;

@@ -17,7 +17,10 @@ tokenisation path, with the same names, argument meaning and error behaviour:
 
 Where the reference computes on the CPU with numpy, everything here runs in the kernels; a
 tokenizer the tables cannot express raises (the reference would fall back to the Hugging Face
-tokenizer, which this library does not do).
+tokenizer, which this library does not do).  No string is rewritten in Python: ``normalize_case``
+and ``handle_invalid_chars`` are a byte translation inside the native packer's one copy and a change
+of the 256-entry id table, padding sides and masks come from the kernels, and the narrow id type
+of ``encode_batch_with_padding`` is a cast on the device before the copy back.
 
 ``encode_batch_with_padding`` on a k-mer tokenizer keeps the reference's literal procedure (pad the
 strings with ``N`` to the target width, encode, overwrite everything past ``ceil(len/k)`` with the
@@ -33,8 +36,7 @@ import numpy as np
 
 from .tables import UnsupportedTokenizer, spec_from_tokenizer
 
-_ALLOWED_UPPER = frozenset("ACGTN")
-_ALLOWED_ALL = frozenset("ACGTNacgtn")
+_UPPER = bytes((c - 32 if 97 <= c <= 122 else c) for c in range(256))      # what str.upper() does to ASCII
 
 
 class DNATok:
@@ -57,17 +59,20 @@ class DNATok:
         self.vocab_size = 0
         self.bpe_backend = None
         self._tok = None
+        self._spec = None
+        self._built_for = None
 
     # ------------------------------------------------------------------ discovery
     def discover(self) -> None:
-        from .tokenizer import B200Tokenizer
         self.use_ids_path = False
         self.kmer_k = None
         self.bpe_backend = None
         self._tok = None
+        self._built_for = None
         if self.tokenizer is None:
             raise UnsupportedTokenizer("embedder has no tokenizer")
         spec = spec_from_tokenizer(self.tokenizer)
+        self._spec = spec
         self.id_pad = self.pad_id = spec.specials.pad_id
         self.unk_id = spec.specials.unk_id
         self.vocab_size = spec.vocab_size
@@ -75,29 +80,60 @@ class DNATok:
             from .gputok_bpe_backend import GPUTokBPEBackend
             self.bpe_backend = GPUTokBPEBackend(self.tokenizer, engine="dnatok")
             return
-        self._tok = B200Tokenizer(spec)
         self.use_ids_path = True
         self.kmer_k = spec.k if spec.kind == "kmer" else None
 
-    # ------------------------------------------------------------------ helpers
-    def _normalize_and_clean_seqs(self, seqs: List[str]) -> List[str]:
-        if not (self.normalize_case or self.handle_invalid_chars):
-            return seqs
-        allowed = _ALLOWED_UPPER if self.normalize_case else _ALLOWED_ALL
-        out = []
-        for s in seqs:
-            if self.normalize_case:
-                s = s.upper()
-            if self.handle_invalid_chars and not allowed.issuperset(s):
-                s = "".join(ch if ch in allowed else "N" for ch in s)
-            out.append(s)
-        return out
+    # ------------------------------------------------------------------ the flags as tables
+    def _byte_table(self) -> Optional[bytes]:
+        """The text rewriting of the reference's ``_normalize_and_clean_seqs`` (``src/dna_tokenizer.py:1535-1558``)
+        as one 256-entry byte translation applied while the rows are packed: upper-casing for
+        ``normalize_case``; for the BPE path (which has no invalid-character id) ``handle_invalid_chars``
+        turns every character outside the alphabet into ``N``."""
+        table = bytearray(range(256))
+        if self.normalize_case:
+            table = bytearray(_UPPER)
+        if self.handle_invalid_chars and not self.use_ids_path:
+            allowed = b"ACGTN" if self.normalize_case else b"ACGTNacgtn"
+            for c in range(256):
+                if table[c] not in allowed:
+                    table[c] = ord("N")
+        if bytes(table) == bytes(range(256)):
+            return None
+        return bytes(table)
 
-    def _encode_device(self, seqs: List[str], pad_left: bool, width: Optional[int] = None):
-        tok = self._tok
+    def _tokenizer(self):
+        """The kernel front end for the current flags.  On the table paths ``handle_invalid_chars`` gives every
+        character outside the alphabet the tokenizer's unknown id (the reference's ``invalid_char_id``,
+        ``src/dna_tokenizer.py:926,948,1017``; the id of ``N`` only when there is no unknown id), which is a
+        change of the 256-entry id table, not of the text (``:1810-1819``)."""
+        from .tokenizer import B200Tokenizer
+        key = (self.normalize_case, self.handle_invalid_chars)
+        if self._tok is not None and self._built_for == key:
+            return self._tok
+        import copy
+        spec = copy.copy(self._spec)
+        if self.handle_invalid_chars:
+            lut = np.array(spec.lut256, dtype=np.int32, copy=True)
+            has_unk = getattr(self.tokenizer, "unk_token_id", None) is not None
+            invalid_id = int(self.unk_id) if has_unk else int(lut[ord("N")])
+            allowed = b"ACGTN" if self.normalize_case else b"ACGTNacgtn"
+            for c in range(256):
+                if c not in allowed:
+                    lut[c] = invalid_id
+            spec.lut256 = lut
+        self._tok = B200Tokenizer(spec)
+        self._built_for = key
+        return self._tok
+
+    def _encode_device(self, seqs: List[str], pad_left: bool, width: Optional[int] = None, *, pad_to_chars: int = 0,
+                       trunc_to_chars: int = 0, mask_dtype=None, return_mask: bool = False):
+        tok = self._tokenizer()
         tok.padding_side = "left" if pad_left else "right"
-        d_bytes, d_off, offsets = tok.to_device(seqs)
+        d_bytes, d_off, offsets = tok.to_device(seqs, table=self._byte_table(), pad_to=pad_to_chars, pad_left=pad_left,
+                                                trunc_to=trunc_to_chars)
         kw = dict(padding="longest") if width is None else dict(padding="max_length", max_length=int(width))
+        if return_mask:
+            kw.update(return_attention_mask=True, mask_dtype=mask_dtype)
         return tok.encode_device(d_bytes, d_off, host_offsets=offsets, add_special_tokens=False, **kw)
 
     # ------------------------------------------------------------------ public encode paths
@@ -105,39 +141,43 @@ class DNATok:
         import torch
         if not seqs:
             raise ValueError("No sequences provided.")
-        if self._tok is None and self.bpe_backend is None:
+        if self._spec is None or (not self.use_ids_path and self.bpe_backend is None):
             raise RuntimeError("discover() has not been run (or found no supported path)")
-        seqs = self._normalize_and_clean_seqs(list(seqs))
+        seqs = list(seqs)
         left = self.padding_side == "left"
+        width = None
         if not self.use_ids_path:
-            ids_dev, mask_dev = self.bpe_backend.encode_batch(seqs, device="cuda")
-            ids = ids_dev.cpu()
-            if left:                                   # the backend pads on the right; move the padding
-                lens = mask_dev.sum(dim=1).cpu()
-                out = torch.full_like(ids, self.pad_id)
-                T = ids.shape[1]
-                for i, n in enumerate(lens.tolist()):
-                    out[i, T - n:] = ids[i, :n]
-                ids = out
+            # the plug-in's own tokenizer, asked to pad on this object's side (the kernels pad on either side)
+            tok = self.bpe_backend._tok
+            old = tok.padding_side
+            tok.padding_side = "left" if left else "right"
+            try:
+                d_bytes, d_off, offsets = tok.to_device(seqs, table=self._byte_table())
+                ids = tok.encode_device(d_bytes, d_off, host_offsets=offsets, padding="longest",
+                                        add_special_tokens=False, return_attention_mask=False)["input_ids"]
+            finally:
+                tok.padding_side = old
         else:
-            ids = self._encode_device(seqs, left)["input_ids"].cpu()
+            ids = self._encode_device(seqs, left)["input_ids"]
         if self.token_len is not None and ids.shape[1] < int(self.token_len):
-            pad = torch.full((ids.shape[0], int(self.token_len) - ids.shape[1]), self.pad_id, dtype=ids.dtype)
+            pad = torch.full((ids.shape[0], int(self.token_len) - ids.shape[1]), self.pad_id, dtype=ids.dtype, device=ids.device)
             ids = torch.cat([pad, ids], dim=1) if left else torch.cat([ids, pad], dim=1)
-        return ids.pin_memory() if torch.cuda.is_available() else ids
+        out = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=torch.cuda.is_available())
+        out.copy_(ids)
+        return out
 
     def encode_batch_with_padding(self, seqs: List[str], max_tokens: int, pad_to_max: bool = False,
                                   pad_multiple: int = 16) -> Tuple[Any, Any]:
         import torch
         if not seqs:
             raise ValueError("Empty batch")
-        if not self.use_ids_path or self._tok is None:
+        if not self.use_ids_path or self._spec is None:
             raise RuntimeError("encode_batch_with_padding needs a per-character or k-mer tokenizer (run discover())")
         k = int(self.kmer_k) if self.kmer_k else 1
         max_chars = int(max_tokens) * k
-        seqs = [s[:max_chars] for s in seqs]
-        char_lengths = [len(s) for s in seqs]
-        target_chars = max(char_lengths)
+        seqs = list(seqs)
+        char_lengths = np.minimum(np.fromiter(map(len, seqs), dtype=np.int64, count=len(seqs)), max_chars)
+        target_chars = int(char_lengths.max())
         if pad_to_max:
             target_chars = max(target_chars, max_chars)
         if k > 1 and target_chars % k:
@@ -147,22 +187,23 @@ class DNATok:
             target_tokens += pad_multiple - target_tokens % pad_multiple
         target_chars = target_tokens * k
         left = self.padding_side == "left"
-
-        seqs = self._normalize_and_clean_seqs(seqs)
-        if k == 1:
-            # one token per character: padding the strings with N and overwriting those columns with
-            # the pad id equals padding with the pad id directly, which the kernel does in one pass
-            ids = self._encode_device(seqs, left, width=target_tokens)["input_ids"].cpu()
-        else:
-            padded = [s.rjust(target_chars, "N") if left else s.ljust(target_chars, "N") for s in seqs]
-            ids = self._encode_device(padded, left)["input_ids"].cpu()
-        T = ids.shape[1]
-        token_lengths = torch.tensor([(n + k - 1) // k for n in char_lengths], dtype=torch.long)
-        cols = torch.arange(T, dtype=torch.long).unsqueeze(0)
-        keep = cols >= (T - token_lengths.unsqueeze(1)) if left else cols < token_lengths.unsqueeze(1)
         max_id = max(int(self.vocab_size or 0) - 1, int(self.id_pad))
         dtype = torch.uint8 if max_id <= 255 else torch.int16 if max_id <= 32767 else \
             torch.int32 if max_id <= 2147483647 else torch.int64
-        ids = ids.to(dtype)
-        ids[~keep] = int(self.id_pad)
-        return ids, keep.to(torch.uint8)
+
+        if k == 1:
+            # one token per character: padding the strings with N and overwriting those columns with
+            # the pad id equals padding with the pad id directly, which the kernel does in one pass,
+            # mask included
+            enc = self._encode_device(seqs, left, width=target_tokens, trunc_to_chars=max_chars, return_mask=True,
+                                      mask_dtype=torch.uint8)
+            return enc["input_ids"].to(dtype).cpu(), enc["attention_mask"].cpu()
+        # k-mers: the rows are padded with N to the target width while they are packed (the window frame of a
+        # left-padded row depends on it), encoded, and everything past ceil(len / k) tokens becomes padding
+        ids = self._encode_device(seqs, left, pad_to_chars=target_chars, trunc_to_chars=max_chars)["input_ids"]
+        T = ids.shape[1]
+        token_lengths = torch.from_numpy((char_lengths + k - 1) // k).to(ids.device)
+        cols = torch.arange(T, dtype=torch.long, device=ids.device).unsqueeze(0)
+        keep = cols >= (T - token_lengths.unsqueeze(1)) if left else cols < token_lengths.unsqueeze(1)
+        ids = torch.where(keep, ids, torch.full((), int(self.id_pad), dtype=ids.dtype, device=ids.device)).to(dtype)
+        return ids.cpu(), keep.to(torch.uint8).cpu()

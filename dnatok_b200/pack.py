@@ -13,25 +13,44 @@ import numpy as np
 Packed = Tuple[np.ndarray, np.ndarray]     # (uint8[total], int64[B+1])
 
 
-def pack_strings(seqs: Sequence[Union[str, bytes]]) -> Packed:
+def _native():
+    try:
+        from . import _pack
+    except ImportError as e:
+        raise RuntimeError("the host packer dnatok_b200/_pack.so is not built; run `python -m dnatok_b200.build` (%s)" % e)
+    return _pack
+
+
+def pack_sizes(seqs, pad_to: int = 0, trunc_to: int = 0) -> int:
+    """Bytes the rows of a list take once packed (every row at least ``pad_to`` bytes, at most ``trunc_to``)."""
+    if not isinstance(seqs, (list, tuple)):
+        seqs = list(seqs)
+    if not seqs:
+        return 0
+    return int(_native().sizes(seqs, np.zeros(len(seqs) + 1, dtype=np.int64), int(pad_to), int(trunc_to)))
+
+
+def pack_strings(seqs: Sequence[Union[str, bytes]], *, table: bytes = None, pad_to: int = 0, pad_byte: int = ord("N"),
+                 pad_left: bool = False, trunc_to: int = 0, out: np.ndarray = None) -> Packed:
+    """Rows of a list into one buffer through the native packer (one pass over the list, threaded copy, no
+    intermediate string).  ``table`` translates every byte on the way (256 entries); ``pad_to`` pads every
+    shorter row to that many bytes with ``pad_byte`` on the chosen side; ``trunc_to`` keeps only the first
+    so many bytes of a row; ``out`` is a uint8 buffer to fill
+    (for instance pinned memory), which must be large enough."""
+    if not isinstance(seqs, (list, tuple)):
+        seqs = list(seqs)
     n = len(seqs)
     offsets = np.zeros(n + 1, dtype=np.int64)
     if n == 0:
         return np.zeros(0, dtype=np.uint8), offsets
-    if isinstance(seqs[0], (bytes, bytearray)):
-        lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=n)
-        buf = b"".join(seqs)
-    else:
-        lens = np.fromiter((len(s) for s in seqs), dtype=np.int64, count=n)
-        try:
-            buf = "".join(seqs).encode("ascii")
-        except UnicodeEncodeError as e:
-            raise ValueError("sequences must be ASCII: %s" % e) from None
-    np.cumsum(lens, out=offsets[1:])
-    flat = np.frombuffer(buf, dtype=np.uint8)
-    if flat.shape[0] != offsets[-1]:
-        raise ValueError("packed length mismatch")
-    return flat, offsets
+    P = _native()
+    total = P.sizes(seqs, offsets, int(pad_to), int(trunc_to))
+    if out is None:
+        out = np.empty(max(total, 1), dtype=np.uint8)
+    elif out.size < total:
+        raise ValueError("output buffer holds %d bytes, %d needed" % (out.size, total))
+    P.copy(seqs, offsets, out, table, int(pad_to), int(pad_byte), 1 if pad_left else 0, 0, int(trunc_to))
+    return out[:total], offsets
 
 
 def pack_any(x) -> Packed:

@@ -185,3 +185,62 @@ def pack_rows(a: np.ndarray):
 def rows_to_strings(flat: np.ndarray, offsets: np.ndarray) -> list[str]:
     buf = flat.tobytes()
     return [buf[offsets[i]:offsets[i + 1]].decode("ascii") for i in range(len(offsets) - 1)]
+
+
+# ----------------------------------------------------------------------------- read-length scenarios
+# The eight workloads of the reference's realistic benchmark (benchmarks/run_realistic_benchmark.py:184-272)
+# as seeded generators: the same names, read counts, length distributions, N rates and base compositions,
+# drawn here with numpy (the reference draws with ``random.Random``; the sequences differ, the shapes do not).
+
+SCENARIOS = {
+    # name: (reads, description)
+    "illumina_short": (5000, "short reads: length ~ Normal(150, 30) clipped to [50, 300]"),
+    "pacbio_hifi": (1000, "HiFi long reads: length ~ Normal(15000, 3000) clipped to [5000, 25000]"),
+    "nanopore_long": (500, "nanopore reads: length ~ LogNormal(ln 10000, 0.7) clipped to [1000, 100000]"),
+    "gene_models": (2000, "gene-length records: log-uniform in [500, 50000]"),
+    "mixed_clinical": (2000, "60 % short, 30 % medium (500..5000), 10 % long (~15000) reads, 0.5 % N"),
+    "gc_low_20": (2000, "AT-rich genome (20 % GC), 1 kbp reads"),
+    "gc_high_65": (2000, "GC-rich genome (65 % GC), 1 kbp reads"),
+    "repeats_polyA": (1000, "1 kbp reads each holding a 200-bp poly-A stretch"),
+}
+
+
+def scenario(name: str, n_reads: int | None = None, seed: int = 0):
+    """(flat uint8, int64 offsets) of one read-length scenario."""
+    if name not in SCENARIOS:
+        raise KeyError("unknown scenario %r (one of %s)" % (name, ", ".join(SCENARIOS)))
+    n = SCENARIOS[name][0] if n_reads is None else int(n_reads)
+    rng = np.random.default_rng(BASE_SEED + 7000 + 17 * list(SCENARIOS).index(name) + seed)
+    clip = lambda x, lo, hi: np.clip(np.floor(x), lo, hi).astype(np.int64)
+    weights, n_rate = np.full(4, 0.25), 0.0
+    if name == "illumina_short":
+        lens, n_rate = clip(rng.normal(150, 30, n), 50, 300), 0.001
+    elif name == "pacbio_hifi":
+        lens = clip(rng.normal(15000, 3000, n), 5000, 25000)
+    elif name == "nanopore_long":
+        lens, n_rate = clip(rng.lognormal(np.log(10000), 0.7, n), 1000, 100000), 0.002
+    elif name == "gene_models":
+        lens = clip(np.exp(rng.uniform(np.log(500), np.log(50000), n)), 500, 50000)
+    elif name == "mixed_clinical":
+        u = rng.random(n)
+        lens = np.where(u < 0.60, clip(rng.normal(150, 30, n), 50, 300),
+                        np.where(u < 0.90, clip(rng.uniform(500, 5000, n), 500, 5000),
+                                 clip(rng.normal(15000, 5000, n), 5000, 30000)))
+        n_rate = 0.005
+    elif name == "gc_low_20":
+        lens, weights = np.full(n, 1000, np.int64), np.array([0.40, 0.10, 0.10, 0.40])
+    elif name == "gc_high_65":
+        lens, weights = np.full(n, 1000, np.int64), np.array([0.175, 0.325, 0.325, 0.175])
+    else:
+        lens = np.full(n, 1000, np.int64)
+    offsets = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(lens, out=offsets[1:])
+    total = int(offsets[-1])
+    flat = _ACGT[rng.choice(4, size=total, p=weights).astype(np.uint8)]
+    if n_rate > 0:
+        flat[rng.random(total) < n_rate] = ord("N")
+    if name == "repeats_polyA":
+        starts = offsets[:-1] + rng.integers(0, 800, size=n)
+        for s in starts.tolist():
+            flat[s:s + 200] = ord("A")
+    return flat, offsets

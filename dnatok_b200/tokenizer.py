@@ -55,6 +55,8 @@ class B200Tokenizer:
         self.device = torch.device(device if not isinstance(device, int) else "cuda:%d" % device)
         self.padding_side = spec.specials.padding_side
         self.check_status = True
+        self._pin = None            # pinned host buffer the native packer fills
+        self._pin_done = None       # event: the last copy out of it
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -292,12 +294,39 @@ class B200Tokenizer:
                              "(Hugging Face cannot build a tensor from such a batch either)"
                              % int(np.flatnonzero(st & _cabi.ROW_CLIPPED)[0]))
 
-    def to_device(self, seqs):
+    def to_device(self, seqs, *, table: Optional[bytes] = None, pad_to: int = 0, pad_byte: int = ord("N"),
+                  pad_left: bool = False, trunc_to: int = 0):
         """Pack rows on the host (after the tokenizer's normalizer) and copy them to the GPU:
-        returns (uint8[total] CUDA tensor, int64[B+1] CUDA tensor, host offsets)."""
+        returns (uint8[total] CUDA tensor, int64[B+1] CUDA tensor, host offsets).  Lists of str / bytes go
+        through the native packer straight into a pinned buffer that the tokenizer keeps and reuses; ``table``
+        (256 bytes) translates every byte on the way and ``pad_to`` pads short rows, both inside that one copy."""
         torch = _torch()
-        flat, offsets = pack_any(self._normalize(seqs))
         dev = self.device
+        seqs = self._normalize(seqs)
+        if isinstance(seqs, (list, tuple)):
+            from .pack import pack_sizes, pack_strings
+            if len(seqs) == 0:
+                return (torch.empty(0, dtype=torch.uint8, device=dev), torch.zeros(1, dtype=torch.int64, device=dev),
+                        np.zeros(1, dtype=np.int64))
+            need = pack_sizes(seqs, pad_to, trunc_to)
+            if self._pin_done is not None:
+                self._pin_done.synchronize()             # the copy out of the pinned buffer by the call before
+            if self._pin is None or self._pin.numel() < need:
+                self._pin = torch.empty(max(need + need // 4, 1 << 16), dtype=torch.uint8).pin_memory()
+            flat, offsets = pack_strings(seqs, table=table, pad_to=pad_to, pad_byte=pad_byte, pad_left=pad_left,
+                                         trunc_to=trunc_to, out=self._pin.numpy())
+            with torch.cuda.device(dev):
+                d_bytes = torch.empty(flat.size, dtype=torch.uint8, device=dev)
+                d_bytes.copy_(self._pin[:flat.size], non_blocking=True)
+                d_off = torch.from_numpy(offsets).to(dev)
+                self._pin_done = torch.cuda.Event()
+                self._pin_done.record()
+            return d_bytes, d_off, offsets
+        if pad_to or trunc_to:
+            raise ValueError("pad_to / trunc_to need a list of rows")
+        flat, offsets = pack_any(seqs)
+        if table is not None:
+            flat = np.frombuffer(table, dtype=np.uint8)[flat]
         d_bytes = torch.from_numpy(flat).to(dev) if flat.size else torch.empty(0, dtype=torch.uint8, device=dev)
         return d_bytes, torch.from_numpy(offsets).to(dev), offsets
 

@@ -101,9 +101,10 @@ int dnatok_set_row_bytes_hint(dnatok_handle* h, int64_t min_bytes, int64_t max_b
 
 /* Bytes of caller-owned device scratch dnatok_prepare / dnatok_encode use for this batch
  * (0 for char).  The scratch must be 256-byte aligned.  BPE requires it.  For k-mer it is optional
- * (one flag per row segment): with it, batches that one warp per row could not spread over the
- * whole GPU (few rows, or very long rows) are cut into segments of 256 windows dealt round-robin
- * to resident warps; without it one warp (or one block, for very long rows) encodes each row.
+ * (one flag per row segment and a ticket counter): with it and with a status array, batches that one
+ * warp per row could not spread over the whole GPU (few rows, or very long rows) are cut into segments
+ * of 256 windows that the warps draw from the counter; without it one warp (or one block, for very
+ * long rows) encodes each row.
  * Results are identical.  The size depends on the handle's row-length hint: query it after
  * dnatok_set_row_bytes_hint. */
 size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes);
@@ -152,6 +153,9 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
  *     DNATOK_ERR_CAPACITY with the sizes in dnatok_last_error(); nothing is launched.
  *   - The handle's merge tables must already be on the current device: one earlier
  *     dnatok_prepare / dnatok_encode call there uploads them; otherwise DNATOK_ERR_INVALID.
+ *     That earlier call also loads and configures every kernel the BPE path can launch (all
+ *     length classes, both id widths), so that this entry point does not meet a kernel for the
+ *     first time: loading a kernel's code is a step the CUDA runtime may allocate for.
  *   - The first call on each device also resolves the array's device address (once per device,
  *     with that device current); make that first call outside any stream capture.
  *   - All calls, on any handle and stream, share the one array, and it keeps the previous call's
@@ -207,7 +211,12 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *                           being produced on the GPU and copied too (-1, default: one per core, at most 16;
  *                           0: always copy the mask from the device)
  *   "host_mask_min_bytes"   the size from which a mask is written by host threads (default 16 MiB)
- *   "kmer_force_segments"   1: use the k-mer segment encoder whenever scratch is given, whatever the batch shape
+ *   "kmer_force_segments"   1: use the k-mer segment encoder whenever scratch and a status array are given, whatever
+ *                           the batch shape
+ *   "kmer_poll_limit"       polls after which a k-mer row segment stops waiting for the segment before it and the row
+ *                           gets DNATOK_ROW_STALLED (default 2^20, about 70 ms)
+ *   "kmer_test_withhold_ticket"  for tests of that path: the segment with this ticket number (segment * n_rows + row)
+ *                           publishes nothing, so the segments after it in its row give up; -1 (default): none
  *   "bpe_block_team_rows"   BPE batches of at most this many rows give every word a whole thread block
  *                           instead of one warp (lower latency when the batch cannot fill the GPU);
  *                           -1 (default): 8 rows per SM */

@@ -635,13 +635,105 @@ def test_seeded_fuzz_against_live_hf(toks, name):
         assert mine(strs, add_special_tokens=special)["input_ids"] == [list(r) for r in rows]
 
 
+def test_kmer_segment_wait_runs_out_on_one_row_only():
+    """The bounded wait of the k-mer segment encoder: one segment is told (test option) to publish nothing
+    and the poll limit is set to a few polls, so the later segments of that row give up.  That row gets
+    DNATOK_ROW_STALLED, every other row is exact, and the call returns at once.  Nothing waits for ever:
+    the wait ends after poll_limit polls whatever happens."""
+    import ctypes, time
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    spec = H.spec("kmer6")
+    handle = _cabi.Handle(spec)
+    rows, length = 12, 6 * 256 * 5 + 77                  # six segments per row
+    flat, offs = synth.pack_rows(synth.config2(batch=rows, length=length, seed=77))
+    d_b, d_o = dev(flat, offs)
+    B, total = rows, len(flat)
+    stride = 1400
+    need = L.dnatok_scratch_bytes(handle.ptr, B, total)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    ids = torch.zeros((B, stride), dtype=torch.int64, device="cuda")
+    mask = torch.zeros((B, stride), dtype=torch.int64, device="cuda")
+    lengths = torch.zeros(B, dtype=torch.int32, device="cuda")
+    status = torch.zeros(B, dtype=torch.int32, device="cuda")
+    fmt = _cabi.Format(64, 64, 0, 0, stride, stride)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    victim = 3
+    _cabi.check(L.dnatok_set_option(b"kmer_force_segments", 1))
+    _cabi.check(L.dnatok_set_option(b"kmer_poll_limit", 8))
+    _cabi.check(L.dnatok_set_option(b"kmer_test_withhold_ticket", 1 * rows + victim))    # segment 1 of the victim row
+    try:
+        t0 = time.perf_counter()
+        _cabi.check(L.dnatok_encode(handle.ptr, p(d_b), p(d_o), B, total, ctypes.byref(fmt), p(ids), p(mask), p(lengths),
+                                    None, p(status), p(scratch), need, None))
+        torch.cuda.synchronize()
+        took = time.perf_counter() - t0
+    finally:
+        _cabi.check(L.dnatok_set_option(b"kmer_force_segments", 0))
+        _cabi.check(L.dnatok_set_option(b"kmer_poll_limit", 1 << 20))
+        _cabi.check(L.dnatok_set_option(b"kmer_test_withhold_ticket", -1))
+    assert took < 1.0
+    st = status.cpu().numpy()
+    assert st[victim] & _cabi.ROW_STALLED
+    assert not (np.delete(st, victim) & _cabi.ROW_STALLED).any()
+    want_ids, want_mask = H.oracle_batch("kmer6", flat, offs, padding="max_length", max_length=stride, truncation=True,
+                                         add_special=False)
+    got_ids, got_mask = ids.cpu().numpy(), mask.cpu().numpy()
+    others = [r for r in range(rows) if r != victim]
+    assert np.array_equal(got_ids[others], want_ids[others]) and np.array_equal(got_mask[others], want_mask[others])
+    # the same call without the test option: every row exact, no status
+    status.zero_()
+    _cabi.check(L.dnatok_set_option(b"kmer_force_segments", 1))
+    try:
+        _cabi.check(L.dnatok_encode(handle.ptr, p(d_b), p(d_o), B, total, ctypes.byref(fmt), p(ids), p(mask), p(lengths),
+                                    None, p(status), p(scratch), need, None))
+        torch.cuda.synchronize()
+    finally:
+        _cabi.check(L.dnatok_set_option(b"kmer_force_segments", 0))
+    assert not status.any()
+    assert np.array_equal(ids.cpu().numpy(), want_ids) and np.array_equal(mask.cpu().numpy(), want_mask)
+    handle.close()
+
+
+def test_dnatok_flags_match_reference_outputs(golden):
+    """normalize_case, handle_invalid_chars and token_len of the DNATok facade against what the reference
+    returned for the same constructor flags (its tests: tests/test_benchmark_correctness.py:146-200)."""
+    from dnatok_b200.dna_tokenizer import DNATok
+
+    class Embedder:
+        def __init__(self, tokenizer):
+            self.tokenizer = tokenizer
+
+        def embed_tokens(self, ids):
+            return ids
+
+    flags = golden["dnatok_flags"]
+    seqs = flags["seqs"]
+    for case in flags["cases"]:
+        helper = DNATok(Embedder(H.hf(case["tokenizer"])), padding_side=case["padding_side"],
+                        normalize_case=case["normalize_case"], handle_invalid_chars=case["handle_invalid_chars"])
+        helper.discover()
+        helper.token_len = case["token_len"]
+        ids = helper.encode_batch_to_ids(seqs).tolist()
+        tag = (case["tokenizer"], case["padding_side"], case["normalize_case"], case["handle_invalid_chars"], case["token_len"])
+        if case["tokenizer"] == "kmer6" and case["padding_side"] == "left":
+            # ragged k-mer rows: the reference leaves a row's tokens in the middle of the row (see the test
+            # above); the tokens per row and a consistent left padding are what is compared
+            pad = helper.id_pad
+            for mine, ref in zip(ids, case["ids"]):
+                assert [t for t in mine if t != pad] == [t for t in ref if t != pad], tag
+                assert len(mine) == len(ref), tag
+        else:
+            assert ids == case["ids"], tag
+
+
 def test_row_length_hint_flags_rows_outside_it():
     """A wrong dnatok_set_row_bytes_hint must not lose rows silently: they get a status bit."""
     import ctypes
     from dnatok_b200 import _cabi
     L = _cabi.lib()
     handle = _cabi.Handle(H.spec("bpe4096"))
-    flat, offs = H.pack_strs(["ACGT" * 10, "ACGTTGCA" * 100, "AC"])
+    flat, offs = H.pack_strs(["ACGT" * 10, "ACGTTGCA" * 400, "AC"])        # the second row belongs to another length class
     d_b, d_o = dev(flat, offs)
     B, total = 3, len(flat)
     need = L.dnatok_scratch_bytes(handle.ptr, B, total)
@@ -688,6 +780,12 @@ def test_cli_validate_info_encode(capsys):
     b = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert b["total_bp"] == 64 * 256 and b["dnatok_mbp_per_s"] > 0
     assert cli.main(["info", "--tokenizer", "/nonexistent/dir"]) == 2
+    # the eight read-length scenarios at a reduced read count, ids of a sample checked against Hugging Face
+    for spec in ("kmer6", fixture):
+        assert cli.main(["scenarios", "--tokenizer", spec, "--reads", "24", "--check", "12", "--chunk", "8", "--json"]) == 0
+        sc = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["scenarios"]
+        assert len(sc) == 8 and all(v["mismatches"] == 0 and v["dnatok_mbp_per_s"] > 0 for v in sc.values())
+        assert sc["nanopore_long"]["length_max"] <= 100000 and sc["illumina_short"]["length_max"] <= 300
 
 
 @pytest.mark.parametrize("name", ["char", "byte"])

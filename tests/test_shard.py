@@ -98,3 +98,59 @@ def test_bind_host_to_gpu_is_harmless_without_nvml():
     if got is None:
         assert os.sched_getaffinity(0) == before
     os.sched_setaffinity(0, before)
+
+
+def test_read_length_scenarios_have_the_stated_shapes():
+    """The eight workloads of the reference's realistic benchmark (benchmarks/run_realistic_benchmark.py:184-272):
+    read counts, length ranges, base composition, N rate and the poly-A stretch."""
+    from dnatok_b200 import synth
+    bounds = {"illumina_short": (50, 300), "pacbio_hifi": (5000, 25000), "nanopore_long": (1000, 100000),
+              "gene_models": (500, 50000), "mixed_clinical": (50, 30000), "gc_low_20": (1000, 1000),
+              "gc_high_65": (1000, 1000), "repeats_polyA": (1000, 1000)}
+    assert list(synth.SCENARIOS) == list(bounds)
+    for name, (lo, hi) in bounds.items():
+        n = min(synth.SCENARIOS[name][0], 300)
+        flat, off = synth.scenario(name, n)
+        lens = np.diff(off)
+        assert len(lens) == n and lens.min() >= lo and lens.max() <= hi and off[-1] == flat.size
+        assert set(np.unique(flat).tolist()) <= set(b"ACGTN")
+        f2, o2 = synth.scenario(name, n)
+        assert np.array_equal(flat, f2) and np.array_equal(off, o2)          # seeded
+    gc = lambda f: np.isin(f, np.frombuffer(b"CG", np.uint8)).mean()
+    assert abs(gc(synth.scenario("gc_low_20", 200)[0]) - 0.20) < 0.02
+    assert abs(gc(synth.scenario("gc_high_65", 200)[0]) - 0.65) < 0.02
+    flat, off = synth.scenario("repeats_polyA", 50)
+    for i in range(50):
+        row = flat[off[i]:off[i + 1]].tobytes()
+        assert b"A" * 200 in row
+    assert synth.scenario("mixed_clinical", 400)[0].tolist().count(ord("N")) > 0
+    with pytest.raises(KeyError):
+        synth.scenario("nope")
+
+
+def test_native_packer_matches_join_encode():
+    """dnatok_b200._pack against the Python packing it replaces, with translation, padding and truncation."""
+    from dnatok_b200.pack import pack_sizes, pack_strings
+    rng = np.random.default_rng(3)
+    seqs = ["".join(rng.choice(list("ACGTNacgtn"), size=int(n))) for n in rng.integers(0, 400, size=300)]
+    flat, off = pack_strings(seqs)
+    assert flat.tobytes() == "".join(seqs).encode() and off.tolist() == np.concatenate([[0], np.cumsum([len(s) for s in seqs])]).tolist()
+    assert pack_sizes(seqs) == flat.size
+    mixed = [s.encode() if i % 3 == 0 else s for i, s in enumerate(seqs)]
+    assert pack_strings(mixed)[0].tobytes() == flat.tobytes()
+    upper = bytes((c - 32 if 97 <= c <= 122 else c) for c in range(256))
+    assert pack_strings(seqs, table=upper)[0].tobytes() == "".join(seqs).upper().encode()
+    f2, o2 = pack_strings(seqs, pad_to=120, trunc_to=200, pad_left=True)
+    want = [s[:200].rjust(120, "N") for s in seqs]
+    assert f2.tobytes() == "".join(want).encode() and o2[-1] == sum(map(len, want))
+    f3, _ = pack_strings(seqs, pad_to=64, pad_byte=ord("-"))
+    assert f3.tobytes() == "".join(s.ljust(64, "-") for s in seqs).encode()
+    big = ["ACGT" * 3000] * 1500                                              # 18 MB: the threaded copy
+    assert pack_strings(big)[0].tobytes() == ("ACGT" * 3000 * 1500).encode()
+    assert pack_strings([])[0].size == 0
+    with pytest.raises(ValueError):
+        pack_strings(["AC\u00e9"])
+    with pytest.raises(TypeError):
+        pack_strings([7])
+    with pytest.raises(ValueError):
+        pack_strings(seqs, out=np.empty(3, np.uint8))

@@ -73,6 +73,49 @@ def test_builtin_scratch_matches_caller_scratch_twice():
     handle.close()
 
 
+def test_builtin_scratch_ragged_output():
+    """Ragged output (no padding: flat ids plus row offsets) through the variant, against the ordinary entry
+    point and the CPU checker."""
+    L = _cabi.lib()
+    handle = _cabi.Handle(H.spec("bpe4096"))
+    flat, offs = synth.config5(n_reads=64, seed=9)
+    keep = np.flatnonzero(np.diff(offs) <= 6000)
+    from dnatok_b200.shard import take_rows
+    flat, offs = take_rows(flat, offs, keep)
+    B, total = len(offs) - 1, len(flat)
+    d_bytes, d_off = torch.from_numpy(np.ascontiguousarray(flat)).cuda(), torch.from_numpy(offs).cuda()
+    need = L.dnatok_scratch_bytes(handle.ptr, B, total)
+    assert 0 < need <= _cabi.BUILTIN_SCRATCH_BYTES
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    fmt = _cabi.Format(64, 0, 1, 0, 0, 0)                    # out_stride 0: ragged
+    outs = []
+    for entry in ("caller_scratch", "builtin", "builtin"):
+        ids = torch.full((total + 2 * B,), -7, dtype=torch.int64, device="cuda")
+        out_off = torch.zeros(B + 1, dtype=torch.int64, device="cuda")
+        lengths = torch.zeros(B, dtype=torch.int32, device="cuda")
+        status = torch.zeros(B, dtype=torch.int32, device="cuda")
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        common = (handle.ptr, _ptr(d_bytes), _ptr(d_off), B, total, ctypes.byref(fmt), _ptr(ids), None, _ptr(lengths),
+                  _ptr(out_off), _ptr(status))
+        if entry == "caller_scratch":
+            _cabi.check(L.dnatok_encode(*common, _ptr(scratch), int(scratch.numel()), stream))
+        else:
+            _cabi.check(L.dnatok_encode_bpe_builtin_scratch(*common, stream))
+        torch.cuda.synchronize()
+        assert not status.any()
+        oo = out_off.cpu().numpy()
+        outs.append((ids.cpu().numpy()[:oo[-1]], oo, lengths.cpu().numpy()))
+    for got in outs[1:]:
+        for w, g in zip(outs[0], got):
+            assert np.array_equal(w, g)
+    sp = H.spec("bpe4096").specials
+    want = H.oracle_rows("bpe4096", flat, offs)
+    ids, oo, _ = outs[1]
+    for i in range(B):
+        assert ids[oo[i]:oo[i + 1]].tolist() == [sp.cls_id] + want[i].tolist() + [sp.sep_id]
+    handle.close()
+
+
 def test_builtin_scratch_refuses_oversized_batch_and_cold_handle():
     L = _cabi.lib()
     handle = _cabi.Handle(H.spec("bpe4096"))
