@@ -23,7 +23,7 @@ EXPORTS = (
     "dnatok_max_tokens", "dnatok_prepare", "dnatok_write", "dnatok_encode",
     "dnatok_scan_lengths", "dnatok_encode_host", "dnatok_launch_count", "dnatok_host_copy_bytes",
     "dnatok_encode_bpe_builtin_scratch", "dnatok_set_option", "dnatok_set_row_bytes_hint",
-    "dnatok_pack_fasta", "dnatok_embed",
+    "dnatok_pack_fasta", "dnatok_embed", "dnatok_create_kmer_table", "dnatok_set_start_lut",
 )
 BUILTIN_SCRATCH_BYTES = 8 << 20
 
@@ -64,6 +64,8 @@ def lib() -> ctypes.CDLL:
     L.dnatok_create_char.argtypes = [p, POINTER(Specials), POINTER(p)]
     L.dnatok_create_kmer.argtypes = [c_int, p, p, POINTER(Specials), POINTER(p)]
     L.dnatok_create_bpe.argtypes = [p, p, p, c_int32, p, POINTER(Specials), POINTER(p)]
+    L.dnatok_create_kmer_table.argtypes = [c_int, p, p, c_int32, p, p, c_int, POINTER(Specials), POINTER(p)]
+    L.dnatok_set_start_lut.argtypes = [p, p]
     L.dnatok_destroy.argtypes = [p]
     L.dnatok_destroy.restype = None
     L.dnatok_kind.argtypes = [p]
@@ -108,6 +110,17 @@ class Handle:
         lut = np.ascontiguousarray(spec.lut256, dtype=np.int32)
         if spec.kind == "char":
             check(L.dnatok_create_char(np_ptr(lut), ctypes.byref(sp), ctypes.byref(h)))
+            if getattr(spec, "start_lut256", None) is not None:
+                start = np.ascontiguousarray(spec.start_lut256, dtype=np.int32)
+                check(L.dnatok_set_start_lut(h, np_ptr(start)))
+        elif spec.kind == "kmer" and getattr(spec, "kmer_table5", None) is not None:
+            t5 = np.ascontiguousarray(spec.kmer_table5, dtype=np.int32)
+            if t5.shape[0] != 5 ** spec.k:
+                raise ValueError("kmer_table5 must have 5**k entries")
+            ro = np.ascontiguousarray(spec.kmer_run_offsets, dtype=np.int32)
+            ri = np.ascontiguousarray(spec.kmer_run_ids, dtype=np.int32)
+            check(L.dnatok_create_kmer_table(int(spec.k), np_ptr(t5), np_ptr(ro), int(len(ro) - 1), np_ptr(ri) if len(ri) else None,
+                                             np_ptr(lut), 1 if spec.kmer_tail_singles else 0, ctypes.byref(sp), ctypes.byref(h)))
         elif spec.kind == "kmer":
             km = np.ascontiguousarray(spec.kmer_ids, dtype=np.int32)
             if km.shape[0] != 4 ** spec.k:

@@ -20,6 +20,7 @@
 #include "embed_kernel.cuh"
 #include "emit_kernel.cuh"
 #include "kmer_kernel.cuh"
+#include "kmer_table_kernel.cuh"
 
 using namespace dnatok;
 
@@ -62,7 +63,11 @@ int fail(int code, const char* fmt, ...) {
 
 struct DeviceTables {
     int32_t* lut256 = nullptr;       // char LUT / k-mer single ids
+    int32_t* start_lut = nullptr;    // char: ids of a row's first character, when they differ
     int32_t* kmer_ids = nullptr;
+    int32_t* table5 = nullptr;       // table-driven k-mer handles: 5^k windows, runs
+    int32_t* exp_off = nullptr;
+    int32_t* exp_ids = nullptr;
     uint32_t* disp = nullptr;
     uint64_t* slots = nullptr;
     uint16_t* merge_out = nullptr;
@@ -95,6 +100,10 @@ struct dnatok_handle {
     std::vector<int32_t> lut256;
     int k = 0;
     std::vector<int32_t> kmer_ids;
+    std::vector<int32_t> start_lut;    // char: 256 ids of a row's first character; empty: same as lut256
+    std::vector<int32_t> table5, exp_off, exp_ids;   // table-driven k-mer handles (dnatok_create_kmer_table)
+    bool kmer_table = false;
+    int tail_singles = 1;
     int32_t kmer_affine_base = -1;     // >= 0 when kmer_ids[i] == base + i for every i
     bool lut_identity = false;         // char: id == byte value for every byte (byte-level tokenizers)
     int64_t hint_min_row = 0, hint_max_row = 0;   // caller's bounds on row length in bytes; 0, 0: unknown
@@ -131,7 +140,7 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
             ~Undo() {
                 if (keep) return;
                 DeviceTables& x = h->dev[dev];
-                void* ptrs[] = {x.lut256, x.kmer_ids, x.disp, x.slots, x.merge_out, x.hot, x.byte_tok};
+                void* ptrs[] = {x.lut256, x.start_lut, x.kmer_ids, x.table5, x.exp_off, x.exp_ids, x.disp, x.slots, x.merge_out, x.hot, x.byte_tok};
                 for (void* p : ptrs) if (p) cudaFree(p);
                 h->dev.erase(dev);
             }
@@ -139,7 +148,13 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
         CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
         int rc = upload(&d.lut256, h->lut256);
         if (rc) return rc;
-        if (h->kind == DNATOK_KIND_KMER && (rc = upload(&d.kmer_ids, h->kmer_ids))) return rc;
+        if (h->kind == DNATOK_KIND_KMER && !h->kmer_table && (rc = upload(&d.kmer_ids, h->kmer_ids))) return rc;
+        if (h->kmer_table) {
+            if ((rc = upload(&d.table5, h->table5))) return rc;
+            if ((rc = upload(&d.exp_off, h->exp_off))) return rc;
+            if ((rc = upload(&d.exp_ids, h->exp_ids))) return rc;
+        }
+        if (!h->start_lut.empty() && (rc = upload(&d.start_lut, h->start_lut))) return rc;
         if (h->kind == DNATOK_KIND_BPE) {
             if ((rc = upload(&d.disp, h->bpe.disp))) return rc;
             if ((rc = upload(&d.slots, h->bpe.slots))) return rc;
@@ -397,6 +412,21 @@ int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, 
     return 0;
 }
 
+// The one-token-per-character path: the emit kernel, then the start ids where the handle has them.
+int launch_char(const dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets, int64_t n_rows,
+                int64_t total_bytes, const RowFormat& rf, int id_bits, void* ids, void* mask, int32_t* lengths,
+                const int64_t* out_offsets, int32_t* status, cudaStream_t st) {
+    int rc = h->lut_identity
+        ? launch_emit<uint8_t, false>(d, bytes, offsets, nullptr, n_rows, total_bytes, rf, id_bits, ids, mask, lengths, out_offsets, status, st)
+        : launch_emit<uint8_t, true>(d, bytes, offsets, nullptr, n_rows, total_bytes, rf, id_bits, ids, mask, lengths, out_offsets, status, st);
+    if (rc || h->start_lut.empty() || n_rows == 0) return rc;
+    const unsigned grid = (unsigned)((n_rows + 255) / 256);
+    if (id_bits == 64) start_fix_kernel<int64_t><<<grid, 256, 0, st>>>(bytes, offsets, n_rows, d.start_lut, rf, (int64_t*)ids, out_offsets);
+    else start_fix_kernel<int32_t><<<grid, 256, 0, st>>>(bytes, offsets, n_rows, d.start_lut, rf, (int32_t*)ids, out_offsets);
+    LAUNCH_CHECK("start_fix_kernel");
+    return 0;
+}
+
 template <typename IdT, int K>
 void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_t* bytes, const int64_t* offsets,
                         int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
@@ -510,6 +540,18 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
                 int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t st) {
     if (n_rows == 0) return 0;
     const int k = h->k;
+    if (h->kmer_table) {
+        const KmerTable t{d.table5, d.exp_off, d.exp_ids, d.lut256, k, h->tail_singles};
+        const unsigned grid = (unsigned)((n_rows + KT_WARPS - 1) / KT_WARPS);
+        if (id_bits == 64)
+            kmer_table_kernel<int64_t, COUNT_ONLY><<<grid, KT_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, t, rf, (int64_t*)ids, mask,
+                                                                                  lengths_in, lengths_out, out_offsets, status);
+        else
+            kmer_table_kernel<int32_t, COUNT_ONLY><<<grid, KT_WARPS * 32, 0, st>>>(bytes, offsets, n_rows, t, rf, (int32_t*)ids, mask,
+                                                                                  lengths_in, lengths_out, out_offsets, status);
+        LAUNCH_CHECK("kmer_table_kernel");
+        return 0;
+    }
     // The segment encoder spends about half as many instructions again per row (look-back, a second
     // pass over segments that hold an N), and its fixed deal of segments to warps cannot follow SMs
     // that run at different speeds the way block scheduling does: it is the choice where one warp
@@ -717,6 +759,46 @@ int dnatok_create_kmer(int k, const int32_t* kmer_ids, const int32_t single_ids[
     return DNATOK_OK;
 }
 
+int dnatok_create_kmer_table(int k, const int32_t* table5, const int32_t* run_offsets, int32_t n_runs, const int32_t* run_ids,
+                             const int32_t single_ids[256], int tail_singles, const dnatok_specials* sp,
+                             dnatok_handle** out) {
+    if (!table5 || !single_ids || !out || n_runs < 0 || (n_runs && (!run_offsets || !run_ids)))
+        return fail(DNATOK_ERR_INVALID, "NULL argument");
+    if (k < 1 || k > KMER_MAX_K) return fail(DNATOK_ERR_UNSUPPORTED, "k must be in 1..%d", KMER_MAX_K);
+    if (int rc = check_specials(sp)) return rc;
+    size_t n5 = 1;
+    for (int i = 0; i < k; ++i) n5 *= 5;
+    for (size_t i = 0; i < n5; ++i)
+        if (table5[i] < 0 && -(int64_t)table5[i] - 1 >= n_runs) return fail(DNATOK_ERR_INVALID, "window %zu names run %lld of %d", i, -(long long)table5[i] - 1, n_runs);
+    for (int32_t e = 0; e < n_runs; ++e)
+        if (run_offsets[e + 1] < run_offsets[e]) return fail(DNATOK_ERR_INVALID, "run offsets must not decrease");
+    auto* h = new (std::nothrow) dnatok_handle();
+    if (!h) return fail(DNATOK_ERR_INVALID, "out of memory");
+    h->kind = DNATOK_KIND_KMER; h->sp = *sp; h->k = k;
+    h->kmer_table = true;
+    h->tail_singles = tail_singles ? 1 : 0;
+    h->lut256.assign(single_ids, single_ids + 256);
+    h->table5.assign(table5, table5 + n5);
+    if (n_runs) {
+        h->exp_off.assign(run_offsets, run_offsets + n_runs + 1);
+        h->exp_ids.assign(run_ids, run_ids + run_offsets[n_runs]);
+    }
+    if (h->exp_off.empty()) h->exp_off.assign(1, 0);
+    if (h->exp_ids.empty()) h->exp_ids.assign(1, 0);
+    *out = h;
+    return DNATOK_OK;
+}
+
+int dnatok_set_start_lut(dnatok_handle* h, const int32_t start_lut[256]) {
+    if (!h || !start_lut) return fail(DNATOK_ERR_INVALID, "NULL argument");
+    if (h->kind != DNATOK_KIND_CHAR) return fail(DNATOK_ERR_INVALID, "only one-token-per-character handles take a start table");
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (!h->dev.empty()) return fail(DNATOK_ERR_INVALID, "the start table must be set before the handle is first used");
+    h->start_lut.assign(start_lut, start_lut + 256);
+    h->lut_identity = false;
+    return DNATOK_OK;
+}
+
 int dnatok_create_bpe(const int32_t* a, const int32_t* b, const int32_t* o, int32_t n,
                       const int32_t byte_ids[256], const dnatok_specials* sp, dnatok_handle** out) {
     if (!a || !b || !o || !byte_ids || !out) return fail(DNATOK_ERR_INVALID, "NULL argument");
@@ -742,7 +824,7 @@ void dnatok_destroy(dnatok_handle* h) {
         DeviceTables& d = kv.second;
         if (cudaSetDevice(kv.first) != cudaSuccess) continue;
         if (d.stream) cudaStreamSynchronize(d.stream);
-        void* ptrs[] = {d.lut256, d.kmer_ids, d.disp, d.slots, d.merge_out, d.hot, d.byte_tok, d.st_bytes, d.st_offsets,
+        void* ptrs[] = {d.lut256, d.start_lut, d.table5, d.exp_off, d.exp_ids, d.kmer_ids, d.disp, d.slots, d.merge_out, d.hot, d.byte_tok, d.st_bytes, d.st_offsets,
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);
@@ -768,7 +850,7 @@ int dnatok_set_row_bytes_hint(dnatok_handle* h, int64_t min_bytes, int64_t max_b
 
 size_t dnatok_scratch_bytes(const dnatok_handle* h, int64_t n_rows, int64_t total_bytes) {
     if (!h || n_rows < 0 || total_bytes < 0) return 0;
-    if (h->kind == DNATOK_KIND_KMER) return kmer_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
+    if (h->kind == DNATOK_KIND_KMER) return h->kmer_table ? 0 : kmer_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
     if (h->kind != DNATOK_KIND_BPE) return 0;
     return bpe_scratch_layout(h, nullptr, n_rows, total_bytes).bytes;
 }
@@ -828,11 +910,8 @@ int dnatok_write(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
     if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
     switch (h->kind) {
         case DNATOK_KIND_CHAR:
-            if (h->lut_identity)
-                return launch_emit<uint8_t, false>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits,
-                                                   d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
-            return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits,
-                                              d_ids, d_mask, nullptr, d_out_offsets, d_status, st);
+            return launch_char(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr,
+                               d_out_offsets, d_status, st);
         case DNATOK_KIND_KMER:
             if (fmt->out_stride > 0 && fmt->pad_left && !d_lengths)
                 return fail(DNATOK_ERR_INVALID, "left padding needs d_lengths from dnatok_prepare");
@@ -880,13 +959,9 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
     if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
     if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
-    if (h->kind == DNATOK_KIND_CHAR) {
-        if (h->lut_identity)
-            return launch_emit<uint8_t, false>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits, d_ids,
-                                               d_mask, d_lengths, nullptr, d_status, st);
-        return launch_emit<uint8_t, true>(*d, d_bytes, d_offsets, nullptr, n_rows, total_bytes, rf, fmt->id_bits, d_ids,
-                                          d_mask, d_lengths, nullptr, d_status, st);
-    }
+    if (h->kind == DNATOK_KIND_CHAR)
+        return launch_char(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, d_lengths, nullptr,
+                           d_status, st);
     return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
                               nullptr, d_status, d_scratch, scratch_bytes, st);
 }
@@ -899,6 +974,7 @@ int dnatok_embed(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
     if (int rc = check_batch(h, d_bytes, d_offsets, n_rows, total_bytes)) return rc;
     if (int rc = check_format(fmt, false)) return rc;
     if (h->kind != DNATOK_KIND_CHAR) return fail(DNATOK_ERR_UNSUPPORTED, "dnatok_embed needs a one-token-per-byte handle");
+    if (!h->start_lut.empty()) return fail(DNATOK_ERR_UNSUPPORTED, "dnatok_embed does not take handles with a start table");
     if (fmt->out_stride <= 0) return fail(DNATOK_ERR_INVALID, "dnatok_embed needs a padded layout (out_stride > 0)");
     if (!d_weight || !d_out) return fail(DNATOK_ERR_INVALID, "NULL weight or output");
     if (row_bytes <= 0 || row_bytes % 16 || vocab_rows <= 0) return fail(DNATOK_ERR_INVALID, "row_bytes must be a positive multiple of 16");

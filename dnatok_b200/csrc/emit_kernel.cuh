@@ -261,6 +261,27 @@ emit_ragged_kernel(const SrcT* __restrict__ src, const int64_t* __restrict__ off
     }
 }
 
+// Tokenizers whose id of a row's first character differs from the id the same character gets later
+// (the reference keeps a second "start" table for them and patches column 0,
+// src/dna_tokenizer.py:1779-1820 with :527-631): after the rows are written, one thread per row puts
+// the start id under the row's first content column.
+template <typename IdT>
+__global__ void start_fix_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
+                                 const int32_t* __restrict__ start_lut, RowFormat f, IdT* __restrict__ ids,
+                                 const int64_t* __restrict__ out_offsets) {
+    const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= n_rows) return;
+    const int64_t off = offsets[row], n_in = offsets[row + 1] - off;
+    const int64_t n = n_in < f.cap_content ? n_in : f.cap_content;
+    if (n <= 0) return;
+    const int has_cls = f.cls_id >= 0 ? 1 : 0, has_sep = f.sep_id >= 0 ? 1 : 0;
+    const IdT v = (IdT)__ldg(start_lut + __ldg(bytes + off));
+    if (f.out_stride == 0) { ids[out_offsets[row] + has_cls] = v; return; }
+    const int64_t T = n + has_cls + has_sep;
+    const int64_t shift = f.pad_left ? f.out_stride - T : 0;
+    ids[row * f.out_stride + shift + has_cls] = v;
+}
+
 // Row lengths of the one-token-per-element paths (no data is read): min(n, cap) + specials.
 __global__ void span_lengths_kernel(const int64_t* __restrict__ offsets, const int32_t* __restrict__ counts,
                                     int64_t n_rows, RowFormat f, int32_t* __restrict__ lengths,

@@ -9,8 +9,11 @@ which reads ``tokenizer.json`` (``:132-176``), checks the model / pre-tokenizer 
 
 Differences by design: BPE tables are built directly in HF id space (the reference keeps a
 kernel-id -> HF-id remap, ``:447-466``), and a k-mer vocabulary is stored as a ``4**k`` table of
-clean windows plus a single-character table, which is only accepted when probing shows that the
-tokenizer really expands every other window character by character.
+clean windows plus a single-character table when probing shows that the tokenizer expands every
+other window character by character (the form the fast kernels read); any other k-mer tokenizer is
+kept as the reference keeps it, as the table of all ``5**k`` windows over ACGTN with runs of ids for
+windows that are not one token.  A per-character tokenizer may give a character one id at the start
+of a sequence and another later on (start / continuation tables).
 
 Nothing here computes token ids for user input; tables only.
 """
@@ -46,6 +49,12 @@ class TokenizerSpec:
     lut256: np.ndarray                          # int32[256]: byte -> id (char), single ids (kmer), initial symbols (bpe)
     k: int = 0
     kmer_ids: Optional[np.ndarray] = None       # int32[4**k], itertools.product("ACGT", k) order
+    # k-mer tokenizers given window by window (any tokenizer the 4**k + singles form cannot express):
+    kmer_table5: Optional[np.ndarray] = None    # int32[5**k] over ACGTN: id, or -(e + 1) for run e
+    kmer_run_offsets: Optional[np.ndarray] = None   # int32[n_runs + 1]
+    kmer_run_ids: Optional[np.ndarray] = None
+    kmer_tail_singles: bool = True              # the len % k tail gives one id per character (False: nothing)
+    start_lut256: Optional[np.ndarray] = None   # char: ids of a row's first character when they differ from lut256
     merge_a: Optional[np.ndarray] = None        # int32[n_merges] left operand id, rank order
     merge_b: Optional[np.ndarray] = None
     merge_out: Optional[np.ndarray] = None
@@ -305,21 +314,32 @@ def spec_from_probing(tok: Any) -> TokenizerSpec:
     got = _ids(tok, [chr(c) for c in chars])
     for c, r in zip(chars, got):
         if len(r) != 1:
-            if chr(c) in "ACGTNacgtn":
-                raise UnsupportedTokenizer("character %r gives %d tokens" % (chr(c), len(r)))
-            continue
+            continue          # no single id (k-mer tokenizers that drop short input): the probes below decide
         singles[c] = r[0]
     # bytes >= 128 and whitespace are outside the supported input domain; they read as unk.
 
-    k = detect_kmer(tok)
+    try:
+        k = detect_kmer(tok)
+    except Exception:
+        k = 0
     if k == 0:
-        # one token per character, and the id must not depend on position (the reference
-        # keeps a second "continuation" LUT for tokenizers where it does; not supported here).
+        # One token per character.  Where a character's id at the start of a sequence differs from its id
+        # later on (word-piece style vocabularies), the later id is read off the second token of the doubled
+        # character, as the reference does (_resolve_cont_ids, src/dna_tokenizer.py:527-558), and the single-
+        # character ids become the table of column 0.
+        cont = singles.copy()
+        doubled = _ids(tok, [chr(c) * 2 for c in chars])
+        for c, r in zip(chars, doubled):
+            if len(r) == 2 and r[0] == singles[c]:
+                cont[c] = r[1]
+        start = singles if np.any(cont != singles) else None
         probes = ["ACGTACGT", "NNACGTNN", "acgtnACG", "TTTTTTTT", "AN", "NA", "Xx"]
         for p, r in zip(probes, _ids(tok, probes)):
-            if r != [int(singles[ord(ch)]) for ch in p]:
-                raise UnsupportedTokenizer("not a position-independent per-character tokenizer (probe %r)" % p)
-        return TokenizerSpec("char", sp, vs, singles, vocab=vocab)
+            want = [int(singles[ord(p[0])])] + [int(cont[ord(ch)]) for ch in p[1:]]
+            if r != want:
+                raise UnsupportedTokenizer("not a per-character tokenizer with at most a start / continuation split "
+                                           "(probe %r)" % p)
+        return TokenizerSpec("char", sp, vs, cont, vocab=vocab, start_lut256=start)
 
     clean = ["".join(t) for t in itertools.product("ACGT", repeat=k)]
     kmer_ids = np.empty(4 ** k, np.int32)
@@ -335,13 +355,75 @@ def spec_from_probing(tok: Any) -> TokenizerSpec:
     tail = "ACGTAC"[:k - 1] if k > 1 else ""
     probes = [d + clean[(7 * i) % len(clean)] + tail for i, d in enumerate(dirty)]
     probes += [clean[5] + "acgtn"[:k - 1], "a" + clean[9][1:] + clean[3], clean[1][:k - 1], "N" * (2 * k + 1)]
+    fast_form = True
     for lo in range(0, len(probes), 4096):
         chunk = probes[lo:lo + 4096]
         for p, r in zip(chunk, _ids(tok, chunk)):
             if r != expected_kmer_ids(p, k, kmer_ids, singles):
-                raise UnsupportedTokenizer("k-mer tokenizer is not window-aligned with single-character "
-                                           "fallback (probe %r)" % p)
-    return TokenizerSpec("kmer", sp, vs, singles, k=k, kmer_ids=kmer_ids, vocab=vocab)
+                fast_form = False
+                break
+        if not fast_form:
+            break
+    if fast_form:
+        return TokenizerSpec("kmer", sp, vs, singles, k=k, kmer_ids=kmer_ids, vocab=vocab)
+    return _kmer_table_spec(tok, k, sp, vs, singles, vocab)
+
+
+def _kmer_table_spec(tok: Any, k: int, sp: Specials, vs: int, singles: np.ndarray, vocab: dict) -> TokenizerSpec:
+    """The complete window table: every one of the 5**k strings over ACGTN is tokenised once and kept as an id
+    or a run of ids (the reference's _build_kmer_lut, src/dna_tokenizer.py:743-822), the tail rule is read off
+    two probes, and the table is accepted only if replaying it reproduces the tokenizer on random ACGTN strings
+    (the reference's _sanity_compare_kmer_expansion, :1220-1273)."""
+    windows = ["".join(t) for t in itertools.product("ACGTN", repeat=k)]
+    table5 = np.empty(5 ** k, np.int32)
+    offsets, flat = [0], []
+    for lo in range(0, len(windows), 4096):
+        for j, r in enumerate(_ids(tok, windows[lo:lo + 4096])):
+            if len(r) == 1:
+                table5[lo + j] = r[0]
+            else:
+                table5[lo + j] = -len(offsets)
+                flat.extend(r)
+                offsets.append(len(flat))
+    one = windows[7 % len(windows)]
+    whole = _ids(tok, [one])[0]
+    with_tail = _ids(tok, [one + "C"])[0] if k > 1 else whole
+    if k == 1 or with_tail == whole + [int(singles[ord("C")])]:
+        tail_singles = True
+    elif with_tail == whole:
+        tail_singles = False
+    else:
+        raise UnsupportedTokenizer("the len %% k tail is neither dropped nor tokenised per character")
+    spec = TokenizerSpec("kmer", sp, vs, singles, k=k, vocab=vocab, kmer_table5=table5,
+                         kmer_run_offsets=np.asarray(offsets, np.int32), kmer_run_ids=np.asarray(flat, np.int32),
+                         kmer_tail_singles=tail_singles)
+    rng = np.random.default_rng(k)
+    probes = ["".join(rng.choice(list("ACGTN"), size=int(n), p=[0.22, 0.22, 0.22, 0.22, 0.12]))
+              for n in list(rng.integers(k, 6 * k + 1, size=48)) + [4 * k] * 16]
+    for p, r in zip(probes, _ids(tok, probes)):
+        if r != expected_kmer_table_ids(p, spec):
+            raise UnsupportedTokenizer("replaying the k-mer window table does not reproduce the tokenizer (probe %r)" % p)
+    return spec
+
+
+def expected_kmer_table_ids(s: str, spec: TokenizerSpec) -> List[int]:
+    """Window-table semantics spelled out (validates a probed table; also the checker of its tests)."""
+    k, digit = spec.k, {"A": 0, "C": 1, "G": 2, "T": 3}
+    out: List[int] = []
+    n_full = len(s) // k
+    for w in range(n_full):
+        idx = 0
+        for ch in s[w * k:(w + 1) * k]:
+            idx = idx * 5 + digit.get(ch, 4)
+        e = int(spec.kmer_table5[idx])
+        if e >= 0:
+            out.append(e)
+        else:
+            lo, hi = spec.kmer_run_offsets[-e - 1], spec.kmer_run_offsets[-e]
+            out.extend(int(v) for v in spec.kmer_run_ids[lo:hi])
+    if spec.kmer_tail_singles:
+        out.extend(int(spec.lut256[ord(ch)]) for ch in s[n_full * k:])
+    return out
 
 
 def expected_kmer_ids(s: str, k: int, kmer_ids: np.ndarray, singles: np.ndarray) -> List[int]:

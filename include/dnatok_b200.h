@@ -11,6 +11,8 @@
  *   dnatok_create_char    the ASCII LUT built by DNATok.discover, src/dna_tokenizer.py:995-1030
  *                         (_build_ascii_lut_probe_all :633-653)
  *   dnatok_create_kmer    _build_kmer_lut, src/dna_tokenizer.py:743-822 (+ tail LUT :957-971)
+ *   dnatok_create_kmer_table  the same with every window's token run tabulated (:759-806, :1896-1953)
+ *   dnatok_set_start_lut  the start / continuation tables, src/dna_tokenizer.py:527-631
  *   dnatok_create_bpe     DNATokBPE(merges_path, byte_to_id_lut, max_iters) constructor,
  *                         src/dnatok_bpe_kernel/dnatok_bpe.cu:797-862 (build_vocab_from_merges :761-791)
  *   dnatok_encode         char: _encode_batch_ascii_lut_numpy :1779-1820 / _map_ascii_bytes_to_ids_cuda
@@ -86,6 +88,22 @@ const char* dnatok_last_error(void);
 int dnatok_create_char(const int32_t lut[256], const dnatok_specials* sp, dnatok_handle** out);
 int dnatok_create_kmer(int k, const int32_t* kmer_ids /* 4^k, product("ACGT") order */,
                        const int32_t single_ids[256], const dnatok_specials* sp, dnatok_handle** out);
+/* A k-mer tokenizer given as the table of all 5^k windows over A, C, G, T, N (index = base-5 number of the
+ * window, A C G T N = 0 1 2 3 4, first character most significant): table5[i] >= 0 is the window's id,
+ * table5[i] = -(e + 1) names run e, ids run_ids[run_offsets[e] .. run_offsets[e + 1]).  Any other character counts
+ * as N.  tail_singles != 0: the len % k characters left over give single_ids[c] each; 0: they give nothing.
+ * Stands in for the reference's complete k-mer table with multi-token expansion: _build_kmer_lut,
+ * src/dna_tokenizer.py:743-822 (kmer_lut / kmer_lut_offsets / kmer_lut_lengths / kmer_lut_flat), replayed by
+ * _encode_kmer_fallback_from_lut :1896-1953 and _expand_kmer_packed_cuda :2736-2824.  dnatok_create_kmer remains the
+ * fast form for tokenizers whose non-ACGT windows expand character by character. */
+int dnatok_create_kmer_table(int k, const int32_t* table5, const int32_t* run_offsets, int32_t n_runs, const int32_t* run_ids,
+                             const int32_t single_ids[256], int tail_singles, const dnatok_specials* sp,
+                             dnatok_handle** out);
+/* Ids of a row's FIRST character for one-token-per-character handles whose tokenizer gives a character another id at
+ * the start of a sequence than later on.  Call before the handle is first used.  Stands in for the reference's start /
+ * continuation tables: _resolve_cont_ids / _rebuild_ascii_luts_from_tokenizer, src/dna_tokenizer.py:527-631, applied to
+ * column 0 at :1779-1820 and :2716-2721. */
+int dnatok_set_start_lut(dnatok_handle* h, const int32_t start_lut[256]);
 int dnatok_create_bpe(const int32_t* merge_a, const int32_t* merge_b, const int32_t* merge_out,
                       int32_t n_merges, const int32_t byte_ids[256], const dnatok_specials* sp,
                       dnatok_handle** out);
