@@ -369,9 +369,8 @@ def run_ours(args):
         # the ranks of one host share its cores: the threads that write attention masks are divided among them
         from dnatok_b200 import _cabi
         local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
-        per_rank = min(16, len(all_cores) // max(local_world, 1))
-        if per_rank < 8:
-            per_rank = 0                 # too few cores per rank to beat the copy (measured: 2 per rank at N=8 lose 10 %)
+        # (the stores bypass the cache, so a few threads per rank keep up with the copy; the mask never crosses the link)
+        per_rank = min(16, max(2, len(all_cores) // max(local_world, 1)))
         if os.environ.get("DNATOK_HOST_MASK_THREADS") is not None:
             per_rank = int(os.environ["DNATOK_HOST_MASK_THREADS"])
         _cabi.check(_cabi.lib().dnatok_set_option(b"host_mask_threads", per_rank))
@@ -459,11 +458,69 @@ def run_ours(args):
             ok = bool(torch.equal(got[:ids.shape[0]], ids))
             line["gather"] = {"ms": round(float(gt[0]), 3), "bytes_to_rank0": int(ids.numel() * ids.element_size() * (world - 1)),
                               "rank0_rows_ok": ok, "backend": "nccl"}
+    if world > 1 and not args.no_extra:
+        strong = strong_scaling(local, rank, world, peak)
+        if rank == 0:
+            line["strong_scaling"] = strong
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+def strong_scaling(local, rank, world, peak):
+    """Fixed total work split over the ranks (the other lines are weak scaling): the byte-level shape x16
+    (128 rows of 1 Mbp, contiguous blocks) and the read set x2 (32,768 reads, longest-first bins).  Every rank
+    builds the same seeded batch, takes its rows with shard.partition / take_rows and encodes them; the time is
+    the max over ranks.  Outside the timed region rank 0 encodes the whole batch alone and compares every row's
+    token count and id sum with what the ranks report, put back in order."""
+    import torch
+    import torch.distributed as dist
+    from dnatok_b200 import shard
+    from dnatok_b200.tokenizer import B200Tokenizer
+    out = {}
+    for kind, scale, mode in (("byte", 16, "contiguous"), ("bpe32k", 2, "greedy")):
+        tok = B200Tokenizer(spec_for(kind), device=local)
+        flat, offsets, call, desc = make_workload(kind, scale)
+        parts = shard.partition(np.diff(offsets), world, mode=mode)
+        f, o = shard.take_rows(flat, offsets, parts[rank])
+        d_bytes, d_off = torch.from_numpy(np.ascontiguousarray(f)).cuda(), torch.from_numpy(o).cuda()
+        barrier = lambda: (dist.barrier(), torch.cuda.synchronize())
+        steps = 10
+        enc, per, total_ms, launches = time_device(tok, d_bytes, d_off, o, call, steps, 3, barrier)
+        t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0]) / steps
+
+        def row_sums(e, n_rows):
+            ids = e["input_ids"]
+            if "offsets" in e:
+                oo = e["offsets"]
+                csum = torch.cat([torch.zeros(1, dtype=torch.int64, device=ids.device), torch.cumsum(ids, 0)])
+                return (oo[1:] - oo[:-1]).cpu().numpy(), (csum[oo[1:]] - csum[oo[:-1]]).cpu().numpy()
+            return e["lengths"].cpu().numpy().astype(np.int64), ids.sum(dim=1).cpu().numpy()
+        mine = row_sums(enc, len(o) - 1)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, (parts[rank], mine[0], mine[1]))
+        ok = None
+        if rank == 0:
+            full = tok.encode_device(torch.from_numpy(flat).cuda(), torch.from_numpy(offsets).cuda(), host_offsets=offsets,
+                                     **device_kwargs(call))
+            want = row_sums(full, len(offsets) - 1)
+            counts = np.zeros(len(offsets) - 1, np.int64)
+            sums = np.zeros(len(offsets) - 1, np.int64)
+            for rows, c, sm in everyone:
+                counts[rows], sums[rows] = c, sm
+            ok = bool(np.array_equal(counts, want[0]) and np.array_equal(sums, want[1]))
+            del full
+        out["%s/x%d" % (kind, scale)] = {"workload": desc, "partition": mode, "ms_per_step": round(ms, 5),
+                                       "Mbp/s": round(int(offsets[-1]) / ms / 1e3, 1), "rows_per_rank": [int(len(p)) for p in parts],
+                                       "bp_per_rank_max": int(max(np.diff(offsets)[p].sum() for p in parts)),
+                                       "rows_equal_single_gpu": ok, "scaling": "strong"}
+        del d_bytes, d_off, enc
+        torch.cuda.empty_cache()
+    return out
 
 
 # dram bytes per launch of the dominant kernel from the committed ncu summaries (profiles/), scaled to

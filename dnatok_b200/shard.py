@@ -49,6 +49,76 @@ def partition(lengths: np.ndarray, world: int, mode: str = "contiguous") -> List
     raise ValueError("mode must be 'contiguous' or 'greedy'")
 
 
+def safe_cut_bytes(spec) -> np.ndarray:
+    """bool[256]: bytes next to which a row may be cut without changing its tokens.
+
+    Per-character tokenizers: every byte.  BPE: bytes whose initial symbol takes part in no merge (the
+    unknown id that N or lower case map to in an upper-case ACGT vocabulary, for instance): no merge ever
+    crosses such a symbol, so the pieces on either side tokenise exactly as they do inside the whole row.
+    k-mer tokenizers are cut by position (multiples of k), see ``split_long_rows``."""
+    if spec.kind in ("char", "kmer"):
+        return np.ones(256, dtype=bool)
+    operands = set(np.asarray(spec.merge_a).tolist()) | set(np.asarray(spec.merge_b).tolist())
+    return np.array([int(t) not in operands for t in np.asarray(spec.lut256)], dtype=bool)
+
+
+def split_long_rows(flat: np.ndarray, offsets: np.ndarray, spec, max_bytes: int):
+    """Cut rows longer than ``max_bytes`` into pieces that tokenise independently, for spreading one long
+    record (a chromosome) over several GPUs.  Returns ``(piece_offsets int64[P + 1], piece_row int64[P])``:
+    the pieces tile the same ``flat`` buffer in order and ``piece_row[p]`` is the row a piece came from.
+
+    Cuts are exact: per-character tokenizers are cut anywhere, k-mer tokenizers at multiples of k from the
+    row start, BPE tokenizers directly before or after a byte whose symbol never merges (``safe_cut_bytes``).
+    A BPE row without such a byte near the wanted cut stays longer than ``max_bytes`` (up to whole): there is
+    no exact cut inside a run of mergeable symbols.  Encode the pieces as rows WITHOUT special tokens and
+    pass the ragged result to ``join_pieces``."""
+    offsets = np.asarray(offsets, dtype=np.int64)
+    if max_bytes < 1:
+        raise ValueError("max_bytes must be positive")
+    safe = safe_cut_bytes(spec)
+    k = int(spec.k) if spec.kind == "kmer" else 1
+    step = max(k, (int(max_bytes) // k) * k)
+    cuts, owner = [0], []
+    for r in range(len(offsets) - 1):
+        lo, hi = int(offsets[r]), int(offsets[r + 1])
+        at = lo
+        while hi - at > max_bytes:
+            want = at + step
+            if spec.kind == "bpe":
+                # the last safe position in (at, want]: a cut at position c is safe when byte c-1 or byte c never merges
+                seg = flat[at:want + 1]
+                ok = safe[seg]
+                pos = np.flatnonzero(ok[:-1] | ok[1:]) + 1          # cut before seg[i+1] for every i with ok[i] or ok[i+1]
+                pos = pos[pos <= want - at]
+                if pos.size == 0:
+                    # none inside the window: the first safe position after it, if the row has one
+                    rest = safe[flat[want:hi]]
+                    nxt = np.flatnonzero(rest)
+                    if nxt.size == 0:
+                        break
+                    want = want + int(nxt[0]) + 1
+                    if want >= hi:
+                        break
+                else:
+                    want = at + int(pos[-1])
+            cuts.append(want)
+            owner.append(r)
+            at = want
+        cuts.append(hi)
+        owner.append(r)
+    piece_offsets = np.asarray(cuts, dtype=np.int64)
+    # empty rows keep their (empty) piece; duplicates from a cut landing on a row end cannot occur (want < hi)
+    return piece_offsets, np.asarray(owner, dtype=np.int64)
+
+
+def join_pieces(piece_out_offsets: np.ndarray, piece_row: np.ndarray, n_rows: int) -> np.ndarray:
+    """Row offsets into the ragged ids of the pieces: the pieces of a row are consecutive, so a row's tokens
+    are the concatenation of its pieces' tokens and only the offsets need regrouping."""
+    piece_out_offsets = np.asarray(piece_out_offsets, dtype=np.int64)
+    first = np.searchsorted(piece_row, np.arange(n_rows), side="left")
+    return np.concatenate([piece_out_offsets[first], piece_out_offsets[-1:]])
+
+
 def take_rows(flat: np.ndarray, offsets: np.ndarray, rows: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     """The sub-batch (flat bytes, offsets) made of ``rows``."""
     lens = (offsets[1:] - offsets[:-1])[rows]

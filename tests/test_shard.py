@@ -88,6 +88,83 @@ def test_two_rank_shard_and_gather_gloo():
     assert q.get(timeout=5) is True
 
 
+def test_split_long_rows_is_exact_for_every_kind():
+    """Pieces cut by split_long_rows tokenise to the same ids as the whole rows (CPU checker)."""
+    from oracle import oracle
+    rng = np.random.default_rng(5)
+    for name in ("char", "kmer6", "bpe4096"):
+        spec = H.spec(name)
+        rows = [synth.config2(batch=1, length=n, seed=n)[0] for n in (50, 7001, 3, 20000)]     # ACGT with N runs
+        flat = np.concatenate(rows)
+        offs = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int64)
+        whole = H.oracle_rows(name, flat, offs)
+        for max_bytes in (999, 4096, 100000):
+            po, prow = shard.split_long_rows(flat, offs, spec, max_bytes)
+            assert po[0] == 0 and po[-1] == offs[-1] and np.all(np.diff(po) >= 0) and len(prow) == len(po) - 1
+            assert set(offs.tolist()) <= set(po.tolist())
+            if name != "bpe4096":
+                assert np.diff(po).max() <= max(max_bytes, 6)
+            pieces = H.oracle_rows(name, flat, po)
+            out_off = np.concatenate([[0], np.cumsum([len(p) for p in pieces])])
+            ids = np.concatenate(pieces) if pieces else np.zeros(0, np.int64)
+            ro = shard.join_pieces(out_off, prow, len(rows))
+            for r in range(len(rows)):
+                assert ids[ro[r]:ro[r + 1]].tolist() == whole[r].tolist(), (name, max_bytes, r)
+    # a BPE row with nothing but mergeable symbols has no exact cut and stays whole
+    spec = H.spec("bpe4096")
+    flat = synth.config3(batch=1, length=5000, seed=1)[0]
+    po, prow = shard.split_long_rows(flat, np.array([0, 5000]), spec, 1000)
+    assert po.tolist() == [0, 5000] and prow.tolist() == [0]
+
+
+def _split_rank_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # one word of 1,048,576 bp (the byte-level shape's row: 0.1 % N, which the BPE vocabulary does not know)
+        # is cut at those N, the pieces are dealt to the ranks, every rank tokenises its pieces (the CPU checker
+        # standing in for its GPU) and rank 0 puts the ids together
+        name = "bpe4096"
+        spec = H.spec(name)
+        flat = np.ascontiguousarray(np.char.upper(synth.config4(batch=1, length=1 << 20, seed=3).view("S1")).view(np.uint8)[0])
+        offs = np.array([0, flat.size], dtype=np.int64)
+        po, prow = shard.split_long_rows(flat, offs, spec, flat.size // (4 * world))
+        parts = shard.partition(np.diff(po), world)
+        mine = parts[rank]
+        f, o = shard.take_rows(flat, po, mine)
+        rows = H.oracle_rows(name, f, o)
+        ids = np.concatenate(rows).astype(np.int64) if rows else np.zeros(0, np.int64)
+        counts = [None] * world
+        dist.all_gather_object(counts, int(ids.size))
+        buf = torch.zeros(max(counts), dtype=torch.int64)
+        buf[:ids.size] = torch.from_numpy(ids)
+        bucket = [torch.zeros(max(counts), dtype=torch.int64) for _ in range(world)] if rank == 0 else None
+        dist.gather(buf, bucket, dst=0)
+        if rank == 0:
+            got = np.concatenate([bucket[r][:counts[r]].numpy() for r in range(world)])
+            want = H.oracle_rows(name, flat, offs)[0]
+            q.put((bool(np.array_equal(got, want)), len(po) - 1, int(np.diff(po).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_one_megabase_word_split_over_two_ranks_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_split_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    ok, n_pieces, longest = q.get(timeout=5)
+    assert ok and n_pieces >= 8 and longest < (1 << 20) // 4
+
+
 def test_bind_host_to_gpu_is_harmless_without_nvml():
     """On a machine without a GPU driver the binding helper reports None and leaves the affinity alone."""
     import os
