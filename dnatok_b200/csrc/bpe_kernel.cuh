@@ -165,13 +165,28 @@ __device__ __forceinline__ uint32_t chain_parity(uint32_t c, int top, uint32_t f
     return odd;
 }
 
+// Where the merge kernels leave a row's final token count (the count after truncation plus the special
+// tokens), so that no separate pass over the rows is needed: lengths may be NULL.
+struct BpeLengths {
+    int32_t* lengths;
+    int64_t cap_content;     // most content tokens a row may keep
+    int32_t n_special;
+    int32_t clip_is_error;   // rows cut by the output width (not by requested truncation) get DNATOK_ROW_CLIPPED
+};
+__device__ __forceinline__ void bpe_put_length(const BpeLengths& L, int32_t* status, int64_t row, int64_t n) {
+    if (!L.lengths) return;
+    const int64_t kept = n < L.cap_content ? n : L.cap_content;
+    L.lengths[row] = (int32_t)kept + L.n_special;
+    if (status && L.clip_is_error && n > kept) atomicOr(status + row, 4);
+}
+
 // Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].  One atomic per
 // warp and class (rows of a batch mostly share a class).  Classes outside class_mask are not
 // launched by the host; a row that belongs to one is flagged instead of being dropped silently.
 __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t n_rows,
                                     int32_t* __restrict__ class_count, int32_t* __restrict__ class_list,
                                     int32_t* __restrict__ counts, int32_t* __restrict__ status,
-                                    uint32_t class_mask) {
+                                    uint32_t class_mask, BpeLengths len_out) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int lane = threadIdx.x & 31;
     int c = -1;
@@ -184,6 +199,7 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
             if (n > BPE_MAX_POSITIONS) { if (status) atomicOr(status + i, 1); c = -1; }
             else if (!((class_mask >> c) & 1u)) { if (status) atomicOr(status + i, 8); c = -1; }   // outside the caller's length hint
         }
+        if (c < 0) bpe_put_length(len_out, nullptr, i, 0);        // no kernel will visit this row
     }
     for (int k = 0; k < BPE_N_CLASSES; ++k) {
         const uint32_t m = __ballot_sync(0xffffffffu, c == k);
@@ -244,7 +260,9 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                  const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
                  int32_t* __restrict__ work_counter, BpeDeviceTable t,
                  uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
-                 int32_t* __restrict__ status) {
+                 int32_t* __restrict__ status, BpeLengths len_out, int32_t n_direct, int32_t direct_limit) {
+    // list == NULL: no binning was done because the caller vouches that every row fits this kernel; the
+    // n_direct rows are taken as they come, and a row that does not fit is flagged and left empty.
     constexpr int P = BPE_LANE_SLOTS;
     constexpr int T = 32 * W;                    // lanes of a team
     constexpr int STRIDE = T + 2;                // elements between the slots of one lane
@@ -277,7 +295,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
     uint32_t nxt = cur + 2 * BUF;                // ... and in the buffer the round writes
     uint32_t* const xf = reinterpret_cast<uint32_t*>(sm + team_base + 2 * BUF);   // [T] entry of every lane's first pair (W > 1)
     uint32_t* const xl = xf + T;                                                  // [T] entry of every lane's last pair  (W > 1)
-    const int n_words = *list_count;
+    const int n_words = list ? *list_count : n_direct;
 
     for (;;) {
         int wi;
@@ -291,9 +309,19 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             wi = s_word[team];
         }
         if (wi >= n_words) break;
-        const int row = list[wi];
+        const int row = list ? list[wi] : wi;
         const int64_t off = offsets[row];
-        int n = (int)(offsets[row + 1] - off);               // 1 <= n <= T * P by classification
+        const int64_t n64 = offsets[row + 1] - off;
+        int n = (int)n64;                                    // 1 <= n <= T * P by classification
+        if (!list && (n64 < 1 || n64 > direct_limit)) {      // direct rows are not vetted: an empty row, or one the hint misstated
+            if (g == 0) {
+                counts[row] = 0;
+                bpe_put_length(len_out, nullptr, row, 0);
+                if (n64 > 0 && status) atomicOr(status + row, 8);
+            }
+            team_sync<W, BW>(team);                          // everybody has read the claimed index
+            continue;
+        }
         uint32_t Pp = (uint32_t)(n + T - 1) / T;             // positions per lane: lane g owns [g Pp, (g + 1) Pp)
         uint32_t inv = s_inv[Pp];
 
@@ -545,6 +573,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
         }
         if (g == 0) {
             counts[row] = n;
+            bpe_put_length(len_out, status, row, n);
             if (round >= max_rounds && status) atomicOr(status + row, 2);
         }
         team_sync<W, BW>(team);
@@ -560,7 +589,7 @@ bpe_long_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ o
                 const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
                 int32_t* __restrict__ work_counter, BpeDeviceTable t, uint16_t* __restrict__ out_tok,
                 int32_t* __restrict__ counts, int32_t* __restrict__ status,
-                uint8_t* __restrict__ long_area, unsigned long long* __restrict__ long_cursor) {
+                uint8_t* __restrict__ long_area, unsigned long long* __restrict__ long_cursor, BpeLengths len_out) {
     constexpr int W = BPE_LONG_WARPS;
     __shared__ uint32_t s_red[W][2];
     __shared__ uint2 s_hot[32 * 32];
@@ -713,6 +742,7 @@ bpe_long_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ o
 
         if (tt == 0) {
             counts[row] = n;
+            bpe_put_length(len_out, status, row, n);
             if (round >= max_rounds && status) atomicOr(status + row, 2);
         }
         __syncthreads();

@@ -36,6 +36,8 @@ std::atomic<int64_t> g_kmer_poll_limit{1 << 20};              // polls before a 
 std::atomic<int64_t> g_kmer_test_withhold{-1};                // tests: the ticket whose segment publishes nothing
 std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the host link (in + out) per chunk of the host pipeline
 std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
+std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
+std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
 
 int fail(int code, const char* fmt, ...) {
@@ -290,7 +292,8 @@ int bpe_launch_info(int dev, const BpeLaunchInfo** out) {
 // Class CLS's rows through teams of W warps (W >= 1 << CLS).
 template <int CLS, int W>
 int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDeviceTable& t, const uint8_t* bytes,
-                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, const BpeLengths& lo,
+                     bool direct, cudaStream_t st) {
     constexpr int BW = bpe_block_warps(W);
     constexpr int TEAMS = BW / W;                              // words in flight per block
     constexpr int WI = W == 1 ? 0 : W == 2 ? 1 : W == 4 ? 2 : W == 8 ? 3 : W == 16 ? 4 : 5;
@@ -301,27 +304,48 @@ int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDe
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
     bpe_lanes_kernel<W><<<(unsigned)grid, BW * 32, smem, st>>>(
-        bytes, offsets, s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
-        s.tokens, s.counts, status);
+        bytes, offsets, direct ? nullptr : s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
+        s.tokens, s.counts, status, lo, (int32_t)n_rows, (int32_t)bpe_class_capacity(CLS));
     LAUNCH_CHECK("bpe_lanes_kernel");
     return 0;
 }
 
-// A small batch cannot fill the GPU with one warp per word: give every word eight warps then, which
-// shortens each word's rounds instead.
+// A small batch cannot fill the GPU with one warp per word: a word then gets a wider team, which shortens
+// each of its rounds.  widen is the team width asked for (a power of two); a class never runs narrower
+// than its own width.
 template <int CLS>
 int launch_bpe_class(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDeviceTable& t, const uint8_t* bytes,
-                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, cudaStream_t st) {
+                     const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, const BpeLengths& lo,
+                     bool direct, int widen, cudaStream_t st) {
     constexpr int W = 1 << CLS;
-    const int64_t lim = g_bpe_block_team_rows.load();
-    if (W < 8 && n_rows <= (lim < 0 ? (int64_t)d.sm_count * 8 : lim))
-        return launch_bpe_lanes<CLS, 8>(d, li, t, bytes, offsets, n_rows, s, status, st);
-    return launch_bpe_lanes<CLS, W>(d, li, t, bytes, offsets, n_rows, s, status, st);
+#define BPE_WIDE(W2) \
+    if (W < W2 && widen >= W2) return launch_bpe_lanes<CLS, (W < W2 ? W2 : W)>(d, li, t, bytes, offsets, n_rows, s, status, lo, direct, st);
+    BPE_WIDE(32) BPE_WIDE(16) BPE_WIDE(8) BPE_WIDE(4) BPE_WIDE(2)
+#undef BPE_WIDE
+    return launch_bpe_lanes<CLS, W>(d, li, t, bytes, offsets, n_rows, s, status, lo, direct, st);
 }
 
+// Team width for a batch of n_rows words of at most max_row bytes.  Wider teams shorten a word's rounds but
+// take more of the GPU per word, so the width is the largest power of two that (a) keeps all words of the
+// batch resident at once on half of the GPU's warp slots (measured: beyond that a second wave costs more
+// than the shorter rounds save) and (b) leaves every lane at least four positions.  A large batch stays at
+// one warp per word.
+int bpe_team_width(const DeviceTables& d, const BpeLaunchInfo& li, int64_t n_rows, int64_t max_row) {
+    const int64_t forced = g_bpe_team_warps.load();
+    if (forced > 0) return (int)(forced > 32 ? 32 : forced);
+    const int64_t lim = g_bpe_block_team_rows.load();
+    if (lim >= 0) return n_rows <= lim ? 8 : 1;
+    const int64_t slots = (int64_t)d.sm_count * li.lanes[0] * 8 / 2;     // li.lanes[0]: blocks of 8 warps per SM
+    const int64_t widest = g_bpe_team_max.load();
+    int w = 1;
+    while (2 * w <= widest && (int64_t)(2 * w) * n_rows <= slots && (int64_t)(2 * w) * 128 <= max_row) w *= 2;
+    return w;
+}
+
+// lengths (may be NULL) receives every row's final token count for the format rf.
 int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
                   int64_t n_rows, int64_t total_bytes, int32_t* status, void* scratch, size_t scratch_bytes,
-                  cudaStream_t st) {
+                  const RowFormat& rf, int32_t* lengths, cudaStream_t st) {
     if (!scratch) return fail(DNATOK_ERR_SCRATCH, "BPE needs a scratch buffer (dnatok_scratch_bytes)");
     if (reinterpret_cast<uintptr_t>(scratch) & 255) return fail(DNATOK_ERR_SCRATCH, "scratch must be 256-byte aligned");
     BpeScratch s = bpe_scratch_layout(h, scratch, n_rows, total_bytes);
@@ -334,6 +358,7 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 192, st));   // class_count, work and long_cursor are adjacent
     // classes that can hold a row of this batch: bounded by the total size and by the caller's hint
     uint32_t class_mask = 0;
+    int64_t max_row = total_bytes;                          // no row is longer than this
     {
         int64_t lo = 1, hi = total_bytes;
         if (h->hint_max_row > 0) { lo = h->hint_min_row > 1 ? h->hint_min_row : 1; if (h->hint_max_row < hi) hi = h->hint_max_row; }
@@ -342,11 +367,18 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
             const int64_t c_hi = c < BPE_LONG_CLASS ? bpe_class_capacity(c) : INT64_MAX;
             if (c_hi >= lo && c_lo <= hi) class_mask |= 1u << c;
         }
+        max_row = hi;
     }
     if (((class_mask >> BPE_LONG_CLASS) & 1u) && !s.long_bytes) class_mask &= ~(1u << BPE_LONG_CLASS);
-    bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
-                                                                       s.class_list, s.counts, status, class_mask);
-    LAUNCH_CHECK("bpe_classify_kernel");
+    const BpeLengths lo{lengths, rf.cap_content, (rf.cls_id >= 0 ? 1 : 0) + (rf.sep_id >= 0 ? 1 : 0), rf.clip_is_error};
+    // One class only, by the caller's bounds on the row lengths: the rows need no binning, the class's kernel
+    // takes them as they come (and flags a row the bounds misstated).
+    const bool direct = h->hint_max_row > 0 && (class_mask & (class_mask - 1)) == 0 && !((class_mask >> BPE_LONG_CLASS) & 1u);
+    if (!direct) {
+        bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
+                                                                           s.class_list, s.counts, status, class_mask, lo);
+        LAUNCH_CHECK("bpe_classify_kernel");
+    }
     BpeDeviceTable t{d.disp, reinterpret_cast<const uint2*>(d.slots), d.merge_out, reinterpret_cast<const uint2*>(d.hot),
                      d.byte_tok, h->bpe.batch_safe ? 0 : 1, h->bpe.hot_ranks, h->bpe.bytes_hot ? 1u : 0u, h->bpe.n_tokens};
     // Classes outside the mask are not launched; a row that falls into one is flagged by the classifier.
@@ -358,12 +390,13 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
         if (grid < 1) grid = 1;
         bpe_long_kernel<<<(unsigned)grid, BPE_LONG_WARPS * 32, 0, st>>>(
             bytes, offsets, s.class_list + (int64_t)BPE_LONG_CLASS * n_rows, s.class_count + BPE_LONG_CLASS,
-            s.work + BPE_LONG_CLASS, t, s.tokens, s.counts, status, s.long_area, s.long_cursor);
+            s.work + BPE_LONG_CLASS, t, s.tokens, s.counts, status, s.long_area, s.long_cursor, lo);
         LAUNCH_CHECK("bpe_long_kernel");
     }
     int rc;
+    const int widen = bpe_team_width(d, *li, n_rows, max_row);
 #define BPE_CLASS(CLS)                                                                                              \
-    if (((class_mask >> CLS) & 1u) && (rc = launch_bpe_class<CLS>(d, *li, t, bytes, offsets, n_rows, s, status, st))) \
+    if (((class_mask >> CLS) & 1u) && (rc = launch_bpe_class<CLS>(d, *li, t, bytes, offsets, n_rows, s, status, lo, direct, widen, st))) \
         return rc;
     BPE_CLASS(5) BPE_CLASS(4) BPE_CLASS(3) BPE_CLASS(2) BPE_CLASS(1) BPE_CLASS(0)
 #undef BPE_CLASS
@@ -712,6 +745,8 @@ void dnatok_host_copy_bytes(int64_t* h2d, int64_t* d2h) {
 int dnatok_set_option(const char* name, int64_t value) {
     if (!name) return fail(DNATOK_ERR_INVALID, "bad option");
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
+    if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
+    if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_min_bytes")) { g_host_mask_min_bytes = value < 0 ? 0 : value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_threads")) { g_host_mask_threads = value < -1 ? -1 : value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_test_withhold_ticket")) { g_kmer_test_withhold = value < 0 ? -1 : value; return DNATOK_OK; }
@@ -886,10 +921,7 @@ int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_of
             return launch_kmer<true>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, 64, nullptr, nullptr, nullptr, d_lengths,
                                      nullptr, d_status, d_scratch, scratch_bytes, st);
         default: {
-            if (int rc = run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, st))
-                return rc;
-            BpeScratch s = bpe_scratch_layout(h, d_scratch, n_rows, total_bytes);
-            return launch_span_lengths(d_offsets, s.counts, n_rows, rf, d_lengths, d_status, st);
+            return run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, rf, d_lengths, st);
         }
     }
 }

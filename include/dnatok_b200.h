@@ -235,9 +235,12 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *                           gets DNATOK_ROW_STALLED (default 2^20, about 70 ms)
  *   "kmer_test_withhold_ticket"  for tests of that path: the segment with this ticket number (segment * n_rows + row)
  *                           publishes nothing, so the segments after it in its row give up; -1 (default): none
- *   "bpe_block_team_rows"   BPE batches of at most this many rows give every word a whole thread block
- *                           instead of one warp (lower latency when the batch cannot fill the GPU);
- *                           -1 (default): 8 rows per SM */
+ *   "bpe_team_warps"        BPE: warps that work on one word (power of two up to 32; a word never gets fewer
+ *                           than its length needs); 0 (default): chosen from the batch - the widest team that
+ *                           keeps all words resident on half of the GPU and leaves a lane four positions
+ *   "bpe_team_max"          widest team the automatic choice takes (default 8)
+ *   "bpe_block_team_rows"   older switch, kept for tests: batches of at most this many rows use teams of eight
+ *                           warps, larger ones a warp per word; -1 (default): the automatic choice above */
 int dnatok_set_option(const char* name, int64_t value);
 
 /* Number of kernels this library has launched from the calling process (for accounting). */
