@@ -213,11 +213,13 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
 }
 
 // Barrier over the W warps of one team (team index `team` within a block of BW warps).
-template <int W, int BW>
+// BAR0 is the hardware barrier of team 0; code that runs teams of several widths in one block gives every
+// width its own range of barriers.
+template <int W, int BW, int BAR0 = 1>
 __device__ __forceinline__ void team_sync(int team) {
     if (W == 1) __syncwarp();
     else if (W == BW) __syncthreads();
-    else asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(W * 32) : "memory");
+    else asm volatile("bar.sync %0, %1;" ::"r"(team + BAR0), "r"(W * 32) : "memory");
 }
 
 // Shared-memory accesses by 32-bit address in the shared window: the lanes kernel keeps its buffer
@@ -253,49 +255,66 @@ __device__ __forceinline__ uint32_t bpe_inv(uint32_t d) { return (0x80000000u + 
 #endif
 __host__ __device__ constexpr int bpe_min_blocks(int W) { return W <= 8 ? BPE_LANES_MIN_BLOCKS : W == 16 ? 2 : 1; }
 
-// W: warps per word.
-template <int W>
-__global__ void __launch_bounds__(bpe_block_warps(W) * 32, bpe_min_blocks(W))
-bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
-                 const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
-                 int32_t* __restrict__ work_counter, BpeDeviceTable t,
+// Block-wide tables of the lanes code, in static shared memory of the kernel that runs it.
+struct BpeLanesShared {
+    uint2* hot;          // [BPE_HOT_WORDS] direct table for pairs of small ids, row stride BPE_HOT_STRIDE
+    uint16_t* btok;      // [256] initial symbol of every byte
+    uint32_t* inv;       // [BPE_LANE_SLOTS + 1] bpe_inv(d)
+    uint32_t* red;       // [BW] per-warp partial minima
+    uint32_t* fn;        // [BW] per-warp carry functions of the two walks
+    uint32_t* blk;       // [BW] per-warp survivor count and border bits
+    int32_t* word;       // [BW] claimed word index, at the team's first warp
+};
+#define BPE_LANES_SHARED(BW_, sh)                                      \
+    __shared__ uint2 sh##_hot[BPE_HOT_WORDS];                          \
+    __shared__ uint16_t sh##_btok[256];                                \
+    __shared__ uint32_t sh##_inv[BPE_LANE_SLOTS + 1];                  \
+    __shared__ uint32_t sh##_red[BW_], sh##_fn[BW_], sh##_blk[BW_];    \
+    __shared__ int32_t sh##_word[BW_];                                 \
+    const BpeLanesShared sh{sh##_hot, sh##_btok, sh##_inv, sh##_red, sh##_fn, sh##_blk, sh##_word}
+
+template <int BW>
+__device__ __forceinline__ void bpe_lanes_setup(const BpeLanesShared& sh, const BpeDeviceTable& t) {
+    for (int i = threadIdx.x; i < BPE_HOT_WORDS; i += BW * 32) sh.hot[i] = make_uint2(BPE_FULL, BPE_FULL);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * 32; i += BW * 32) sh.hot[(i >> 5) * BPE_HOT_STRIDE + (i & 31)] = __ldg(t.hot + i);
+    for (int i = threadIdx.x; i < 256; i += BW * 32) sh.btok[i] = __ldg(t.byte_tok + i);
+    if (threadIdx.x >= 1 && threadIdx.x <= BPE_LANE_SLOTS) sh.inv[threadIdx.x] = bpe_inv(threadIdx.x);
+    __syncthreads();
+}
+
+// The words of one list through teams of W warps, in a block of BW warps whose teams each own TEAM_BYTES of
+// the dynamic shared memory.  list == NULL: no binning was done because the caller vouches that every row
+// fits; the n_words rows are taken as they come, and a row longer than direct_limit is flagged and left empty.
+template <int W, int BW, int BAR0, int TEAM_BYTES>
+__device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, uint16_t* const sm,
+                 const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
+                 const int32_t* __restrict__ list, const int n_words,
+                 int32_t* __restrict__ work_counter, const BpeDeviceTable& t,
                  uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
-                 int32_t* __restrict__ status, BpeLengths len_out, int32_t n_direct, int32_t direct_limit) {
-    // list == NULL: no binning was done because the caller vouches that every row fits this kernel; the
-    // n_direct rows are taken as they come, and a row that does not fit is flagged and left empty.
+                 int32_t* __restrict__ status, const BpeLengths& len_out, int32_t direct_limit) {
     constexpr int P = BPE_LANE_SLOTS;
     constexpr int T = 32 * W;                    // lanes of a team
     constexpr int STRIDE = T + 2;                // elements between the slots of one lane
     constexpr int BUF = (P + 1) * STRIDE;        // one token buffer: P slots and the copy of the next lane's first token
-    constexpr int BW = bpe_block_warps(W);
-    constexpr int TEAMS = BW / W;
-    extern __shared__ uint4 bpe_dyn[];
-    __shared__ uint2 s_hot[BPE_HOT_WORDS];       // direct table for pairs of small ids, row stride BPE_HOT_STRIDE
-    __shared__ uint16_t s_btok[256];
-    __shared__ uint32_t s_inv[P + 1];            // bpe_inv(d)
-    __shared__ uint32_t s_red[BW];               // per-warp partial minima
-    __shared__ uint32_t s_fn[BW];                // per-warp carry functions of the two walks
-    __shared__ uint32_t s_blk[BW];               // per-warp survivor count and border bits
-    __shared__ int32_t s_word[TEAMS];            // claimed word index
-    for (int i = threadIdx.x; i < BPE_HOT_WORDS; i += BW * 32) s_hot[i] = make_uint2(BPE_FULL, BPE_FULL);
-    __syncthreads();
-    for (int i = threadIdx.x; i < 32 * 32; i += BW * 32) s_hot[(i >> 5) * BPE_HOT_STRIDE + (i & 31)] = __ldg(t.hot + i);
-    for (int i = threadIdx.x; i < 256; i += BW * 32) s_btok[i] = __ldg(t.byte_tok + i);
-    if (threadIdx.x >= 1 && threadIdx.x <= P) s_inv[threadIdx.x] = bpe_inv(threadIdx.x);
-    __syncthreads();
+    static_assert(TEAM_BYTES >= (int)bpe_team_bytes(W), "team area too small");
+    uint16_t* const s_btok = sh.btok;
+    uint32_t* const s_inv = sh.inv;
+    uint32_t* const s_red = sh.red;
+    uint32_t* const s_fn = sh.fn;
+    uint32_t* const s_blk = sh.blk;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int team = warp / W, tw = warp % W;    // team, warp within team
+    int32_t* const s_word = sh.word + team * W;
     const int g = tw * 32 + lane;                // lane within team
     // All token traffic goes through shared-memory byte addresses held in registers.
     constexpr uint32_t S2 = 2 * STRIDE;          // bytes between the slots of one lane
-    uint16_t* const sm = reinterpret_cast<uint16_t*>(bpe_dyn);
-    const uint32_t team_base = (uint32_t)team * (bpe_team_bytes(W) / 2);
-    const uint32_t hot_base = smem_u32(s_hot);
+    const uint32_t team_base = (uint32_t)team * (TEAM_BYTES / 2);
+    const uint32_t hot_base = smem_u32(sh.hot);
     uint32_t cur = smem_u32(sm + team_base + g); // this lane's column in the buffer of live tokens
     uint32_t nxt = cur + 2 * BUF;                // ... and in the buffer the round writes
     uint32_t* const xf = reinterpret_cast<uint32_t*>(sm + team_base + 2 * BUF);   // [T] entry of every lane's first pair (W > 1)
     uint32_t* const xl = xf + T;                                                  // [T] entry of every lane's last pair  (W > 1)
-    const int n_words = list ? *list_count : n_direct;
 
     for (;;) {
         int wi;
@@ -304,11 +323,14 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             if (lane == 0) wi = atomicAdd(work_counter, 1);
             wi = __shfl_sync(BPE_FULL, wi, 0);
         } else {
-            if (g == 0) s_word[team] = atomicAdd(work_counter, 1);
-            team_sync<W, BW>(team);
-            wi = s_word[team];
+            if (g == 0) s_word[0] = atomicAdd(work_counter, 1);
+            team_sync<W, BW, BAR0>(team);
+            wi = s_word[0];
         }
-        if (wi >= n_words) break;
+        if (wi >= n_words) {
+            team_sync<W, BW, BAR0>(team);                    // the claim slot is reused by whatever this team runs next
+            break;
+        }
         const int row = list ? list[wi] : wi;
         const int64_t off = offsets[row];
         const int64_t n64 = offsets[row + 1] - off;
@@ -319,7 +341,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 bpe_put_length(len_out, nullptr, row, 0);
                 if (n64 > 0 && status) atomicOr(status + row, 8);
             }
-            team_sync<W, BW>(team);                          // everybody has read the claimed index
+            team_sync<W, BW, BAR0>(team);                          // everybody has read the claimed index
             continue;
         }
         uint32_t Pp = (uint32_t)(n + T - 1) / T;             // positions per lane: lane g owns [g Pp, (g + 1) Pp)
@@ -355,7 +377,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 }
             }
         }
-        team_sync<W, BW>(team);
+        team_sync<W, BW, BAR0>(team);
 
         int round = 0;
         const int max_rounds = n + 2;
@@ -365,7 +387,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             // the next lane's first token becomes this lane's slot Pp, so that every slot finds its right neighbour one slot up
             uint32_t t_up = lds_u16(cur + 2);                // handed from slot to slot: the token one slot up
             sts_u16(cur + Pp * S2, t_up);
-            team_sync<W, BW>(team);
+            team_sync<W, BW, BAR0>(team);
 
             // ---- A: entries of the lane's pairs, the word's bound, "right neighbour ranks better" bits.
             // While every token of the word is a small id all pairs come from the shared-memory table and
@@ -425,7 +447,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 xf[g] = v_first;
                 xl[g] = v_top;
                 if (lane == 0) s_red[warp] = emin;
-                team_sync<W, BW>(team);
+                team_sync<W, BW, BAR0>(team);
 #pragma unroll
                 for (int k = 0; k < W; ++k) emin = min(emin, s_red[team * W + k]);
                 v_nf = g + 1 < T ? xf[g + 1] : BPE_FULL;
@@ -487,7 +509,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 const uint32_t any_cand = t.single_step ? __ballot_sync(BPE_FULL, cand != 0u) : 0u;
                 const bool any_big = __any_sync(BPE_FULL, big);
                 if (lane == 0) s_fn[warp] = fn_r | (fn_l << 2) | (any_cand ? 16u : 0u) | (any_big ? 32u : 0u);
-                team_sync<W, BW>(team);
+                team_sync<W, BW, BAR0>(team);
                 bool carry_r = false, carry_l = false, earlier = false;
 #pragma unroll
                 for (int k = 0; k < W; ++k) all_hot = all_hot && !(s_fn[team * W + k] & 32u);
@@ -514,7 +536,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 }
                 const uint32_t first_valid = __shfl_sync(BPE_FULL, valid & 1u, 0);
                 if (lane == 31) s_blk[warp] = (uint32_t)incl | ((sel >> top) << 16) | (first_valid << 17);
-                team_sync<W, BW>(team);
+                team_sync<W, BW, BAR0>(team);
                 // lane k looks at block k: its count drops by one when the block before it merged across the border
                 const uint32_t w = lane < W ? s_blk[team * W + lane] : 0u;
                 uint32_t lost = __shfl_up_sync(BPE_FULL, (w >> 16) & 1u, 1);
@@ -562,7 +584,7 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
                 }
                 if (g == 0) sts_u16(dst + 2 * T, filler);    // the column behind the last lane
             }
-            team_sync<W, BW>(team);
+            team_sync<W, BW, BAR0>(team);
             const uint32_t sw = cur; cur = nxt; nxt = sw;
             n = n_new; Pp = Pn; inv = inv_n;
         }
@@ -576,8 +598,74 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
             bpe_put_length(len_out, status, row, n);
             if (round >= max_rounds && status) atomicOr(status + row, 2);
         }
-        team_sync<W, BW>(team);
+        team_sync<W, BW, BAR0>(team);
     }
+}
+
+// W: warps per word.
+template <int W>
+__global__ void __launch_bounds__(bpe_block_warps(W) * 32, bpe_min_blocks(W))
+bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
+                 const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
+                 int32_t* __restrict__ work_counter, BpeDeviceTable t,
+                 uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
+                 int32_t* __restrict__ status, BpeLengths len_out, int32_t n_direct, int32_t direct_limit) {
+    constexpr int BW = bpe_block_warps(W);
+    extern __shared__ uint4 bpe_dyn[];
+    BPE_LANES_SHARED(BW, sh);
+    bpe_lanes_setup<BW>(sh, t);
+    bpe_lanes_body<W, BW, 1, (int)bpe_team_bytes(W)>(sh, reinterpret_cast<uint16_t*>(bpe_dyn), bytes, offsets, list,
+                                                     list ? *list_count : n_direct, work_counter, t, out_tok, counts,
+                                                     status, len_out, direct_limit);
+}
+
+// Rows of several length classes in one launch: a block of BPE_MIXED_WARPS warps works through the classes
+// from the widest team to the narrowest, splitting into more and more teams on the way, so a batch of mixed
+// lengths has one tail instead of one per class.  levels.classes[k] holds the classes (bit c: class c) that
+// run with teams of 1 << k warps; a team's area at every width lies inside the area of the team it was part
+// of one width up, and every width has its own hardware barriers, so teams move on without waiting for their
+// block.
+constexpr int BPE_MIXED_WARPS = 16;
+constexpr int BPE_MIXED_LEVELS = 5;
+__host__ __device__ constexpr size_t bpe_mixed_warp_bytes() {      // shared memory per warp so that every width fits
+    size_t m = 0;
+    for (int w = 1; w <= BPE_MIXED_WARPS; w *= 2) {
+        const size_t per = (bpe_team_bytes(w) + (size_t)w - 1) / (size_t)w;
+        if (per > m) m = per;
+    }
+    return (m + 15) / 16 * 16;
+}
+__host__ __device__ constexpr size_t bpe_mixed_bytes() { return bpe_mixed_warp_bytes() * BPE_MIXED_WARPS; }
+struct BpeMixedLevels { uint32_t classes[BPE_MIXED_LEVELS]; };
+
+template <int W, int BAR0>
+__device__ __forceinline__ void bpe_mixed_level(const BpeLanesShared& sh, uint16_t* sm, uint32_t classes,
+                 const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
+                 const int32_t* __restrict__ class_list, int64_t n_rows, const int32_t* __restrict__ class_count,
+                 int32_t* __restrict__ work, const BpeDeviceTable& t, uint16_t* __restrict__ out_tok,
+                 int32_t* __restrict__ counts, int32_t* __restrict__ status, const BpeLengths& len_out) {
+    for (; classes; classes &= classes - 1u) {
+        const int c = __ffs(classes) - 1;
+        bpe_lanes_body<W, BPE_MIXED_WARPS, BAR0, (int)(bpe_mixed_warp_bytes() * W)>(
+            sh, sm, bytes, offsets, class_list + (int64_t)c * n_rows, class_count[c], work + c, t, out_tok, counts, status,
+            len_out, 0);
+    }
+}
+
+__global__ void __launch_bounds__(BPE_MIXED_WARPS * 32, 2)
+bpe_mixed_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
+                 const int32_t* __restrict__ class_list, int64_t n_rows, const int32_t* __restrict__ class_count,
+                 int32_t* __restrict__ work, BpeDeviceTable t, uint16_t* __restrict__ out_tok,
+                 int32_t* __restrict__ counts, int32_t* __restrict__ status, BpeLengths len_out, BpeMixedLevels levels) {
+    extern __shared__ uint4 bpe_dyn[];
+    BPE_LANES_SHARED(BPE_MIXED_WARPS, sh);
+    bpe_lanes_setup<BPE_MIXED_WARPS>(sh, t);
+    uint16_t* const sm = reinterpret_cast<uint16_t*>(bpe_dyn);
+#define BPE_LEVEL(K, BAR0) \
+    bpe_mixed_level<(1 << K), BAR0>(sh, sm, levels.classes[K], bytes, offsets, class_list, n_rows, class_count, work, t, \
+                                    out_tok, counts, status, len_out);
+    BPE_LEVEL(4, 0) BPE_LEVEL(3, 1) BPE_LEVEL(2, 3) BPE_LEVEL(1, 7) BPE_LEVEL(0, 0)
+#undef BPE_LEVEL
 }
 #undef BPE_SLOTS_DOWN
 

@@ -38,6 +38,7 @@ std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the h
 std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
+std::atomic<int64_t> g_bpe_mixed{1};                         // BPE: batches of several length classes in one launch
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
 
 int fail(int code, const char* fmt, ...) {
@@ -249,7 +250,7 @@ BpeScratch bpe_scratch_layout(const dnatok_handle* h, void* base, int64_t n_rows
 
 // Resident blocks per SM of every merge kernel on a device; filling it also sets the kernels'
 // shared-memory attribute, so a later launch does nothing but launch.
-struct BpeLaunchInfo { int lanes[BPE_LONG_CLASS]; };
+struct BpeLaunchInfo { int lanes[BPE_LONG_CLASS]; int mixed; };   // resident blocks per SM of every merge kernel
 
 template <int W>
 int bpe_setup_lanes(int* bps) {
@@ -273,6 +274,9 @@ int bpe_launch_info(int dev, const BpeLaunchInfo** out) {
             (rc = bpe_setup_lanes<4>(&li.lanes[2])) || (rc = bpe_setup_lanes<8>(&li.lanes[3])) ||
             (rc = bpe_setup_lanes<16>(&li.lanes[4])) || (rc = bpe_setup_lanes<32>(&li.lanes[5])))
             return rc;
+        CUDA_TRY(cudaFuncSetAttribute(bpe_mixed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bpe_mixed_bytes()));
+        CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&li.mixed, bpe_mixed_kernel, BPE_MIXED_WARPS * 32, bpe_mixed_bytes()));
+        if (li.mixed < 1) li.mixed = 1;
         cudaFuncAttributes fa;
         CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_long_kernel));      // loads the kernel's code now, not at its first launch
         CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_classify_kernel));
@@ -395,6 +399,25 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     }
     int rc;
     const int widen = bpe_team_width(d, *li, n_rows, max_row);
+    if (!direct && g_bpe_mixed.load()) {
+        // the classes below the widest in one launch, every class at the width of its own or the batch's, whichever is wider
+        BpeMixedLevels lv{};
+        int level_of_widen = 0;
+        while ((2 << level_of_widen) <= widen && level_of_widen + 1 < BPE_MIXED_LEVELS) ++level_of_widen;
+        uint32_t any = 0;
+        for (int c = 0; c < BPE_MIXED_LEVELS; ++c)
+            if ((class_mask >> c) & 1u) { lv.classes[c > level_of_widen ? c : level_of_widen] |= 1u << c; any = 1; }
+        if ((class_mask >> 5) & 1u)
+            if ((rc = launch_bpe_class<5>(d, *li, t, bytes, offsets, n_rows, s, status, lo, false, widen, st))) return rc;
+        if (any) {
+            int64_t grid = (int64_t)d.sm_count * li->mixed;
+            if (grid > n_rows) grid = n_rows;
+            bpe_mixed_kernel<<<(unsigned)grid, BPE_MIXED_WARPS * 32, bpe_mixed_bytes(), st>>>(
+                bytes, offsets, s.class_list, n_rows, s.class_count, s.work, t, s.tokens, s.counts, status, lo, lv);
+            LAUNCH_CHECK("bpe_mixed_kernel");
+        }
+        return 0;
+    }
 #define BPE_CLASS(CLS)                                                                                              \
     if (((class_mask >> CLS) & 1u) && (rc = launch_bpe_class<CLS>(d, *li, t, bytes, offsets, n_rows, s, status, lo, direct, widen, st))) \
         return rc;
@@ -747,6 +770,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
+    if (!strcmp(name, "bpe_mixed_launch")) { g_bpe_mixed = value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_min_bytes")) { g_host_mask_min_bytes = value < 0 ? 0 : value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_threads")) { g_host_mask_threads = value < -1 ? -1 : value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_test_withhold_ticket")) { g_kmer_test_withhold = value < 0 ? -1 : value; return DNATOK_OK; }

@@ -239,6 +239,8 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *                           than its length needs); 0 (default): chosen from the batch - the widest team that
  *                           keeps all words resident on half of the GPU and leaves a lane four positions
  *   "bpe_team_max"          widest team the automatic choice takes (default 8)
+ *   "bpe_mixed_launch"      1 (default): the rows of all length classes up to 16,384 bytes go through one launch
+ *                           whose blocks work from the longest class down; 0: one launch per class
  *   "bpe_block_team_rows"   older switch, kept for tests: batches of at most this many rows use teams of eight
  *                           warps, larger ones a warp per word; -1 (default): the automatic choice above */
 int dnatok_set_option(const char* name, int64_t value);

@@ -12,16 +12,21 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.fixture(params=["auto", "warp_teams", "block_teams"])
+@pytest.fixture(params=["auto", "warp_teams", "block_teams", "teams_of_2", "teams_of_32", "launch_per_class"])
 def bpe_team_mode(request):
     """Run a BPE test under each way of assigning warps to words (small batches would otherwise only
-    ever see the block-per-word kernels)."""
+    ever see the wide-team kernels), and with one launch per length class instead of the shared one."""
     from dnatok_b200 import _cabi
     L = _cabi.lib()
-    value = {"auto": -1, "warp_teams": 0, "block_teams": 1 << 40}[request.param]
-    _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", value))
+    rows, warps, mixed = {"auto": (-1, 0, 1), "warp_teams": (0, 0, 1), "block_teams": (1 << 40, 0, 1),
+                          "teams_of_2": (-1, 2, 1), "teams_of_32": (-1, 32, 1), "launch_per_class": (-1, 0, 0)}[request.param]
+    _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", rows))
+    _cabi.check(L.dnatok_set_option(b"bpe_team_warps", warps))
+    _cabi.check(L.dnatok_set_option(b"bpe_mixed_launch", mixed))
     yield request.param
     _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", -1))
+    _cabi.check(L.dnatok_set_option(b"bpe_team_warps", 0))
+    _cabi.check(L.dnatok_set_option(b"bpe_mixed_launch", 1))
 
 
 @pytest.fixture(scope="module")
