@@ -488,10 +488,10 @@ void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_
                         int64_t n_rows, int64_t total_bytes, const RowFormat& rf, void* ids, void* mask,
                         const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets, int32_t* status,
                         cudaStream_t st) {
-    const unsigned grid = (unsigned)((n_rows + KW_WARPS - 1) / KW_WARPS);
+    const unsigned grid = (unsigned)((n_rows + KW_ROW_WARPS - 1) / KW_ROW_WARPS);
     const bool fuse = mask && rf.mask_bits == (int)sizeof(IdT) * 8;
     const bool affine = affine_base >= 0;
-#define KLAUNCH(A, F) kmer_warp_rows_kernel<IdT, K, A, F><<<grid, KW_WARPS * 32, 0, st>>>(                          \
+#define KLAUNCH(A, F) kmer_warp_rows_kernel<IdT, K, A, F><<<grid, KW_ROW_WARPS * 32, 0, st>>>(                                \
         bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
         lengths_out, out_offsets, status)
     if (affine && fuse) KLAUNCH(true, true);

@@ -188,7 +188,11 @@ kmer_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
 namespace dnatok {
 
 constexpr int KW_WARPS = 8;
-constexpr int KW_BLOCKS_PER_SM = 6;     // row-per-warp encoder: 65,536 / (6 * 256) registers, i.e. 40 per thread
+// Row-per-warp encoder: two rows (warps) per block, because a block's slot is only refilled when its slowest
+// row is done (rows with N runs take longer); 24 such blocks per SM, i.e. 65,536 / (24 * 64) = 42 registers
+// per thread at most.
+constexpr int KW_ROW_WARPS = 2;
+constexpr int KW_BLOCKS_PER_SM = 24;
 
 // 2-bit codes of four ASCII bytes at once (A C G T -> 0 1 2 3 in each byte's low bits), and a word
 // that is zero exactly in the bytes that are one of A, C, G, T.
@@ -594,7 +598,7 @@ __device__ __forceinline__ void kmer_finish_row(const KmerRow<IdT>& r, int64_t r
 
 // One warp per row, no scratch memory: used when the caller passes no scratch buffer.
 template <typename IdT, int K, bool AFFINE, bool FUSE_MASK>
-__global__ void __launch_bounds__(KW_WARPS * 32, KW_BLOCKS_PER_SM)
+__global__ void __launch_bounds__(KW_ROW_WARPS * 32, KW_BLOCKS_PER_SM)
 kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets, int64_t n_rows,
                       int64_t total_bytes, const int32_t* __restrict__ kmer_ids, int32_t affine_base,
                       const int32_t* __restrict__ single_ids, RowFormat f, IdT* __restrict__ ids,
@@ -602,7 +606,7 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                       int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
                       int32_t* __restrict__ status) {
     const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * KW_WARPS + (threadIdx.x >> 5);
+    const int64_t row = (int64_t)blockIdx.x * KW_ROW_WARPS + (threadIdx.x >> 5);
     if (row >= n_rows) return;
     const KmerRow<IdT> r = kmer_row_setup<IdT, K>(bytes, offsets[row], offsets[row + 1], row, total_bytes, f, ids, lengths_in,
                                                   out_offsets);
