@@ -73,7 +73,14 @@ struct BpeDeviceTable {
     uint32_t hot_ranks;          // every rank below this creates an id < 32
     uint32_t bytes_hot;          // 1: every initial symbol is an id < 32
     uint32_t filler;             // one past the largest token id: a token whose pairs never merge (disp and slots have room for it)
+    // the table packed for shared memory (NULL when it does not exist): 16-bit displacements, 32-bit slots
+    // (left << 16) | rank, one word (F << 16) | created id per rank
+    const uint4* compact;
+    uint32_t compact_bytes, compact_slot, compact_info, compact_last;
 };
+
+// Shared-memory addresses of the three parts of the packed table.
+struct BpeSmemTable { uint32_t disp, slot, info, last; };
 
 // One table entry: x = (rank << 16) | created id, y = (left id << 16) | F.  Ranks compare like the x
 // words themselves (equal ranks create equal ids), so x is what the kernels keep per pair.  What
@@ -233,10 +240,29 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
 __device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
     asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((uint16_t)v) : "memory");
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
     return v;
+}
+
+// The entry of the pair (a, b) from the packed table in shared memory: three dependent shared-memory
+// loads where bpe_cold_entry makes two dependent loads from global memory.
+__device__ __forceinline__ uint2 bpe_smem_entry(const BpeSmemTable& st, uint32_t a, uint32_t b) {
+    const uint32_t idx = min(lds_u16(st.disp + 2u * a) + b, st.last);
+    const uint32_t s = lds_u32(st.slot + 4u * idx);
+    const bool hit = (s >> 16) == a;
+    const uint32_t r = hit ? (s & 0xFFFFu) : 0u;
+    const uint32_t inf = lds_u32(st.info + 4u * r);
+    uint2 e;
+    e.x = hit ? (r << 16) | (inf & 0xFFFFu) : BPE_FULL;
+    e.y = hit ? (inf & 0xFFFF0000u) | r : BPE_FULL;
+    return e;
 }
 
 // floor(x / d) for 1 <= d <= 32, x < 2^16: __umulhi(2 x + 1, ceil(2^31 / d)).
@@ -286,8 +312,8 @@ __device__ __forceinline__ void bpe_lanes_setup(const BpeLanesShared& sh, const 
 // The words of one list through teams of W warps, in a block of BW warps whose teams each own TEAM_BYTES of
 // the dynamic shared memory.  list == NULL: no binning was done because the caller vouches that every row
 // fits; the n_words rows are taken as they come, and a row longer than direct_limit is flagged and left empty.
-template <int W, int BW, int BAR0, int TEAM_BYTES>
-__device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, uint16_t* const sm,
+template <int W, int BW, int BAR0, int TEAM_BYTES, bool ST = false>
+__device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, const BpeSmemTable& stab, uint16_t* const sm,
                  const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
                  const int32_t* __restrict__ list, const int n_words,
                  int32_t* __restrict__ work_counter, const BpeDeviceTable& t,
@@ -417,7 +443,7 @@ __device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, uint16_
 #define BPE_A(J)                                                                              \
                     case J + 1: {                                                             \
                         const uint32_t a = lds_u16(cur + J * S2), b = t_up;                   \
-                        const uint2 e = bpe_cold_entry(t, a, b);             /* the filler's pairs are empty */ \
+                        const uint2 e = ST ? bpe_smem_entry(stab, a, b) : bpe_cold_entry(t, a, b);   /* the filler's pairs are empty */ \
                         t_up = a;                                                             \
                         BPE_A_TAIL(J)                                                         \
                     }
@@ -614,9 +640,33 @@ bpe_lanes_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ 
     extern __shared__ uint4 bpe_dyn[];
     BPE_LANES_SHARED(BW, sh);
     bpe_lanes_setup<BW>(sh, t);
-    bpe_lanes_body<W, BW, 1, (int)bpe_team_bytes(W)>(sh, reinterpret_cast<uint16_t*>(bpe_dyn), bytes, offsets, list,
+    bpe_lanes_body<W, BW, 1, (int)bpe_team_bytes(W)>(sh, BpeSmemTable{}, reinterpret_cast<uint16_t*>(bpe_dyn), bytes, offsets, list,
                                                      list ? *list_count : n_direct, work_counter, t, out_tok, counts,
                                                      status, len_out, direct_limit);
+}
+
+// The same for a vocabulary whose packed table fits into shared memory beside the teams' buffers: one block of
+// 32 warps per SM, the table copied in once per block, every lookup of the general mode answered from it.
+constexpr int BPE_ST_WARPS = 32;
+__host__ __device__ constexpr size_t bpe_st_team_area(int W) { return (size_t)(BPE_ST_WARPS / W) * bpe_team_bytes(W); }
+template <int W>
+__global__ void __launch_bounds__(BPE_ST_WARPS * 32, 1)
+bpe_lanes_st_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ offsets,
+                    const int32_t* __restrict__ list, const int32_t* __restrict__ list_count,
+                    int32_t* __restrict__ work_counter, BpeDeviceTable t,
+                    uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
+                    int32_t* __restrict__ status, BpeLengths len_out, int32_t n_direct, int32_t direct_limit) {
+    extern __shared__ uint4 bpe_dyn[];
+    BPE_LANES_SHARED(BPE_ST_WARPS, sh);
+    uint4* const tab = bpe_dyn + bpe_st_team_area(W) / 16;
+    for (uint32_t i = threadIdx.x; i < t.compact_bytes / 16; i += BPE_ST_WARPS * 32) tab[i] = __ldg(t.compact + i);
+    bpe_lanes_setup<BPE_ST_WARPS>(sh, t);                     // ends with a block-wide barrier
+    const uint32_t base = smem_u32(tab);
+    const BpeSmemTable stab{base, base + t.compact_slot, base + t.compact_info, t.compact_last};
+    // sixteen teams of two warps need sixteen hardware barriers: barrier 0 is theirs as well once the set-up is over
+    bpe_lanes_body<W, BPE_ST_WARPS, (W == 2 ? 0 : 1), (int)bpe_team_bytes(W), true>(sh, stab, reinterpret_cast<uint16_t*>(bpe_dyn), bytes,
+                                                                     offsets, list, list ? *list_count : n_direct, work_counter,
+                                                                     t, out_tok, counts, status, len_out, direct_limit);
 }
 
 // Rows of several length classes in one launch: a block of BPE_MIXED_WARPS warps works through the classes
@@ -647,7 +697,7 @@ __device__ __forceinline__ void bpe_mixed_level(const BpeLanesShared& sh, uint16
     for (; classes; classes &= classes - 1u) {
         const int c = __ffs(classes) - 1;
         bpe_lanes_body<W, BPE_MIXED_WARPS, BAR0, (int)(bpe_mixed_warp_bytes() * W)>(
-            sh, sm, bytes, offsets, class_list + (int64_t)c * n_rows, class_count[c], work + c, t, out_tok, counts, status,
+            sh, BpeSmemTable{}, sm, bytes, offsets, class_list + (int64_t)c * n_rows, class_count[c], work + c, t, out_tok, counts, status,
             len_out, 0);
     }
 }

@@ -88,6 +88,29 @@ int build_bpe_table(const int32_t* a, const int32_t* b, const int32_t* o, int32_
         const uint64_t hi = ((uint64_t)a[r] << 16) | f;
         return lo | (hi << 32);
     };
+    {
+        uint32_t max_disp = 0;
+        for (uint32_t d : t->disp) max_disp = std::max(max_disp, d);
+        t->compact.clear();
+        if (n_tokens + 1 < 0xFFFFu && max_disp <= 0xFFFFu && n > 0) {
+            size_t used = 0;
+            for (size_t i = 0; i < slots.size(); ++i) if (slots[i] != 0xFFFFFFFFu) used = i + 1;
+            auto pad16 = [](size_t x) { return (x + 15) / 16 * 16; };
+            const size_t off_slot = pad16(2 * t->disp.size()), off_info = off_slot + pad16(4 * (used + 1));
+            t->compact.assign(off_info + pad16(4 * (size_t)n), 0xFF);
+            uint16_t* d16 = reinterpret_cast<uint16_t*>(t->compact.data());
+            uint32_t* s32 = reinterpret_cast<uint32_t*>(t->compact.data() + off_slot);
+            uint32_t* i32 = reinterpret_cast<uint32_t*>(t->compact.data() + off_info);
+            for (size_t i = 0; i < t->disp.size(); ++i) d16[i] = (uint16_t)t->disp[i];
+            for (size_t i = 0; i < used; ++i) s32[i] = slots[i];
+            s32[used] = 0xFFFFFFFFu;
+            for (int32_t r = 0; r < n; ++r)
+                i32[r] = ((safe ? (uint32_t)t->future[r] : (uint32_t)r + 1u) << 16) | (uint32_t)o[r];
+            t->compact_slot = (uint32_t)off_slot;
+            t->compact_info = (uint32_t)off_info;
+            t->compact_last = (uint32_t)used;
+        }
+    }
     t->slots.assign(slots.size(), ~0ull);
     for (size_t i = 0; i < slots.size(); ++i)
         if (slots[i] != 0xFFFFFFFFu) t->slots[i] = entry((int32_t)(slots[i] & 0xFFFFu));

@@ -25,6 +25,13 @@ struct BpeHostTable {
     uint32_t hot_ranks = 0;            // every rank below this creates an id < 32
     bool bytes_hot = false;            // every initial symbol is an id < 32
     std::vector<uint16_t> byte_tok;    // [256] initial symbol of each byte
+    // The same table packed for a kernel that keeps it in shared memory (empty when an id or a displacement does
+    // not fit 16 bits): 16-bit displacements [n_tokens + 1], then 32-bit slots (left id << 16) | rank up to the last
+    // used one plus one empty slot (larger indices are clamped to it), then one word per rank,
+    // (future rank << 16) | created id.  compact_slot / compact_info are the byte offsets of the second and
+    // third part (multiples of 16).
+    std::vector<uint8_t> compact;
+    uint32_t compact_slot = 0, compact_info = 0, compact_last = 0;   // compact_last: index of the empty last slot
     uint32_t n_tokens = 0;
     uint32_t n_merges = 0;
     // True when every merge's operands are created by lower ranks (or are initial symbols).

@@ -38,6 +38,7 @@ std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the h
 std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
+std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
 std::atomic<int64_t> g_bpe_mixed{1};                         // BPE: batches of several length classes in one launch
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
 
@@ -66,6 +67,7 @@ int fail(int code, const char* fmt, ...) {
 
 struct DeviceTables {
     int32_t* lut256 = nullptr;       // char LUT / k-mer single ids
+    uint8_t* bpe_compact = nullptr;  // BPE: the merge table packed for shared memory (when it exists)
     int32_t* start_lut = nullptr;    // char: ids of a row's first character, when they differ
     int32_t* kmer_ids = nullptr;
     int32_t* table5 = nullptr;       // table-driven k-mer handles: 5^k windows, runs
@@ -143,7 +145,7 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
             ~Undo() {
                 if (keep) return;
                 DeviceTables& x = h->dev[dev];
-                void* ptrs[] = {x.lut256, x.start_lut, x.kmer_ids, x.table5, x.exp_off, x.exp_ids, x.disp, x.slots, x.merge_out, x.hot, x.byte_tok};
+                void* ptrs[] = {x.lut256, x.start_lut, x.kmer_ids, x.table5, x.exp_off, x.exp_ids, x.disp, x.slots, x.merge_out, x.hot, x.byte_tok, x.bpe_compact};
                 for (void* p : ptrs) if (p) cudaFree(p);
                 h->dev.erase(dev);
             }
@@ -160,6 +162,7 @@ int tables_for_current_device(dnatok_handle* h, DeviceTables** out) {
         if (!h->start_lut.empty() && (rc = upload(&d.start_lut, h->start_lut))) return rc;
         if (h->kind == DNATOK_KIND_BPE) {
             if ((rc = upload(&d.disp, h->bpe.disp))) return rc;
+            if (!h->bpe.compact.empty() && (rc = upload(&d.bpe_compact, h->bpe.compact))) return rc;
             if ((rc = upload(&d.slots, h->bpe.slots))) return rc;
             if ((rc = upload(&d.merge_out, h->bpe.merge_out))) return rc;
             if ((rc = upload(&d.hot, h->bpe.hot))) return rc;
@@ -250,7 +253,22 @@ BpeScratch bpe_scratch_layout(const dnatok_handle* h, void* base, int64_t n_rows
 
 // Resident blocks per SM of every merge kernel on a device; filling it also sets the kernels'
 // shared-memory attribute, so a later launch does nothing but launch.
-struct BpeLaunchInfo { int lanes[BPE_LONG_CLASS]; int mixed; };   // resident blocks per SM of every merge kernel
+struct BpeLaunchInfo { int lanes[BPE_LONG_CLASS]; int mixed; int st_room[BPE_LONG_CLASS]; };   // resident blocks per SM of every merge kernel; st_room: bytes a shared-memory table may take beside the teams of each width (0: kernel not usable)
+
+template <int W>
+int bpe_setup_st(int* room) {
+    cudaFuncAttributes fa;
+    CUDA_TRY(cudaFuncGetAttributes(&fa, bpe_lanes_st_kernel<W>));
+    int dev = 0, most = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&most, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    const int64_t dyn = (int64_t)most - (int64_t)fa.sharedSizeBytes;
+    *room = 0;
+    if (dyn <= (int64_t)bpe_st_team_area(W)) return 0;
+    CUDA_TRY(cudaFuncSetAttribute(bpe_lanes_st_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    *room = (int)(dyn - (int64_t)bpe_st_team_area(W));
+    return 0;
+}
 
 template <int W>
 int bpe_setup_lanes(int* bps) {
@@ -273,6 +291,10 @@ int bpe_launch_info(int dev, const BpeLaunchInfo** out) {
         if ((rc = bpe_setup_lanes<1>(&li.lanes[0])) || (rc = bpe_setup_lanes<2>(&li.lanes[1])) ||
             (rc = bpe_setup_lanes<4>(&li.lanes[2])) || (rc = bpe_setup_lanes<8>(&li.lanes[3])) ||
             (rc = bpe_setup_lanes<16>(&li.lanes[4])) || (rc = bpe_setup_lanes<32>(&li.lanes[5])))
+            return rc;
+        if ((rc = bpe_setup_st<1>(&li.st_room[0])) || (rc = bpe_setup_st<2>(&li.st_room[1])) ||
+            (rc = bpe_setup_st<4>(&li.st_room[2])) || (rc = bpe_setup_st<8>(&li.st_room[3])) ||
+            (rc = bpe_setup_st<16>(&li.st_room[4])) || (rc = bpe_setup_st<32>(&li.st_room[5])))
             return rc;
         CUDA_TRY(cudaFuncSetAttribute(bpe_mixed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bpe_mixed_bytes()));
         CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&li.mixed, bpe_mixed_kernel, BPE_MIXED_WARPS * 32, bpe_mixed_bytes()));
@@ -298,9 +320,22 @@ template <int CLS, int W>
 int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDeviceTable& t, const uint8_t* bytes,
                      const int64_t* offsets, int64_t n_rows, const BpeScratch& s, int32_t* status, const BpeLengths& lo,
                      bool direct, cudaStream_t st) {
+    constexpr int WI = W == 1 ? 0 : W == 2 ? 1 : W == 4 ? 2 : W == 8 ? 3 : W == 16 ? 4 : 5;
+    if (t.compact && g_bpe_smem_table.load() && t.compact_bytes <= (uint32_t)li.st_room[WI]) {
+        // the whole merge table fits into shared memory beside the teams: one block of 32 warps per SM
+        constexpr int ST_TEAMS = BPE_ST_WARPS / W;
+        int64_t grid = d.sm_count;
+        const int64_t need = (n_rows + ST_TEAMS - 1) / ST_TEAMS;
+        if (grid > need) grid = need;
+        if (grid < 1) grid = 1;
+        bpe_lanes_st_kernel<W><<<(unsigned)grid, BPE_ST_WARPS * 32, bpe_st_team_area(W) + t.compact_bytes, st>>>(
+            bytes, offsets, direct ? nullptr : s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
+            s.tokens, s.counts, status, lo, (int32_t)n_rows, (int32_t)bpe_class_capacity(CLS));
+        LAUNCH_CHECK("bpe_lanes_st_kernel");
+        return 0;
+    }
     constexpr int BW = bpe_block_warps(W);
     constexpr int TEAMS = BW / W;                              // words in flight per block
-    constexpr int WI = W == 1 ? 0 : W == 2 ? 1 : W == 4 ? 2 : W == 8 ? 3 : W == 16 ? 4 : 5;
     const size_t smem = (size_t)TEAMS * bpe_team_bytes(W);
     // Resident-size grid: every team pulls words from the class's shared counter.
     int64_t grid = (int64_t)d.sm_count * li.lanes[WI];
@@ -384,7 +419,9 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
         LAUNCH_CHECK("bpe_classify_kernel");
     }
     BpeDeviceTable t{d.disp, reinterpret_cast<const uint2*>(d.slots), d.merge_out, reinterpret_cast<const uint2*>(d.hot),
-                     d.byte_tok, h->bpe.batch_safe ? 0 : 1, h->bpe.hot_ranks, h->bpe.bytes_hot ? 1u : 0u, h->bpe.n_tokens};
+                     d.byte_tok, h->bpe.batch_safe ? 0 : 1, h->bpe.hot_ranks, h->bpe.bytes_hot ? 1u : 0u, h->bpe.n_tokens,
+                     reinterpret_cast<const uint4*>(d.bpe_compact), (uint32_t)h->bpe.compact.size(), h->bpe.compact_slot,
+                     h->bpe.compact_info, h->bpe.compact_last};
     // Classes outside the mask are not launched; a row that falls into one is flagged by the classifier.
     // Longest class first: its few, slow words start while nothing else competes for the SMs.
     if ((class_mask >> BPE_LONG_CLASS) & 1u) {
@@ -770,6 +807,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
+    if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_mixed_launch")) { g_bpe_mixed = value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_min_bytes")) { g_host_mask_min_bytes = value < 0 ? 0 : value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_threads")) { g_host_mask_threads = value < -1 ? -1 : value; return DNATOK_OK; }
@@ -883,7 +921,7 @@ void dnatok_destroy(dnatok_handle* h) {
         DeviceTables& d = kv.second;
         if (cudaSetDevice(kv.first) != cudaSuccess) continue;
         if (d.stream) cudaStreamSynchronize(d.stream);
-        void* ptrs[] = {d.lut256, d.start_lut, d.table5, d.exp_off, d.exp_ids, d.kmer_ids, d.disp, d.slots, d.merge_out, d.hot, d.byte_tok, d.st_bytes, d.st_offsets,
+        void* ptrs[] = {d.lut256, d.start_lut, d.table5, d.exp_off, d.exp_ids, d.kmer_ids, d.disp, d.slots, d.merge_out, d.hot, d.byte_tok, d.bpe_compact, d.st_bytes, d.st_offsets,
                         d.st_ids, d.st_mask, d.st_lengths, d.st_status, d.st_out_offsets, d.st_scratch};
         for (void* p : ptrs) if (p) cudaFree(p);
         if (d.stream) cudaStreamDestroy(d.stream);
@@ -1037,6 +1075,15 @@ int dnatok_embed(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offs
     if ((reinterpret_cast<uintptr_t>(d_weight) | reinterpret_cast<uintptr_t>(d_out)) & 15)
         return fail(DNATOK_ERR_INVALID, "weight and output must be 16-byte aligned");
     if (h->sp.pad_id >= vocab_rows) return fail(DNATOK_ERR_INVALID, "pad id outside the weight matrix");
+    {
+        // every id this handle can produce must be a row of the weight matrix; nothing is remapped silently
+        int32_t top = -1;
+        for (int32_t v : h->lut256) if (v > top) top = v;
+        if (fmt->add_special) { if (h->sp.cls_id > top) top = h->sp.cls_id; if (h->sp.sep_id > top) top = h->sp.sep_id; }
+        if (top >= vocab_rows)
+            return fail(DNATOK_ERR_INVALID, "the tokenizer produces ids up to %d but the weight matrix has %lld rows", top,
+                        (long long)vocab_rows);
+    }
     cudaStream_t st = (cudaStream_t)stream;
     DeviceTables* d;
     if (int rc = tables_for_current_device(h, &d)) return rc;
@@ -1306,6 +1353,8 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
             if (n < lo) lo = n;
             if (n > hi) hi = n;
         }
+        if (hi > 0x7fffffff && h->kind == DNATOK_KIND_KMER)
+            return fail(DNATOK_ERR_UNSUPPORTED, "a k-mer row of %lld bytes: rows must be shorter than 2 GiB", (long long)hi);
         h->hint_min_row = lo; h->hint_max_row = hi > 0 ? hi : 1;
     }
     DeviceTables* d;

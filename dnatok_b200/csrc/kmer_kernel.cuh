@@ -328,6 +328,11 @@ struct KmerRow {
     int shift;                 // left padding columns
 };
 
+// A row of 2 GiB or more is encoded up to its first 2^31 - 1 bytes and reported.
+__device__ __forceinline__ void kmer_flag_long_row(int64_t len64, int32_t* status, int64_t row, int lane) {
+    if (len64 > 0x7fffffff && status && lane == 0) atomicOr(status + row, 1);
+}
+
 // off, end: the row's bounds in the input buffer (offsets[row], offsets[row + 1])
 template <typename IdT, int K>
 __device__ __forceinline__ KmerRow<IdT> kmer_row_setup(const uint8_t* bytes, int64_t off, int64_t end, int64_t row,
@@ -335,7 +340,7 @@ __device__ __forceinline__ KmerRow<IdT> kmer_row_setup(const uint8_t* bytes, int
                                                        const int32_t* lengths_in, const int64_t* out_offsets) {
     KmerRow<IdT> r;
     const int64_t len64 = end - off;
-    r.len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);              // rows are < 2 GiB
+    r.len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);              // a longer row is cut here and flagged (kmer_flag_long_row)
     r.n_win = (r.len + K - 1) / K;
     r.src = bytes + off;
     r.room_total = total_bytes - off;
@@ -612,6 +617,7 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                                                   out_offsets);
     const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
     const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
+    kmer_flag_long_row(offsets[row + 1] - offsets[row], status, row, lane);
     bool clipped = false;
     const int base = kmer_encode_windows<IdT, K, AFFINE, FUSE_MASK>(r, cap, kmer_ids, affine_base, single_ids, mdelta, lane,
                                                                     0, r.n_win, 0, &clipped);
@@ -672,6 +678,7 @@ kmer_seg_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restric
         const KmerRow<IdT> r = kmer_row_setup<IdT, K>(bytes, off, end, row, total_bytes, f, ids, lengths_in, out_offsets);
         const int64_t w0 = (int64_t)seg * KSEG_WINDOWS;
         if (seg > 0 && w0 >= r.n_win) continue;                                  // the row ended in an earlier segment
+        if (seg == 0) kmer_flag_long_row(end - off, status, row, lane);
         const bool last = seg == n_seg - 1 || w0 + KSEG_WINDOWS >= r.n_win;
         const int w_end = last ? r.n_win : (int)w0 + KSEG_WINDOWS;
         uint32_t* my_flag = flags + (int64_t)seg * n_rows + row;

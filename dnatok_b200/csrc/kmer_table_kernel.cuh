@@ -35,6 +35,7 @@ kmer_table_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__
     const int64_t off = offsets[row];
     const int64_t len64 = offsets[row + 1] - off;
     const int len = (int)(len64 < 0x7fffffff ? len64 : 0x7fffffff);
+    if (!COUNT_ONLY) kmer_flag_long_row(len64, status, row, lane);
     const int k = t.k;
     const int n_full = len / k, tail = len - n_full * k;
     const int n_win = n_full + (tail ? 1 : 0);

@@ -48,7 +48,8 @@ extern "C" {
 #define DNATOK_ERR_CAPACITY    (-5)   /* output buffer too small */
 
 /* per-row status bits written to d_status (0 = fine) */
-#define DNATOK_ROW_TOO_LONG       1   /* BPE word longer than DNATOK_BPE_MAX_WORD; row left empty */
+#define DNATOK_ROW_TOO_LONG       1   /* BPE word longer than DNATOK_BPE_MAX_WORD: row left empty; k-mer row of 2 GiB
+                                         or more: only its first 2^31 - 1 bytes are encoded */
 #define DNATOK_ROW_NOT_CONVERGED  2   /* BPE pass limit reached (cannot happen for a consistent table) */
 #define DNATOK_ROW_CLIPPED        4   /* row had more tokens than out_stride and was cut to fit */
 #define DNATOK_ROW_OUTSIDE_HINT   8   /* BPE row length outside dnatok_set_row_bytes_hint; row left empty */
@@ -239,6 +240,9 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *                           than its length needs); 0 (default): chosen from the batch - the widest team that
  *                           keeps all words resident on half of the GPU and leaves a lane four positions
  *   "bpe_team_max"          widest team the automatic choice takes (default 8)
+ *   "bpe_smem_table"        1 (default): a vocabulary whose packed merge table fits into shared memory beside the
+ *                           words in flight (about 75 KB: vocabularies of a few thousand tokens) is looked up there;
+ *                           0: always in global memory
  *   "bpe_mixed_launch"      1 (default): the rows of all length classes up to 16,384 bytes go through one launch
  *                           whose blocks work from the longest class down; 0: one launch per class
  *   "bpe_block_team_rows"   older switch, kept for tests: batches of at most this many rows use teams of eight

@@ -12,21 +12,24 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.fixture(params=["auto", "warp_teams", "block_teams", "teams_of_2", "teams_of_32", "launch_per_class"])
+@pytest.fixture(params=["auto", "warp_teams", "block_teams", "teams_of_2", "teams_of_32", "launch_per_class", "table_in_global"])
 def bpe_team_mode(request):
     """Run a BPE test under each way of assigning warps to words (small batches would otherwise only
     ever see the wide-team kernels), and with one launch per length class instead of the shared one."""
     from dnatok_b200 import _cabi
     L = _cabi.lib()
-    rows, warps, mixed = {"auto": (-1, 0, 1), "warp_teams": (0, 0, 1), "block_teams": (1 << 40, 0, 1),
-                          "teams_of_2": (-1, 2, 1), "teams_of_32": (-1, 32, 1), "launch_per_class": (-1, 0, 0)}[request.param]
+    rows, warps, mixed, smem = {"auto": (-1, 0, 1, 1), "warp_teams": (0, 0, 1, 1), "block_teams": (1 << 40, 0, 1, 1),
+                                "teams_of_2": (-1, 2, 1, 1), "teams_of_32": (-1, 32, 1, 1), "launch_per_class": (-1, 0, 0, 1),
+                                "table_in_global": (-1, 0, 0, 0)}[request.param]
     _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", rows))
     _cabi.check(L.dnatok_set_option(b"bpe_team_warps", warps))
     _cabi.check(L.dnatok_set_option(b"bpe_mixed_launch", mixed))
+    _cabi.check(L.dnatok_set_option(b"bpe_smem_table", smem))
     yield request.param
     _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", -1))
     _cabi.check(L.dnatok_set_option(b"bpe_team_warps", 0))
     _cabi.check(L.dnatok_set_option(b"bpe_mixed_launch", 1))
+    _cabi.check(L.dnatok_set_option(b"bpe_smem_table", 1))
 
 
 @pytest.fixture(scope="module")
@@ -821,3 +824,9 @@ def test_fused_embedding_gather(toks, name, dim, dtype):
             want = weight[torch.from_numpy(o_ids).cuda()]
             assert torch.equal(got["embeddings"], want)
             assert torch.equal(got["lengths"], ref["lengths"])
+    # a weight matrix that lacks a row for some id the tokenizer can produce is refused, not patched over
+    from dnatok_b200 import _cabi
+    top = int(max(max(tok.spec.lut256), tok.spec.specials.cls_id, tok.spec.specials.sep_id))
+    short = weight[:top].contiguous()
+    with pytest.raises(_cabi.DnatokError, match="weight matrix"):
+        tok.embed_device(d_b, d_o, short, host_offsets=offs, padding="longest")
