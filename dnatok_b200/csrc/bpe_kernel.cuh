@@ -179,6 +179,13 @@ struct BpeLengths {
     int64_t cap_content;     // most content tokens a row may keep
     int32_t n_special;
     int32_t clip_is_error;   // rows cut by the output width (not by requested truncation) get DNATOK_ROW_CLIPPED
+    // When ids is set the merge kernels also write every finished row in its final padded layout ([CLS] tokens
+    // [SEP] padding, or the padding first), so no output pass follows; otherwise the tokens go to the scratch buffer.
+    void* ids;
+    void* mask;              // may be NULL
+    int64_t out_stride;
+    int32_t cls_id, sep_id, pad_id, pad_left;
+    int32_t id_bits, mask_bits;
 };
 __device__ __forceinline__ void bpe_put_length(const BpeLengths& L, int32_t* status, int64_t row, int64_t n) {
     if (!L.lengths) return;
@@ -186,6 +193,35 @@ __device__ __forceinline__ void bpe_put_length(const BpeLengths& L, int32_t* sta
     L.lengths[row] = (int32_t)kept + L.n_special;
     if (status && L.clip_is_error && n > kept) atomicOr(status + row, 4);
 }
+
+// One finished row of n tokens into the caller's padded layout, the columns dealt to the T threads that worked on
+// the row (g: this thread's index among them); tok(i) returns token i.
+template <typename TokFn>
+__device__ __forceinline__ void bpe_write_row(const BpeLengths& L, int64_t row, int n, int g, int T, TokFn tok) {
+    const int stride = (int)L.out_stride;
+    const int kept = n < L.cap_content ? n : (int)L.cap_content;
+    const bool has_cls = L.cls_id >= 0, has_sep = L.sep_id >= 0;
+    const int total = kept + (has_cls ? 1 : 0) + (has_sep ? 1 : 0);
+    const int c0 = (L.pad_left ? stride - total : 0) + (has_cls ? 1 : 0);     // column of the first content token
+    const int64_t base = row * L.out_stride;
+    for (int col = g; col < stride; col += T) {
+        const int i = col - c0;
+        int32_t v = L.pad_id;
+        bool on = true;
+        if (i >= 0 && i < kept) v = (int32_t)tok(i);
+        else if (i == -1 && has_cls) v = L.cls_id;
+        else if (i == kept && has_sep) v = L.sep_id;
+        else on = false;
+        if (L.id_bits == 64) reinterpret_cast<int64_t*>(L.ids)[base + col] = v;
+        else reinterpret_cast<int32_t*>(L.ids)[base + col] = v;
+        if (L.mask) {
+            if (L.mask_bits == 64) reinterpret_cast<int64_t*>(L.mask)[base + col] = on;
+            else if (L.mask_bits == 32) reinterpret_cast<int32_t*>(L.mask)[base + col] = on;
+            else reinterpret_cast<uint8_t*>(L.mask)[base + col] = on;
+        }
+    }
+}
+
 
 // Bin rows by length: class_count[c] rows land in class_list[c * n_rows ...].  One atomic per
 // warp and class (rows of a batch mostly share a class).  Classes outside class_mask are not
@@ -206,7 +242,10 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
             if (n > BPE_MAX_POSITIONS) { if (status) atomicOr(status + i, 1); c = -1; }
             else if (!((class_mask >> c) & 1u)) { if (status) atomicOr(status + i, 8); c = -1; }   // outside the caller's length hint
         }
-        if (c < 0) bpe_put_length(len_out, nullptr, i, 0);        // no kernel will visit this row
+        if (c < 0) {                                              // no kernel will visit this row
+            bpe_put_length(len_out, nullptr, i, 0);
+            if (len_out.ids) bpe_write_row(len_out, i, 0, 0, 1, [](int) { return 0u; });
+        }
     }
     for (int k = 0; k < BPE_N_CLASSES; ++k) {
         const uint32_t m = __ballot_sync(0xffffffffu, c == k);
@@ -367,6 +406,7 @@ __device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, const B
                 bpe_put_length(len_out, nullptr, row, 0);
                 if (n64 > 0 && status) atomicOr(status + row, 8);
             }
+            if (len_out.ids) bpe_write_row(len_out, row, 0, g, T, [](int) { return 0u; });
             team_sync<W, BW, BAR0>(team);                          // everybody has read the claimed index
             continue;
         }
@@ -615,9 +655,17 @@ __device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, const B
             n = n_new; Pp = Pn; inv = inv_n;
         }
 
-        for (int q = g; q < n; q += T) {
-            const uint32_t l = __umulhi(2u * (uint32_t)q + 1u, inv);
-            out_tok[off + q] = (uint16_t)lds_u16(cur - 2 * g + 2 * (((uint32_t)q - l * Pp) * STRIDE + l));
+        if (len_out.ids) {
+            const uint32_t col0 = cur - 2 * g;               // the team's buffer
+            bpe_write_row(len_out, row, n, g, T, [&](int q) {
+                const uint32_t l = __umulhi(2u * (uint32_t)q + 1u, inv);
+                return lds_u16(col0 + 2 * (((uint32_t)q - l * Pp) * STRIDE + l));
+            });
+        } else {
+            for (int q = g; q < n; q += T) {
+                const uint32_t l = __umulhi(2u * (uint32_t)q + 1u, inv);
+                out_tok[off + q] = (uint16_t)lds_u16(cur - 2 * g + 2 * (((uint32_t)q - l * Pp) * STRIDE + l));
+            }
         }
         if (g == 0) {
             counts[row] = n;
@@ -878,6 +926,7 @@ bpe_long_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ o
             n = n_new;
         }
 
+        if (len_out.ids) bpe_write_row(len_out, row, n, tt, W * 32, [&](int q) { return (uint32_t)tok[q]; });
         if (tt == 0) {
             counts[row] = n;
             bpe_put_length(len_out, status, row, n);

@@ -39,6 +39,7 @@ std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below th
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
 std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
+std::atomic<int64_t> g_bpe_fused_output{1};                  // BPE, padded layout through dnatok_encode: merge kernels write the final rows
 std::atomic<int64_t> g_bpe_mixed{1};                         // BPE: batches of several length classes in one launch
 std::atomic<int64_t> g_bpe_block_team_rows{-1};              // BPE: batches up to this many rows use a block per word; -1: 8 per SM
 
@@ -382,9 +383,12 @@ int bpe_team_width(const DeviceTables& d, const BpeLaunchInfo& li, int64_t n_row
 }
 
 // lengths (may be NULL) receives every row's final token count for the format rf.
+// ids (may be NULL): when given and the layout is padded, the merge kernels write the final ids and mask
+// themselves and no output pass is needed afterwards.
 int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
                   int64_t n_rows, int64_t total_bytes, int32_t* status, void* scratch, size_t scratch_bytes,
-                  const RowFormat& rf, int32_t* lengths, cudaStream_t st) {
+                  const RowFormat& rf, int32_t* lengths, cudaStream_t st, void* ids = nullptr, void* mask = nullptr,
+                  int id_bits = 0) {
     if (!scratch) return fail(DNATOK_ERR_SCRATCH, "BPE needs a scratch buffer (dnatok_scratch_bytes)");
     if (reinterpret_cast<uintptr_t>(scratch) & 255) return fail(DNATOK_ERR_SCRATCH, "scratch must be 256-byte aligned");
     BpeScratch s = bpe_scratch_layout(h, scratch, n_rows, total_bytes);
@@ -409,7 +413,9 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
         max_row = hi;
     }
     if (((class_mask >> BPE_LONG_CLASS) & 1u) && !s.long_bytes) class_mask &= ~(1u << BPE_LONG_CLASS);
-    const BpeLengths lo{lengths, rf.cap_content, (rf.cls_id >= 0 ? 1 : 0) + (rf.sep_id >= 0 ? 1 : 0), rf.clip_is_error};
+    const BpeLengths lo{lengths, rf.cap_content, (rf.cls_id >= 0 ? 1 : 0) + (rf.sep_id >= 0 ? 1 : 0), rf.clip_is_error,
+                        ids, rf.mask_bits ? mask : nullptr, rf.out_stride, rf.cls_id, rf.sep_id, rf.pad_id, rf.pad_left,
+                        id_bits, rf.mask_bits};
     // One class only, by the caller's bounds on the row lengths: the rows need no binning, the class's kernel
     // takes them as they come (and flags a row the bounds misstated).
     const bool direct = h->hint_max_row > 0 && (class_mask & (class_mask - 1)) == 0 && !((class_mask >> BPE_LONG_CLASS) & 1u);
@@ -808,6 +814,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
+    if (!strcmp(name, "bpe_fused_output")) { g_bpe_fused_output = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_mixed_launch")) { g_bpe_mixed = value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_min_bytes")) { g_host_mask_min_bytes = value < 0 ? 0 : value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_threads")) { g_host_mask_threads = value < -1 ? -1 : value; return DNATOK_OK; }
@@ -1036,6 +1043,14 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     RowFormat rf;
     if (int rc = resolve(h, fmt, fmt->out_stride, &rf)) return rc;
 
+    if (h->kind == DNATOK_KIND_BPE && !ragged && g_bpe_fused_output.load() && fmt->out_stride < 0x7fffffff) {
+        // padded BPE output: the merge kernels write ids and mask in their final layout
+        if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
+        if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
+        if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
+        return run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, rf, d_lengths,
+                             st, d_ids, d_mask, fmt->id_bits);
+    }
     const bool need_prepare = ragged || h->kind == DNATOK_KIND_BPE ||
                               (h->kind == DNATOK_KIND_KMER && fmt->pad_left);
     if (need_prepare) {

@@ -243,6 +243,9 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *   "bpe_smem_table"        1 (default): a vocabulary whose packed merge table fits into shared memory beside the
  *                           words in flight (about 75 KB: vocabularies of a few thousand tokens) is looked up there;
  *                           0: always in global memory
+ *   "bpe_fused_output"      1 (default): dnatok_encode with a padded layout lets the BPE merge kernels write ids and
+ *                           mask in their final place (one launch for a batch of one length class); 0: merged tokens
+ *                           go to the scratch buffer and an output pass follows, as dnatok_prepare + dnatok_write do
  *   "bpe_mixed_launch"      1 (default): the rows of all length classes up to 16,384 bytes go through one launch
  *                           whose blocks work from the longest class down; 0: one launch per class
  *   "bpe_block_team_rows"   older switch, kept for tests: batches of at most this many rows use teams of eight

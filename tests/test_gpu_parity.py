@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.fixture(params=["auto", "warp_teams", "block_teams", "teams_of_2", "teams_of_32", "launch_per_class", "table_in_global"])
+@pytest.fixture(params=["auto", "warp_teams", "block_teams", "teams_of_2", "teams_of_32", "launch_per_class", "table_in_global", "separate_output_pass"])
 def bpe_team_mode(request):
     """Run a BPE test under each way of assigning warps to words (small batches would otherwise only
     ever see the wide-team kernels), and with one launch per length class instead of the shared one."""
@@ -20,7 +20,8 @@ def bpe_team_mode(request):
     L = _cabi.lib()
     rows, warps, mixed, smem = {"auto": (-1, 0, 1, 1), "warp_teams": (0, 0, 1, 1), "block_teams": (1 << 40, 0, 1, 1),
                                 "teams_of_2": (-1, 2, 1, 1), "teams_of_32": (-1, 32, 1, 1), "launch_per_class": (-1, 0, 0, 1),
-                                "table_in_global": (-1, 0, 0, 0)}[request.param]
+                                "table_in_global": (-1, 0, 0, 0), "separate_output_pass": (-1, 0, 1, 1)}[request.param]
+    _cabi.check(L.dnatok_set_option(b"bpe_fused_output", 0 if request.param == "separate_output_pass" else 1))
     _cabi.check(L.dnatok_set_option(b"bpe_block_team_rows", rows))
     _cabi.check(L.dnatok_set_option(b"bpe_team_warps", warps))
     _cabi.check(L.dnatok_set_option(b"bpe_mixed_launch", mixed))
@@ -30,6 +31,7 @@ def bpe_team_mode(request):
     _cabi.check(L.dnatok_set_option(b"bpe_team_warps", 0))
     _cabi.check(L.dnatok_set_option(b"bpe_mixed_launch", 1))
     _cabi.check(L.dnatok_set_option(b"bpe_smem_table", 1))
+    _cabi.check(L.dnatok_set_option(b"bpe_fused_output", 1))
 
 
 @pytest.fixture(scope="module")
