@@ -337,11 +337,53 @@ def pcie_probe(mb=256, reps=5):
 
     run(True, True)
     t_in, t_out, t_both = run(True, False), run(False, True), run(True, True)
+
+    # the host's own memory beside the link: T threads copying between ordinary arrays (numpy releases the
+    # interpreter lock), alone and while both link copies run.  A copy of x bytes reads x and writes x.
+    import threading
+    T = min(16, len(os.sched_getaffinity(0)))
+    src = np.ones(n, dtype=np.uint8)
+    dst = np.empty(n, dtype=np.uint8)
+    cuts = [n * i // T for i in range(T + 1)]
+
+    def host_copy(stop_at):
+        done = [0] * T
+
+        def work(i):
+            while time.perf_counter() < stop_at:
+                np.copyto(dst[cuts[i]:cuts[i + 1]], src[cuts[i]:cuts[i + 1]])
+                done[i] += cuts[i + 1] - cuts[i]
+        th = [threading.Thread(target=work, args=(i,)) for i in range(T)]
+        for t in th:
+            t.start()
+        return th, done
+
+    window = 0.25
+    t0 = time.perf_counter()
+    th, done = host_copy(t0 + window)
+    for t in th:
+        t.join()
+    copy_alone = sum(done) / (time.perf_counter() - t0)
+    t0 = time.perf_counter()
+    th, done = host_copy(t0 + window)
+    link_bytes = 0
+    while time.perf_counter() < t0 + window:
+        run(True, True)
+        link_bytes += 2 * n * reps
+    t_link = time.perf_counter() - t0
+    for t in th:
+        t.join()
+    t_all = time.perf_counter() - t0
     print(json.dumps({"probe": "pcie", "mb_each_way": mb, "h2d_GB/s": round(n / t_in / 1e9, 1),
                       "d2h_GB/s": round(n / t_out / 1e9, 1), "both_ms": round(t_both * 1e3, 2),
                       "serial_ms": round((t_in + t_out) * 1e3, 2),
                       "duplex_GB/s_total": round(2 * n / t_both / 1e9, 1),
-                      "duplex_over_serial": round((t_in + t_out) / t_both, 2)}))
+                      "duplex_over_serial": round((t_in + t_out) / t_both, 2),
+                      "host_copy_threads": T, "host_copy_alone_GB/s": round(copy_alone / 1e9, 1),
+                      "with_both_link_copies": {"link_GB/s_total": round(link_bytes / t_link / 1e9, 1),
+                                                "host_copy_GB/s": round(sum(done) / t_all / 1e9, 1)},
+                      "note": "host_copy figures are bytes copied per second; the memory traffic is twice that "
+                              "(three times with the write-allocate reads)"}))
 
 
 def peaks():
