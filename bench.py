@@ -465,7 +465,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
                      "kernel": {"kmer6": "kmer_warp_rows_kernel", "char": "emit_padded_kernel", "byte": "emit_padded_kernel",
-                                "bpe4k": "bpe_rounds_kernel", "bpe32k": "bpe_rounds_kernel"}[kind],
+                                "bpe4k": "bpe_lanes_st_kernel", "bpe32k": "bpe_mixed_kernel"}[kind],
                      "algorithmic_bytes_per_launch": abytes, "kernel_ms": round(kernel_ms, 5)},
         "e2e": {"value": round(world * total_bp / e2e_s / 1e6, 1), "unit": "Mbp/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
@@ -567,7 +567,7 @@ def strong_scaling(local, rank, world, peak):
 
 # dram bytes per launch of the dominant kernel from the committed ncu summaries (profiles/), scaled to
 # the default workload where the capture ran on a smaller case; None until a capture exists.
-TRAFFIC = {"kmer6": 667.5e6, "char": 1085.3e6}
+TRAFFIC = {"kmer6": 669.1e6, "char": 1085.3e6}
 
 
 def per_config(local, peak, args):
