@@ -711,6 +711,14 @@ bpe_lanes_st_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict
     bpe_lanes_setup<BPE_ST_WARPS>(sh, t);                     // ends with a block-wide barrier
     const uint32_t base = smem_u32(tab);
     const BpeSmemTable stab{base, base + t.compact_slot, base + t.compact_info, t.compact_last};
+    {
+        // A small batch is spread over all blocks: only as many teams of a block take part as the words per
+        // block ask for (words are claimed from one counter, and the blocks that start first would otherwise
+        // take them all while other SMs stay idle).
+        const int n_words = list ? *list_count : n_direct;
+        const int active = (n_words + (int)gridDim.x - 1) / (int)gridDim.x;
+        if ((int)(threadIdx.x >> 5) / W >= active) return;
+    }
     // sixteen teams of two warps need sixteen hardware barriers: barrier 0 is theirs as well once the set-up is over
     bpe_lanes_body<W, BPE_ST_WARPS, (W == 2 ? 0 : 1), (int)bpe_team_bytes(W), true>(sh, stab, reinterpret_cast<uint16_t*>(bpe_dyn), bytes,
                                                                      offsets, list, list ? *list_count : n_direct, work_counter,

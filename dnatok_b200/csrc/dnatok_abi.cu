@@ -325,9 +325,8 @@ int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDe
     if (t.compact && g_bpe_smem_table.load() && t.compact_bytes <= (uint32_t)li.st_room[WI]) {
         // the whole merge table fits into shared memory beside the teams: one block of 32 warps per SM
         constexpr int ST_TEAMS = BPE_ST_WARPS / W;
-        int64_t grid = d.sm_count;
-        const int64_t need = (n_rows + ST_TEAMS - 1) / ST_TEAMS;
-        if (grid > need) grid = need;
+        int64_t grid = d.sm_count;                          // every SM takes part, however few the words (the kernel
+        if (grid > n_rows) grid = n_rows;                    // lets only as many of a block's teams work as are needed)
         if (grid < 1) grid = 1;
         bpe_lanes_st_kernel<W><<<(unsigned)grid, BPE_ST_WARPS * 32, bpe_st_team_area(W) + t.compact_bytes, st>>>(
             bytes, offsets, direct ? nullptr : s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
