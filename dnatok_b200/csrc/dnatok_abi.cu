@@ -38,8 +38,6 @@ std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the h
 std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
-std::atomic<int64_t> g_kmer_team_rows{0};                    // k-mer: 1 a block of warps per row, 0 a warp per row, -1 by row length
-constexpr int64_t KTEAM_MIN_ROW_BYTES = 2048;
 std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
 std::atomic<int64_t> g_bpe_fused_output{1};                  // BPE, padded layout through dnatok_encode: merge kernels write the final rows
 std::atomic<int64_t> g_bpe_mixed{1};                         // BPE: batches of several length classes in one launch
@@ -538,19 +536,6 @@ void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_
     const bool fuse = mask && rf.mask_bits == (int)sizeof(IdT) * 8 &&
                       ((reinterpret_cast<uintptr_t>(mask) ^ reinterpret_cast<uintptr_t>(ids)) & 15) == 0;
     const bool affine = affine_base >= 0;
-    const int64_t team = g_kmer_team_rows.load();
-    if (team > 0 || (team < 0 && n_rows <= 0x7fffffff && total_bytes / n_rows >= KTEAM_MIN_ROW_BYTES)) {
-        // a block of warps per row: short row latency, so the last rows of the launch drain quickly
-#define KLAUNCH(A, F) kmer_team_rows_kernel<IdT, K, A, F><<<(unsigned)n_rows, KTEAM_WARPS * 32, 0, st>>>(                     \
-        bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
-        lengths_out, out_offsets, status)
-        if (affine && fuse) KLAUNCH(true, true);
-        else if (affine) KLAUNCH(true, false);
-        else if (fuse) KLAUNCH(false, true);
-        else KLAUNCH(false, false);
-#undef KLAUNCH
-        return;
-    }
 #define KLAUNCH(A, F) kmer_warp_rows_kernel<IdT, K, A, F><<<grid, KW_ROW_WARPS * 32, 0, st>>>(                                \
         bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
         lengths_out, out_offsets, status)
@@ -830,7 +815,6 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
-    if (!strcmp(name, "kmer_team_rows")) { g_kmer_team_rows = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_fused_output")) { g_bpe_fused_output = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_mixed_launch")) { g_bpe_mixed = value; return DNATOK_OK; }
