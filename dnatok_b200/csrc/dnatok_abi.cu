@@ -38,6 +38,7 @@ std::atomic<int64_t> g_host_chunk_bytes{64ll << 20};         // bytes over the h
 std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below this size are not chunked
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
+std::atomic<int64_t> g_kmer_overlap_launch{1};               // k-mer row kernel launched with programmatic stream serialisation
 std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
 std::atomic<int64_t> g_bpe_fused_output{1};                  // BPE, padded layout through dnatok_encode: merge kernels write the final rows
 std::atomic<int64_t> g_bpe_mixed{1};                         // BPE: batches of several length classes in one launch
@@ -536,9 +537,22 @@ void launch_kmer_warp_k(const DeviceTables& d, int32_t affine_base, const uint8_
     const bool fuse = mask && rf.mask_bits == (int)sizeof(IdT) * 8 &&
                       ((reinterpret_cast<uintptr_t>(mask) ^ reinterpret_cast<uintptr_t>(ids)) & 15) == 0;
     const bool affine = affine_base >= 0;
-#define KLAUNCH(A, F) kmer_warp_rows_kernel<IdT, K, A, F><<<grid, KW_ROW_WARPS * 32, 0, st>>>(                                \
-        bytes, offsets, n_rows, total_bytes, d.kmer_ids, affine_base, d.lut256, rf, (IdT*)ids, mask, lengths_in,    \
-        lengths_out, out_offsets, status)
+    // Programmatic stream serialisation: the kernel's blocks may be placed on the SMs while the launch before it
+    // in the stream drains; they wait (griddepcontrol.wait) until that launch is complete before they touch memory.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(KW_ROW_WARPS * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_kmer_overlap_launch.load() ? 1 : 0;
+    const int32_t* kmer_ids = d.kmer_ids;
+    const int32_t* singles = d.lut256;
+    IdT* ids_t = (IdT*)ids;
+#define KLAUNCH(A, F) cudaLaunchKernelEx(&cfg, kmer_warp_rows_kernel<IdT, K, A, F>, bytes, offsets, n_rows, total_bytes, kmer_ids,    \
+                                         affine_base, singles, rf, ids_t, mask, lengths_in, lengths_out, out_offsets, status)
     if (affine && fuse) KLAUNCH(true, true);
     else if (affine) KLAUNCH(true, false);
     else if (fuse) KLAUNCH(false, true);
@@ -815,6 +829,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_block_team_rows")) { g_bpe_block_team_rows = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
+    if (!strcmp(name, "kmer_overlap_launch")) { g_kmer_overlap_launch = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_fused_output")) { g_bpe_fused_output = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_mixed_launch")) { g_bpe_mixed = value; return DNATOK_OK; }

@@ -189,10 +189,12 @@ namespace dnatok {
 
 constexpr int KW_WARPS = 8;
 // Row-per-warp encoder: two rows (warps) per block, because a block's slot is only refilled when its slowest
-// row is done (rows with N runs take longer); 24 such blocks per SM, i.e. 65,536 / (24 * 64) = 42 registers
-// per thread at most.
+// row is done (rows with N runs take longer); 16 such blocks per SM (32 warps, up to 64 registers per thread):
+// the long loop keeps the words of four chunks in flight per lane, which pays more than a third more warps
+// with half the loads each.
 constexpr int KW_ROW_WARPS = 2;
-constexpr int KW_BLOCKS_PER_SM = 24;
+constexpr int KW_BLOCKS_PER_SM = 16;
+constexpr int KW_TRIP_CHUNKS = 4;       // clean chunks of 64 windows per trip of the long loop
 
 // 2-bit codes of four ASCII bytes at once (A C G T -> 0 1 2 3 in each byte's low bits), and a word
 // that is zero exactly in the bytes that are one of A, C, G, T.
@@ -508,6 +510,29 @@ __device__ __forceinline__ int kmer_encode_windows(const KmerRow<IdT>& r, int ca
             const uint32_t sh = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u) * 8u;   // constant while w moves by 64: 64K % 4 == 0
             const uint32_t* gw = reinterpret_cast<const uint32_t*>(g - (sh >> 3));
             IdT* d = dst + base + 2 * lane;
+            // KW_TRIP_CHUNKS clean chunks per trip while they last: more loads in flight per wait
+            {
+                constexpr int NCH = KW_TRIP_CHUNKS;
+                while (w + 64 * NCH <= n_tight && base + 64 * NCH <= cap) {
+                    uint32_t q[NCH][NW];
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) load_words(gw + i * 16 * K, q[i]);
+                    uint32_t ia[NCH], ib[NCH], bad = 0;
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) bad |= decode_words(q[i], sh, &ia[i], &ib[i]);
+                    if (__any_sync(0xffffffffu, bad != 0)) { dirty = true; break; }   // the two-chunk loop below sorts it out
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        Pair v;
+                        v.x = (IdT)(AFFINE ? affine_base + (int32_t)ia[i] : __ldg(kmer_ids + ia[i]));
+                        v.y = (IdT)(AFFINE ? affine_base + (int32_t)ib[i] : __ldg(kmer_ids + ib[i]));
+                        *reinterpret_cast<Pair*>(d + 64 * i) = v;
+                        if (FUSE_MASK) *reinterpret_cast<Pair*>(d + mdelta + 64 * i) = one;
+                    }
+                    gw += NCH * 16 * K; d += 64 * NCH; base += 64 * NCH; w += 64 * NCH;
+                }
+                dirty = false;                                    // the loops below look again
+            }
             while (w + 128 <= n_tight && base + 128 <= cap) {
                 uint32_t c0[NW], c1[NW];
                 load_words(gw, c0);
@@ -610,6 +635,10 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                       void* __restrict__ mask, const int32_t* __restrict__ lengths_in,
                       int32_t* __restrict__ lengths_out, const int64_t* __restrict__ out_offsets,
                       int32_t* __restrict__ status) {
+    // Launched with programmatic stream serialisation: the next launch of the stream may be set up while this grid
+    // drains, and this grid starts its work only once everything before it in the stream is complete and visible.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * KW_ROW_WARPS + (threadIdx.x >> 5);
     if (row >= n_rows) return;
