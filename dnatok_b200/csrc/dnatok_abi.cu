@@ -5,6 +5,8 @@
 
 #include <atomic>
 #include <climits>
+#include <condition_variable>
+#include <functional>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -97,6 +99,7 @@ struct DeviceTables {
     std::vector<cudaEvent_t> pipe_events;
     void* st_pipe_rows = nullptr; size_t st_pipe_rows_cap = 0;    // lengths then status, int32 each
     int64_t* h_offsets = nullptr; size_t h_offsets_cap = 0;
+    int32_t* h_rows = nullptr; size_t h_rows_cap = 0;   // pinned: row lengths and status on their way back (2 x n_rows)
 };
 
 }  // namespace
@@ -759,6 +762,60 @@ template <typename M> inline void put_once(M* p, M v) { *p = v; }
 inline void put_once_done() {}
 #endif
 
+// Host workers that outlive a call: starting a thread and giving it the device's context costs far more than
+// writing its share of a mask, so the threads are started once and handed jobs.  run(n, fn) calls fn(0) on the
+// calling thread and fn(1) .. fn(n - 1) on workers, and returns when all are done.  One job at a time.
+class HostPool {
+public:
+    static HostPool& get() {
+        static HostPool* pool = new HostPool();      // never destroyed: the workers sleep until the process ends
+        return *pool;
+    }
+    void run(int n, const std::function<void(int)>& fn) {
+        if (n <= 1) { fn(0); return; }
+        std::lock_guard<std::mutex> one_job(job_mu_);
+        {
+            std::unique_lock<std::mutex> lk(mu_);
+            while ((int)threads_.size() < n - 1) {
+                const int id = (int)threads_.size() + 1;
+                threads_.emplace_back([this, id] { loop(id); });
+            }
+            fn_ = &fn; want_ = n; pending_ = n - 1; ++generation_;
+        }
+        cv_.notify_all();
+        fn(0);
+        std::unique_lock<std::mutex> lk(mu_);
+        done_.wait(lk, [this] { return pending_ == 0; });
+        fn_ = nullptr;
+    }
+
+private:
+    void loop(int id) {
+        uint64_t seen = 0;
+        for (;;) {
+            const std::function<void(int)>* fn;
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return generation_ != seen; });
+                seen = generation_;
+                if (id >= want_) continue;           // this job needs fewer workers
+                fn = fn_;
+            }
+            (*fn)(id);
+            {
+                std::lock_guard<std::mutex> lk(mu_);
+                if (--pending_ == 0) done_.notify_one();
+            }
+        }
+    }
+    std::mutex mu_, job_mu_;
+    std::condition_variable cv_, done_;
+    std::vector<std::thread> threads_;
+    const std::function<void(int)>* fn_ = nullptr;
+    int want_ = 0, pending_ = 0;
+    uint64_t generation_ = 0;
+};
+
 template <typename M>
 void fill_mask_rows(M* mask, const int32_t* lengths, int64_t r0, int64_t r1, int64_t stride, bool pad_left) {
     for (int64_t r = r0; r < r1; ++r) {
@@ -772,6 +829,18 @@ void fill_mask_rows(M* mask, const int32_t* lengths, int64_t r0, int64_t r1, int
         for (int64_t j = lo + T; j < stride; ++j) put_once(row + j, (M)0);
     }
     put_once_done();
+}
+
+// Pinned landing place for row lengths and status words: a copy to the caller's arrays, which are ordinary memory
+// as a rule, would block the calling thread until everything before it in the stream is done.
+int pinned_rows(DeviceTables* d, int64_t n_rows) {
+    const size_t need = (size_t)n_rows * 8 + 64;
+    if (need <= d->h_rows_cap) return 0;
+    if (d->h_rows) CUDA_TRY(cudaFreeHost(d->h_rows));
+    d->h_rows = nullptr; d->h_rows_cap = 0;
+    CUDA_TRY(cudaMallocHost((void**)&d->h_rows, need + 65536));
+    d->h_rows_cap = need + 65536;
+    return 0;
 }
 
 // The attention mask of a large padded batch, written by n_threads host workers once the row lengths
@@ -794,11 +863,7 @@ int host_mask_fill(const HostMask& hm, int n_threads) {
     if (n_threads > hm.n_rows) n_threads = (int)hm.n_rows;
     if (n_threads < 1) n_threads = 1;
     std::vector<int> errs((size_t)n_threads, 0);
-    std::vector<std::thread> pool;
-    pool.reserve((size_t)n_threads);
-    for (int t = 1; t < n_threads; ++t) pool.emplace_back(host_mask_worker, std::cref(hm), t, n_threads, &errs[(size_t)t]);
-    host_mask_worker(hm, 0, n_threads, &errs[0]);
-    for (auto& th : pool) th.join();
+    HostPool::get().run(n_threads, [&](int t) { host_mask_worker(hm, t, n_threads, &errs[(size_t)t]); });
     for (int e : errs) if (e) return fail(DNATOK_ERR_CUDA, "a host worker could not wait for the row lengths");
     return 0;
 }
@@ -954,6 +1019,7 @@ void dnatok_destroy(dnatok_handle* h) {
         for (auto ev : d.pipe_events) cudaEventDestroy(ev);
         if (d.st_pipe_rows) cudaFree(d.st_pipe_rows);
         if (d.h_offsets) cudaFreeHost(d.h_offsets);
+        if (d.h_rows) cudaFreeHost(d.h_rows);
     }
     if (!h->dev.empty()) cudaSetDevice(cur);
     delete h;
@@ -1307,9 +1373,9 @@ static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, 
 
     int32_t* d_len_all = (int32_t*)d->st_pipe_rows;
     int32_t* d_st_all = d_len_all + n_rows;
-    std::vector<int32_t> tmp_len;
-    int32_t* hl = h_lengths;
-    if (host_mask && !hl) { tmp_len.resize((size_t)n_rows); hl = tmp_len.data(); }
+    if (int rc = pinned_rows(d, n_rows)) return rc;
+    int32_t* hl = d->h_rows;                                   // lengths land here, status words behind them
+    int32_t* hs = d->h_rows + n_rows;
     for (int64_t c = 0; c < n_chunks; ++c) {
         const int64_t r0 = c * rows_per_chunk, r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
         const int64_t rows = r1 - r0, b0 = h_offsets[r0], nbytes = h_offsets[r1] - b0;
@@ -1326,8 +1392,8 @@ static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, 
                                    scratch_total ? (uint8_t*)d->st_scratch + scratch_at[(size_t)c] : nullptr,
                                    scratch_at[(size_t)c + 1] - scratch_at[(size_t)c], st))
             return rc;
-        if (hl) CUDA_TRY(cudaMemcpyAsync(hl + r0, d_len_all + r0, (size_t)rows * 4, cudaMemcpyDeviceToHost, st));
-        if (h_status) CUDA_TRY(cudaMemcpyAsync(h_status + r0, d_st_all + r0, (size_t)rows * 4, cudaMemcpyDeviceToHost, st));
+        CUDA_TRY(cudaMemcpyAsync(hl + r0, d_len_all + r0, (size_t)rows * 4, cudaMemcpyDeviceToHost, st));
+        if (h_status) CUDA_TRY(cudaMemcpyAsync(hs + r0, d_st_all + r0, (size_t)rows * 4, cudaMemcpyDeviceToHost, st));
         CUDA_TRY(cudaEventRecord(d->pipe_events[(size_t)c], st));
         CUDA_TRY(cudaMemcpyAsync((uint8_t*)h_ids + (size_t)(r0 * stride) * id_sz, dids, (size_t)(rows * stride) * id_sz,
                                  cudaMemcpyDeviceToHost, st));
@@ -1336,7 +1402,7 @@ static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, 
                                      (size_t)(rows * stride) * mask_sz, cudaMemcpyDeviceToHost, st));
     }
     g_last_h2d = total + (n_rows + n_chunks) * 8;
-    g_last_d2h = n_rows * stride * (int64_t)(id_sz + (host_mask ? 0 : mask_sz)) + (hl ? n_rows * 4 : 0) + (h_status ? n_rows * 4 : 0);
+    g_last_d2h = n_rows * stride * (int64_t)(id_sz + (host_mask ? 0 : mask_sz)) + n_rows * 4 + (h_status ? n_rows * 4 : 0);
     int rc_mask = 0;
     if (host_mask) {
         // every worker takes its stripe of each chunk once that chunk's lengths have arrived
@@ -1353,14 +1419,12 @@ static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, 
                 else fill_mask_rows<uint8_t>((uint8_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
             }
         };
-        std::vector<std::thread> pool;
-        pool.reserve((size_t)nt);
-        for (int t = 1; t < nt; ++t) pool.emplace_back(work, t);
-        work(0);
-        for (auto& th : pool) th.join();
+        HostPool::get().run(nt, work);
         for (int e : errs) if (e) rc_mask = fail(DNATOK_ERR_CUDA, "a host worker could not wait for the row lengths");
     }
     for (auto& st : d->pipe_streams) if (st) CUDA_TRY(cudaStreamSynchronize(st));
+    if (h_lengths) memcpy(h_lengths, hl, (size_t)n_rows * 4);
+    if (h_status) memcpy(h_status, hs, (size_t)n_rows * 4);
     return rc_mask;
 }
 
@@ -1546,11 +1610,11 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
     g_last_d2h = n_out * (int64_t)id_sz + (ragged && h_out_offsets ? (n_rows + 1) * 8 : 0);
     if (host_mask && n_rows) {
         // lengths first (small), then the ids; the mask is filled while the ids are still being copied
-        std::vector<int32_t> tmp;
-        int32_t* hl = h_lengths;
-        if (!hl) { tmp.resize((size_t)n_rows); hl = tmp.data(); }
+        if (int rc2 = pinned_rows(d, n_rows)) return rc2;
+        int32_t* hl = d->h_rows;
+        int32_t* hs = d->h_rows + n_rows;
         CUDA_TRY(cudaMemcpyAsync(hl, d->st_lengths, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
-        if (h_status) CUDA_TRY(cudaMemcpyAsync(h_status, d->st_status, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
+        if (h_status) CUDA_TRY(cudaMemcpyAsync(hs, d->st_status, (size_t)n_rows * 4, cudaMemcpyDeviceToHost, st));
         if (!d->ev_lengths) CUDA_TRY(cudaEventCreateWithFlags(&d->ev_lengths, cudaEventDisableTiming));
         CUDA_TRY(cudaEventRecord(d->ev_lengths, st));
         if (n_out) CUDA_TRY(cudaMemcpyAsync(h_ids, d->st_ids, (size_t)n_out * id_sz, cudaMemcpyDeviceToHost, st));
@@ -1560,6 +1624,8 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
         if (int rc2 = host_mask_fill(hm, mask_threads)) return rc2;
         g_last_d2h += n_rows * 4 * (h_status ? 2 : 1);
         CUDA_TRY(cudaStreamSynchronize(st));
+        if (h_lengths) memcpy(h_lengths, hl, (size_t)n_rows * 4);
+        if (h_status) memcpy(h_status, hs, (size_t)n_rows * 4);
         if (out_stride_used) *out_stride_used = stride;
         return DNATOK_OK;
     }
