@@ -186,12 +186,20 @@ struct BpeLengths {
     int64_t out_stride;
     int32_t cls_id, sep_id, pad_id, pad_left;
     int32_t id_bits, mask_bits;
+    // 1: the caller did not zero the status words: the kernel that sees a row first (the binning pass, or the merge
+    // kernel when rows are not binned) writes the row's word instead of OR-ing into it
+    int32_t store_status;
 };
-__device__ __forceinline__ void bpe_put_length(const BpeLengths& L, int32_t* status, int64_t row, int64_t n) {
-    if (!L.lengths) return;
+// A row's status bits into its word.
+__device__ __forceinline__ void bpe_put_status(int32_t* status, int64_t row, int32_t bits, bool store) {
+    if (!status) return;
+    if (store) status[row] = bits;
+    else if (bits) atomicOr(status + row, bits);
+}
+__device__ __forceinline__ int32_t bpe_put_length(const BpeLengths& L, int64_t row, int64_t n) {
     const int64_t kept = n < L.cap_content ? n : L.cap_content;
-    L.lengths[row] = (int32_t)kept + L.n_special;
-    if (status && L.clip_is_error && n > kept) atomicOr(status + row, 4);
+    if (L.lengths) L.lengths[row] = (int32_t)kept + L.n_special;
+    return (L.clip_is_error && n > kept) ? 4 : 0;            // DNATOK_ROW_CLIPPED
 }
 
 // One finished row of n tokens into the caller's padded layout, the columns dealt to the T threads that worked on
@@ -235,17 +243,19 @@ __global__ void bpe_classify_kernel(const int64_t* __restrict__ offsets, int64_t
     int c = -1;
     if (i < n_rows) {
         const int64_t n = offsets[i + 1] - offsets[i];
+        int32_t bits = 0;
         counts[i] = 0;
         if (n > 0) {
             c = 0;
             while (c < BPE_LONG_CLASS && (int64_t)bpe_class_capacity(c) < n) ++c;
-            if (n > BPE_MAX_POSITIONS) { if (status) atomicOr(status + i, 1); c = -1; }
-            else if (!((class_mask >> c) & 1u)) { if (status) atomicOr(status + i, 8); c = -1; }   // outside the caller's length hint
+            if (n > BPE_MAX_POSITIONS) { bits = 1; c = -1; }
+            else if (!((class_mask >> c) & 1u)) { bits = 8; c = -1; }   // outside the caller's length hint
         }
         if (c < 0) {                                              // no kernel will visit this row
-            bpe_put_length(len_out, nullptr, i, 0);
+            bpe_put_length(len_out, i, 0);
             if (len_out.ids) bpe_write_row(len_out, i, 0, 0, 1, [](int) { return 0u; });
         }
+        bpe_put_status(status, i, bits, len_out.store_status != 0);
     }
     for (int k = 0; k < BPE_N_CLASSES; ++k) {
         const uint32_t m = __ballot_sync(0xffffffffu, c == k);
@@ -381,9 +391,15 @@ __device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, const B
     uint32_t* const xf = reinterpret_cast<uint32_t*>(sm + team_base + 2 * BUF);   // [T] entry of every lane's first pair (W > 1)
     uint32_t* const xl = xf + T;                                                  // [T] entry of every lane's last pair  (W > 1)
 
+    // work_counter == NULL: the batch is a single wave (no more words than teams in the grid), and team k of block b
+    // takes word b + k * blocks, with no counter to claim from (and none to zero before the launch)
+    bool first = true;
     for (;;) {
         int wi;
-        if (W == 1) {
+        if (!work_counter) {
+            wi = first ? (int)blockIdx.x + (int)gridDim.x * team : n_words;
+            first = false;
+        } else if (W == 1) {
             wi = 0;
             if (lane == 0) wi = atomicAdd(work_counter, 1);
             wi = __shfl_sync(BPE_FULL, wi, 0);
@@ -403,8 +419,8 @@ __device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, const B
         if (!list && (n64 < 1 || n64 > direct_limit)) {      // direct rows are not vetted: an empty row, or one the hint misstated
             if (g == 0) {
                 counts[row] = 0;
-                bpe_put_length(len_out, nullptr, row, 0);
-                if (n64 > 0 && status) atomicOr(status + row, 8);
+                bpe_put_length(len_out, row, 0);
+                bpe_put_status(status, row, n64 > 0 ? 8 : 0, len_out.store_status != 0);
             }
             if (len_out.ids) bpe_write_row(len_out, row, 0, g, T, [](int) { return 0u; });
             team_sync<W, BW, BAR0>(team);                          // everybody has read the claimed index
@@ -669,8 +685,8 @@ __device__ __forceinline__ void bpe_lanes_body(const BpeLanesShared& sh, const B
         }
         if (g == 0) {
             counts[row] = n;
-            bpe_put_length(len_out, status, row, n);
-            if (round >= max_rounds && status) atomicOr(status + row, 2);
+            const int32_t bits = bpe_put_length(len_out, row, n) | (round >= max_rounds ? 2 : 0);
+            bpe_put_status(status, row, bits, len_out.store_status != 0 && !list);   // binned rows were written by the binning pass
         }
         team_sync<W, BW, BAR0>(team);
     }
@@ -704,6 +720,10 @@ bpe_lanes_st_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict
                     int32_t* __restrict__ work_counter, BpeDeviceTable t,
                     uint16_t* __restrict__ out_tok, int32_t* __restrict__ counts,
                     int32_t* __restrict__ status, BpeLengths len_out, int32_t n_direct, int32_t direct_limit) {
+    // Launched with programmatic stream serialisation when the launch before it in the stream may be a kernel: this
+    // grid's blocks can be placed while that one drains, and wait here until it is complete and visible.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ uint4 bpe_dyn[];
     BPE_LANES_SHARED(BPE_ST_WARPS, sh);
     uint4* const tab = bpe_dyn + bpe_st_team_area(W) / 16;
@@ -937,8 +957,8 @@ bpe_long_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restrict__ o
         if (len_out.ids) bpe_write_row(len_out, row, n, tt, W * 32, [&](int q) { return (uint32_t)tok[q]; });
         if (tt == 0) {
             counts[row] = n;
-            bpe_put_length(len_out, status, row, n);
-            if (round >= max_rounds && status) atomicOr(status + row, 2);
+            const int32_t bits = bpe_put_length(len_out, row, n) | (round >= max_rounds ? 2 : 0);
+            bpe_put_status(status, row, bits, false);
         }
         __syncthreads();
     }

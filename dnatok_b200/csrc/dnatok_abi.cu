@@ -41,6 +41,7 @@ std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below th
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
 std::atomic<int64_t> g_kmer_overlap_launch{1};               // k-mer row kernel launched with programmatic stream serialisation
+std::atomic<int64_t> g_bpe_overlap_launch{1};                // BPE shared-memory-table kernel launched with programmatic stream serialisation
 std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
 std::atomic<int64_t> g_bpe_fused_output{1};                  // BPE, padded layout through dnatok_encode: merge kernels write the final rows
 std::atomic<int64_t> g_bpe_mixed{1};                         // BPE: batches of several length classes in one launch
@@ -332,9 +333,26 @@ int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDe
         int64_t grid = d.sm_count;                          // every SM takes part, however few the words (the kernel
         if (grid > n_rows) grid = n_rows;                    // lets only as many of a block's teams work as are needed)
         if (grid < 1) grid = 1;
-        bpe_lanes_st_kernel<W><<<(unsigned)grid, BPE_ST_WARPS * 32, bpe_st_team_area(W) + t.compact_bytes, st>>>(
-            bytes, offsets, direct ? nullptr : s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
-            s.tokens, s.counts, status, lo, (int32_t)n_rows, (int32_t)bpe_class_capacity(CLS));
+        // Rows that are not binned and fit the grid's teams in one go need no work counter: every team takes the word
+        // its position names.  Then nothing is zeroed before the launch, the launch before this one in the stream is
+        // a kernel as a rule, and programmatic stream serialisation lets this grid's blocks be placed while it drains.
+        const bool one_wave = direct && n_rows <= grid * ST_TEAMS;
+        if (direct && !one_wave) CUDA_TRY(cudaMemsetAsync(s.work + CLS, 0, 4, st));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(BPE_ST_WARPS * 32);
+        cfg.dynamicSmemBytes = bpe_st_team_area(W) + t.compact_bytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_bpe_overlap_launch.load() ? 1 : 0;
+        const int32_t* list = direct ? nullptr : s.class_list + (int64_t)CLS * n_rows;
+        const int32_t* list_count = s.class_count + CLS;
+        int32_t* work = one_wave ? nullptr : s.work + CLS;
+        cudaLaunchKernelEx(&cfg, bpe_lanes_st_kernel<W>, bytes, offsets, list, list_count, work, t, s.tokens, s.counts, status, lo,
+                           (int32_t)n_rows, (int32_t)bpe_class_capacity(CLS));
         LAUNCH_CHECK("bpe_lanes_st_kernel");
         return 0;
     }
@@ -346,9 +364,11 @@ int launch_bpe_lanes(const DeviceTables& d, const BpeLaunchInfo& li, const BpeDe
     const int64_t need = (n_rows + TEAMS - 1) / TEAMS;
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
+    const bool one_wave = direct && grid == need;             // as above: no counter to claim from, none to zero
+    if (direct && !one_wave) CUDA_TRY(cudaMemsetAsync(s.work + CLS, 0, 4, st));
     bpe_lanes_kernel<W><<<(unsigned)grid, BW * 32, smem, st>>>(
-        bytes, offsets, direct ? nullptr : s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS, s.work + CLS, t,
-        s.tokens, s.counts, status, lo, (int32_t)n_rows, (int32_t)bpe_class_capacity(CLS));
+        bytes, offsets, direct ? nullptr : s.class_list + (int64_t)CLS * n_rows, s.class_count + CLS,
+        one_wave ? nullptr : s.work + CLS, t, s.tokens, s.counts, status, lo, (int32_t)n_rows, (int32_t)bpe_class_capacity(CLS));
     LAUNCH_CHECK("bpe_lanes_kernel");
     return 0;
 }
@@ -391,7 +411,7 @@ int bpe_team_width(const DeviceTables& d, const BpeLaunchInfo& li, int64_t n_row
 int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
                   int64_t n_rows, int64_t total_bytes, int32_t* status, void* scratch, size_t scratch_bytes,
                   const RowFormat& rf, int32_t* lengths, cudaStream_t st, void* ids = nullptr, void* mask = nullptr,
-                  int id_bits = 0) {
+                  int id_bits = 0, bool status_unset = false) {
     if (!scratch) return fail(DNATOK_ERR_SCRATCH, "BPE needs a scratch buffer (dnatok_scratch_bytes)");
     if (reinterpret_cast<uintptr_t>(scratch) & 255) return fail(DNATOK_ERR_SCRATCH, "scratch must be 256-byte aligned");
     BpeScratch s = bpe_scratch_layout(h, scratch, n_rows, total_bytes);
@@ -401,7 +421,6 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     CUDA_TRY(cudaGetDevice(&dev));
     const BpeLaunchInfo* li;
     if (int rc = bpe_launch_info(dev, &li)) return rc;
-    CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 192, st));   // class_count, work and long_cursor are adjacent
     // classes that can hold a row of this batch: bounded by the total size and by the caller's hint
     uint32_t class_mask = 0;
     int64_t max_row = total_bytes;                          // no row is longer than this
@@ -418,10 +437,13 @@ int run_bpe_merge(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes,
     if (((class_mask >> BPE_LONG_CLASS) & 1u) && !s.long_bytes) class_mask &= ~(1u << BPE_LONG_CLASS);
     const BpeLengths lo{lengths, rf.cap_content, (rf.cls_id >= 0 ? 1 : 0) + (rf.sep_id >= 0 ? 1 : 0), rf.clip_is_error,
                         ids, rf.mask_bits ? mask : nullptr, rf.out_stride, rf.cls_id, rf.sep_id, rf.pad_id, rf.pad_left,
-                        id_bits, rf.mask_bits};
+                        id_bits, rf.mask_bits, status_unset ? 1 : 0};
     // One class only, by the caller's bounds on the row lengths: the rows need no binning, the class's kernel
     // takes them as they come (and flags a row the bounds misstated).
     const bool direct = h->hint_max_row > 0 && (class_mask & (class_mask - 1)) == 0 && !((class_mask >> BPE_LONG_CLASS) & 1u);
+    // class_count, work and long_cursor are adjacent; rows that are not binned need at most their class's work counter,
+    // which launch_bpe_lanes zeroes when it uses it
+    if (!direct) CUDA_TRY(cudaMemsetAsync(s.class_count, 0, 192, st));
     if (!direct) {
         bpe_classify_kernel<<<(unsigned)((n_rows + 255) / 256), 256, 0, st>>>(offsets, n_rows, s.class_count,
                                                                            s.class_list, s.counts, status, class_mask, lo);
@@ -895,6 +917,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_overlap_launch")) { g_kmer_overlap_launch = value; return DNATOK_OK; }
+    if (!strcmp(name, "bpe_overlap_launch")) { g_bpe_overlap_launch = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_fused_output")) { g_bpe_fused_output = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_mixed_launch")) { g_bpe_mixed = value; return DNATOK_OK; }
@@ -1130,9 +1153,9 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
         // padded BPE output: the merge kernels write ids and mask in their final layout
         if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
         if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
-        if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
+        // the status words are written by the first kernel that sees each row: no separate pass zeroes them
         return run_bpe_merge(h, *d, d_bytes, d_offsets, n_rows, total_bytes, d_status, d_scratch, scratch_bytes, rf, d_lengths,
-                             st, d_ids, d_mask, fmt->id_bits);
+                             st, d_ids, d_mask, fmt->id_bits, true);
     }
     const bool need_prepare = ragged || h->kind == DNATOK_KIND_BPE ||
                               (h->kind == DNATOK_KIND_KMER && fmt->pad_left);

@@ -243,6 +243,9 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *                           than its length needs); 0 (default): chosen from the batch - the widest team that
  *                           keeps all words resident on half of the GPU and leaves a lane four positions
  *   "bpe_team_max"          widest team the automatic choice takes (default 8)
+ *   "bpe_overlap_launch"    1 (default): the BPE kernel with the merge table in shared memory is launched with programmatic
+ *                           stream serialisation (as "kmer_overlap_launch"); a batch of one length class that fits the
+ *                           grid in one go is launched without a work counter, so nothing is zeroed between two encodes
  *   "bpe_smem_table"        1 (default): a vocabulary whose packed merge table fits into shared memory beside the
  *                           words in flight (about 75 KB: vocabularies of a few thousand tokens) is looked up there;
  *                           0: always in global memory
