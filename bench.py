@@ -567,7 +567,7 @@ def strong_scaling(local, rank, world, peak):
 
 # dram bytes per launch of the dominant kernel from the committed ncu summaries (profiles/), scaled to
 # the default workload where the capture ran on a smaller case; None until a capture exists.
-TRAFFIC = {"kmer6": 669.1e6, "char": 1085.3e6}
+TRAFFIC = {"kmer6": 665.6e6, "char": 1085.3e6}
 
 
 def per_config(local, peak, args):
