@@ -412,7 +412,7 @@ def run_ours(args):
         from dnatok_b200 import _cabi
         local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
         # (the stores bypass the cache, so a few threads per rank keep up with the copy; the mask never crosses the link)
-        per_rank = min(16, max(2, len(all_cores) // max(local_world, 1)))
+        per_rank = min(4, max(2, len(all_cores) // max(local_world, 1)))
         if os.environ.get("DNATOK_HOST_MASK_THREADS") is not None:
             per_rank = int(os.environ["DNATOK_HOST_MASK_THREADS"])
         _cabi.check(_cabi.lib().dnatok_set_option(b"host_mask_threads", per_rank))

@@ -30,7 +30,7 @@ namespace {
 
 thread_local std::string g_err;
 std::atomic<int64_t> g_launches{0};
-std::atomic<int64_t> g_host_mask_threads{-1};                 // -1: as many as the host has cores, at most 16; 0: mask copied from the device
+std::atomic<int64_t> g_host_mask_threads{-1};                 // -1: as many as the host has cores, at most 4; 0: mask copied from the device
 std::atomic<int64_t> g_host_mask_min_bytes{16ll << 20};      // smaller masks are not worth the threads
 thread_local int64_t g_last_h2d = 0, g_last_d2h = 0;          // bytes the last dnatok_encode_host of this thread copied
 std::atomic<int64_t> g_kmer_force_segments{0};                // 1: segment encoder whenever scratch is given
@@ -41,6 +41,7 @@ std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below th
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
 std::atomic<int64_t> g_kmer_overlap_launch{1};               // k-mer row kernel launched with programmatic stream serialisation
+std::atomic<int64_t> g_host_mask_early{1};                   // host path: masks whose row lengths follow from the byte counts are written at once
 std::atomic<int64_t> g_bpe_overlap_launch{1};                // BPE shared-memory-table kernel launched with programmatic stream serialisation
 std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
 std::atomic<int64_t> g_bpe_fused_output{1};                  // BPE, padded layout through dnatok_encode: merge kernels write the final rows
@@ -917,6 +918,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_overlap_launch")) { g_kmer_overlap_launch = value; return DNATOK_OK; }
+    if (!strcmp(name, "host_mask_early")) { g_host_mask_early = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_overlap_launch")) { g_bpe_overlap_launch = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_fused_output")) { g_bpe_fused_output = value; return DNATOK_OK; }
@@ -1348,6 +1350,29 @@ static int grow(void** p, size_t* cap, size_t need) {
 // nothing is reused and the issuing thread never waits.  The row lengths of a chunk come back
 // before its ids; with host-written masks the worker threads wait for each chunk's lengths in turn
 // and fill its mask rows while later chunks are still moving.
+// Row lengths (tokens kept + special tokens) that follow from the rows' byte counts alone: one token per byte for the
+// per-character tables; for k-mer tables a row with at least as many complete windows as it may keep tokens is cut to
+// exactly that many, whatever its windows hold (every window yields at least one token).  Returns false as soon as a row's
+// length depends on its content.  With these the host can write a padded batch's attention mask without waiting for
+// the GPU; the lengths the GPU reports are compared afterwards.
+static bool lengths_from_sizes(const dnatok_handle* h, const dnatok_format* f, int64_t stride, const int64_t* h_offsets,
+                               int64_t n_rows, std::vector<int32_t>* out) {
+    if (h->kind != DNATOK_KIND_CHAR && !(h->kind == DNATOK_KIND_KMER && !h->kmer_table && h->k > 0)) return false;
+    RowFormat rf;
+    if (resolve(h, f, stride, &rf)) return false;
+    const int ns = n_special(h, f);
+    out->resize((size_t)n_rows);
+    for (int64_t r = 0; r < n_rows; ++r) {
+        const int64_t len = h_offsets[r + 1] - h_offsets[r];
+        int64_t t;
+        if (h->kind == DNATOK_KIND_CHAR) t = len < rf.cap_content ? len : rf.cap_content;
+        else if (len / h->k >= rf.cap_content) t = rf.cap_content;
+        else return false;
+        (*out)[(size_t)r] = (int32_t)(t + ns);
+    }
+    return true;
+}
+
 static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, const uint8_t* h_bytes,
                                  const int64_t* h_offsets, int64_t n_rows, const dnatok_format* f,
                                  int64_t rows_per_chunk, void* h_ids, void* h_mask, int32_t* h_lengths,
@@ -1399,6 +1424,8 @@ static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, 
     if (int rc = pinned_rows(d, n_rows)) return rc;
     int32_t* hl = d->h_rows;                                   // lengths land here, status words behind them
     int32_t* hs = d->h_rows + n_rows;
+    std::vector<int32_t> known;                                // lengths the host can tell beforehand (else empty)
+    const bool lengths_known = host_mask && g_host_mask_early.load() && lengths_from_sizes(h, f, stride, h_offsets, n_rows, &known);
     for (int64_t c = 0; c < n_chunks; ++c) {
         const int64_t r0 = c * rows_per_chunk, r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
         const int64_t rows = r1 - r0, b0 = h_offsets[r0], nbytes = h_offsets[r1] - b0;
@@ -1431,18 +1458,30 @@ static int encode_host_pipelined(dnatok_handle* h, DeviceTables* d, int device, 
         // every worker takes its stripe of each chunk once that chunk's lengths have arrived
         const int nt = mask_threads;
         std::vector<int> errs((size_t)nt, 0);
+        auto fill = [&](const int32_t* len, int64_t a, int64_t b) {
+            if (f->mask_bits == 64) fill_mask_rows<int64_t>((int64_t*)h_mask, len, a, b, stride, f->pad_left != 0);
+            else if (f->mask_bits == 32) fill_mask_rows<int32_t>((int32_t*)h_mask, len, a, b, stride, f->pad_left != 0);
+            else fill_mask_rows<uint8_t>((uint8_t*)h_mask, len, a, b, stride, f->pad_left != 0);
+        };
         auto work = [&](int t) {
             if (cudaSetDevice(device) != cudaSuccess) { errs[(size_t)t] = 1; return; }
+            if (lengths_known) {                                 // nothing to wait for: the whole stripe at once
+                fill(known.data(), n_rows * t / nt, n_rows * (t + 1) / nt);
+                return;
+            }
             for (int64_t c = 0; c < n_chunks; ++c) {
                 if (cudaEventSynchronize(d->pipe_events[(size_t)c]) != cudaSuccess) { errs[(size_t)t] = 1; return; }
                 const int64_t r0 = c * rows_per_chunk, r1 = r0 + rows_per_chunk < n_rows ? r0 + rows_per_chunk : n_rows;
-                const int64_t a = r0 + (r1 - r0) * t / nt, b = r0 + (r1 - r0) * (t + 1) / nt;
-                if (f->mask_bits == 64) fill_mask_rows<int64_t>((int64_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
-                else if (f->mask_bits == 32) fill_mask_rows<int32_t>((int32_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
-                else fill_mask_rows<uint8_t>((uint8_t*)h_mask, hl, a, b, stride, f->pad_left != 0);
+                fill(hl, r0 + (r1 - r0) * t / nt, r0 + (r1 - r0) * (t + 1) / nt);
             }
         };
         HostPool::get().run(nt, work);
+        if (lengths_known) {
+            // the GPU's lengths have the last word: a row that came out otherwise gets its mask again
+            for (auto& st : d->pipe_streams) if (st) CUDA_TRY(cudaStreamSynchronize(st));
+            for (int64_t r = 0; r < n_rows; ++r)
+                if (hl[r] != known[(size_t)r]) fill(hl, r, r + 1);
+        }
         for (int e : errs) if (e) rc_mask = fail(DNATOK_ERR_CUDA, "a host worker could not wait for the row lengths");
     }
     for (auto& st : d->pipe_streams) if (st) CUDA_TRY(cudaStreamSynchronize(st));
@@ -1500,7 +1539,7 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
             int mask_threads = (int)g_host_mask_threads.load();
             if (mask_threads < 0) {
                 const unsigned hc = std::thread::hardware_concurrency();
-                mask_threads = hc == 0 ? 1 : (hc > 16 ? 16 : (int)hc);
+                mask_threads = hc == 0 ? 1 : (hc > 4 ? 4 : (int)hc);   // non-temporal stores: two threads keep up with the link, more only add contention
             }
             const bool want_mask = mask_sz && h_mask;
             const bool host_mask = want_mask && mask_threads > 0 &&
@@ -1598,7 +1637,7 @@ int dnatok_encode_host(dnatok_handle* h, int device, const uint8_t* h_bytes, con
     int mask_threads = (int)g_host_mask_threads.load();
     if (mask_threads < 0) {
         const unsigned hc = std::thread::hardware_concurrency();
-        mask_threads = hc == 0 ? 1 : (hc > 16 ? 16 : (int)hc);
+        mask_threads = hc == 0 ? 1 : (hc > 4 ? 4 : (int)hc);   // non-temporal stores: two threads keep up with the link, more only add contention
     }
     const bool host_mask = mask_sz && h_mask && !ragged && mask_threads > 0 &&
                            (int64_t)((size_t)out_elems * mask_sz) >= g_host_mask_min_bytes.load();

@@ -226,9 +226,13 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *                           0 disables splitting (default 64 MiB)
  *   "host_chunk_threshold"  only batches at least this large are split (default 128 MiB)
  *   "host_mask_threads"     dnatok_encode_host, padded output with a mask of 16 MiB or more: the mask is written by
- *                           this many host threads from the row lengths while the ids are copied back, instead of
- *                           being produced on the GPU and copied too (-1, default: one per core, at most 16;
- *                           0: always copy the mask from the device)
+ *                           this many host threads (non-temporal stores) while the ids are copied back, instead of
+ *                           being produced on the GPU and copied too (-1, default: one per core, at most 4: two keep up
+ *                           with the link, more only compete with the copies for the host's memory; 0: always copy the
+ *                           mask from the device)
+ *   "host_mask_early"       1 (default): when every row's length follows from its byte count (per-character tables; k-mer
+ *                           rows with at least as many complete windows as tokens are kept) the mask is written without
+ *                           waiting for the GPU, whose lengths are compared afterwards; 0: always wait for them
  *   "host_mask_min_bytes"   the size from which a mask is written by host threads (default 16 MiB)
  *   "kmer_force_segments"   1: use the k-mer segment encoder whenever scratch and a status array are given, whatever
  *                           the batch shape

@@ -447,6 +447,36 @@ def test_host_entry_chunked_pipeline(toks, name, rows, length, kw, mask_threads)
     assert np.array_equal(enc["lengths"], o_mask.sum(axis=1))
 
 
+@pytest.mark.parametrize("early", [1, 0])
+@pytest.mark.parametrize("pad_left", [False, True])
+def test_host_entry_mask_from_row_sizes(toks, early, pad_left):
+    """Rows whose token count follows from their byte count (k-mer rows with at least max_length complete windows, N runs
+    or not): the host writes the mask without waiting for the GPU's lengths, which must agree with it."""
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    tok = toks["kmer6"]
+    flat, offs = synth.pack_rows(synth.config2(batch=3000, length=6003, seed=77))
+    kw = dict(padding="max_length", max_length=1000, truncation=True, add_special_tokens=False)
+    _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 4 << 20))
+    _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 0))
+    _cabi.check(L.dnatok_set_option(b"host_mask_min_bytes", 0))
+    _cabi.check(L.dnatok_set_option(b"host_mask_early", early))
+    tok.padding_side = "left" if pad_left else "right"
+    try:
+        enc = tok.encode_host((flat, offs), **kw)
+    finally:
+        tok.padding_side = "right"
+        _cabi.check(L.dnatok_set_option(b"host_chunk_bytes", 64 << 20))
+        _cabi.check(L.dnatok_set_option(b"host_chunk_threshold", 128 << 20))
+        _cabi.check(L.dnatok_set_option(b"host_mask_min_bytes", 16 << 20))
+        _cabi.check(L.dnatok_set_option(b"host_mask_early", 1))
+    o_ids, o_mask = H.oracle_batch("kmer6", flat, offs, padding="max_length", max_length=1000, truncation=True,
+                                   add_special=False, pad_left=pad_left)
+    assert np.array_equal(enc["input_ids"], o_ids)
+    assert np.array_equal(enc["attention_mask"], o_mask)
+    assert enc["attention_mask"].all() and np.array_equal(enc["lengths"], np.full(3000, 1000))
+
+
 @pytest.mark.parametrize("name", ["char", "kmer6", "bpe4096"])
 @pytest.mark.parametrize("mask_dtype", [np.int64, np.int32, np.uint8])
 def test_host_entry_mask_written_by_host_threads(toks, name, mask_dtype):
