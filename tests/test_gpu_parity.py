@@ -54,6 +54,33 @@ def run_device(tok, flat, offs, **kw):
     return enc
 
 
+@pytest.mark.parametrize("name,rows,length", [("bpe4096", 6000, 1024), ("bpe32000", 3000, 2000), ("bpe32000", 100, 2000),
+                                              ("bpe4096", 700, 300)])
+@pytest.mark.parametrize("side", ["right", "left"])
+def test_bpe_rows_of_one_length_class(toks, name, rows, length, side):
+    """Batches whose row bounds name one length class are not binned: more words than the GPU holds at once (words
+    claimed from a counter), and fewer (every team takes the word its position names), with the merge kernel writing
+    ids, mask, lengths and status itself; both padding sides; a few rows shorter than the rest."""
+    tok = toks[name]
+    flat, offs = synth.pack_rows(synth.config3(batch=rows, length=length, seed=rows))
+    lens = np.diff(offs)
+    lens[::97] = length - 5                                  # still the same class
+    lens[5] = length - 200 if length > 1100 else length - 3
+    offs2 = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    flat = np.concatenate([flat[offs[i]:offs[i] + lens[i]] for i in range(rows)])
+    width = length // 3
+    tok.padding_side = side
+    try:
+        enc = run_device(tok, flat, offs2, padding="max_length", max_length=width, truncation=True)
+    finally:
+        tok.padding_side = "right"
+    o_ids, o_mask = H.oracle_batch(name, flat, offs2, padding="max_length", max_length=width, truncation=True,
+                                   pad_left=(side == "left"))
+    assert np.array_equal(enc["input_ids"].cpu().numpy(), o_ids)
+    assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask)
+    assert np.array_equal(enc["lengths"].cpu().numpy(), o_mask.sum(axis=1))
+
+
 @pytest.mark.parametrize("cfg", H.ALL_CONFIGS)
 def test_golden_configs_device(golden, toks, cfg, bpe_team_mode):
     if bpe_team_mode != "auto" and "bpe" not in cfg:
