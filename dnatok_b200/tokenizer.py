@@ -316,9 +316,9 @@ class B200Tokenizer:
             flat, offsets = pack_strings(seqs, table=table, pad_to=pad_to, pad_byte=pad_byte, pad_left=pad_left,
                                          trunc_to=trunc_to, out=self._pin.numpy())
             with torch.cuda.device(dev):
+                d_off = torch.from_numpy(offsets).to(dev)        # small, and before the large copy so it does not wait for it
                 d_bytes = torch.empty(flat.size, dtype=torch.uint8, device=dev)
                 d_bytes.copy_(self._pin[:flat.size], non_blocking=True)
-                d_off = torch.from_numpy(offsets).to(dev)
                 self._pin_done = torch.cuda.Event()
                 self._pin_done.record()
             return d_bytes, d_off, offsets
