@@ -55,8 +55,9 @@ class B200Tokenizer:
         self.device = torch.device(device if not isinstance(device, int) else "cuda:%d" % device)
         self.padding_side = spec.specials.padding_side
         self.check_status = True
-        self._pin = None            # pinned host buffer the native packer fills
-        self._pin_done = None       # event: the last copy out of it
+        self._pins = [None, None]   # two pinned host buffers the native packer fills in turn, so that packing one
+        self._pin_done = [None, None]   # batch can overlap the copy of the batch before; events: the last copy out of each
+        self._pin_turn = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -309,18 +310,22 @@ class B200Tokenizer:
                 return (torch.empty(0, dtype=torch.uint8, device=dev), torch.zeros(1, dtype=torch.int64, device=dev),
                         np.zeros(1, dtype=np.int64))
             need = pack_sizes(seqs, pad_to, trunc_to)
-            if self._pin_done is not None:
-                self._pin_done.synchronize()             # the copy out of the pinned buffer by the call before
-            if self._pin is None or self._pin.numel() < need:
-                self._pin = torch.empty(max(need + need // 4, 1 << 16), dtype=torch.uint8).pin_memory()
+            k = self._pin_turn
+            self._pin_turn ^= 1
+            if self._pin_done[k] is not None:
+                self._pin_done[k].synchronize()          # the copy out of this buffer two calls ago
+            if self._pins[k] is None or self._pins[k].numel() < need:
+                self._pins[k] = torch.empty(max(need + need // 4, 1 << 16), dtype=torch.uint8).pin_memory()
+            pin = self._pins[k]
             flat, offsets = pack_strings(seqs, table=table, pad_to=pad_to, pad_byte=pad_byte, pad_left=pad_left,
-                                         trunc_to=trunc_to, out=self._pin.numpy())
+                                         trunc_to=trunc_to, out=pin.numpy())
             with torch.cuda.device(dev):
                 d_off = torch.from_numpy(offsets).to(dev)        # small, and before the large copy so it does not wait for it
                 d_bytes = torch.empty(flat.size, dtype=torch.uint8, device=dev)
-                d_bytes.copy_(self._pin[:flat.size], non_blocking=True)
-                self._pin_done = torch.cuda.Event()
-                self._pin_done.record()
+                d_bytes.copy_(pin[:flat.size], non_blocking=True)
+                if self._pin_done[k] is None:
+                    self._pin_done[k] = torch.cuda.Event()
+                self._pin_done[k].record()
             return d_bytes, d_off, offsets
         if pad_to or trunc_to:
             raise ValueError("pad_to / trunc_to need a list of rows")
