@@ -15,6 +15,8 @@ struct RowFormat {
     int32_t pad_left;
     int32_t mask_bits;      // 0, 8, 32, 64
     int32_t clip_is_error;  // rows cut by the stride (not by requested truncation) get DNATOK_ROW_CLIPPED
+    int32_t store_status;   // 1: the status words were not zeroed: the kernel writes a row's word instead of OR-ing into it
+                            // (only kernels in which one thread finishes a row, and only when the host says so)
 };
 
 template <typename T> struct Vec16;

@@ -208,6 +208,7 @@ int resolve(const dnatok_handle* h, const dnatok_format* f, int64_t stride, RowF
     r->mask_bits = f->mask_bits;
     int64_t cap = INT64_MAX;
     r->clip_is_error = 0;
+    r->store_status = 0;
     if (f->max_tokens > 0) {
         if (f->max_tokens < ns) return fail(DNATOK_ERR_INVALID, "max_tokens smaller than the special tokens");
         cap = f->max_tokens - ns;
@@ -678,10 +679,19 @@ template <bool COUNT_ONLY>
 int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, const int64_t* offsets,
                 int64_t n_rows, int64_t total_bytes, const RowFormat& rf, int id_bits, void* ids, void* mask,
                 const int32_t* lengths_in, int32_t* lengths_out, const int64_t* out_offsets,
-                int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+                int32_t* status, void* scratch, size_t scratch_bytes, cudaStream_t st, bool status_unset = false) {
     if (n_rows == 0) return 0;
     const int k = h->k;
+    // status_unset: the caller left the status words as they were.  The row-per-warp encoder writes every row's word
+    // itself (so nothing sits between two such launches in a stream); every other kernel ORs bits into zeroed words.
+    bool need_zero = status_unset && status;
+    auto zero_now = [&]() -> int {
+        if (need_zero) CUDA_TRY(cudaMemsetAsync(status, 0, (size_t)n_rows * 4, st));
+        need_zero = false;
+        return 0;
+    };
     if (h->kmer_table) {
+        if (int rc = zero_now()) return rc;
         const KmerTable t{d.table5, d.exp_off, d.exp_ids, d.lut256, k, h->tail_singles};
         const unsigned grid = (unsigned)((n_rows + KT_WARPS - 1) / KT_WARPS);
         if (id_bits == 64)
@@ -707,6 +717,7 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
         (few_rows || long_rows || g_kmer_force_segments)) {
         const KmerScratch ks = kmer_scratch_layout(h, scratch, n_rows, total_bytes);
         if (ks.bytes <= scratch_bytes && (ks.n_seg > 1 || g_kmer_force_segments)) {
+            if (int rc = zero_now()) return rc;
             CUDA_TRY(cudaMemsetAsync(scratch, 0, ks.bytes, st));
             if (id_bits == 64) launch_kmer_seg<int64_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask,
                                                         lengths_in, lengths_out, out_offsets, status, ks, st);
@@ -716,6 +727,7 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
             return 0;
         }
     }
+    if (COUNT_ONLY) if (int rc = zero_now()) return rc;
     if (COUNT_ONLY && scratch && !(reinterpret_cast<uintptr_t>(scratch) & 255) && (few_rows || long_rows)) {
         const KmerScratch ks = kmer_scratch_layout(h, scratch, n_rows, total_bytes);
         if (ks.bytes <= scratch_bytes && ks.n_seg > 1) {
@@ -741,13 +753,16 @@ int launch_kmer(dnatok_handle* h, const DeviceTables& d, const uint8_t* bytes, c
         return 0;
     }
     if (!COUNT_ONLY && total_bytes / n_rows <= KMER_WARP_MAX_AVG_LEN) {
-        if (id_bits == 64) launch_kmer_warp<int64_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
+        RowFormat rfw = rf;
+        if (need_zero) { rfw.store_status = 1; need_zero = false; }
+        if (id_bits == 64) launch_kmer_warp<int64_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rfw, ids, mask, lengths_in,
                                                      lengths_out, out_offsets, status, st);
-        else launch_kmer_warp<int32_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rf, ids, mask, lengths_in,
+        else launch_kmer_warp<int32_t>(k, d, h->kmer_affine_base, bytes, offsets, n_rows, total_bytes, rfw, ids, mask, lengths_in,
                                        lengths_out, out_offsets, status, st);
         LAUNCH_CHECK("kmer_warp_rows_kernel");
         return 0;
     }
+    if (int rc = zero_now()) return rc;
     const size_t smem = (size_t)((KMER_TILE_W * k + 32 + 15) & ~15) + (size_t)KMER_TILE_W * k * 4;
     const unsigned grid = (unsigned)(n_rows < (int64_t)d.sm_count * 64 ? n_rows : (int64_t)d.sm_count * 64);
     if (id_bits == 64)
@@ -1175,12 +1190,14 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     // padded char / right-padded k-mer: one kernel, lengths written on the way
     if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
     if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
-    if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
-    if (h->kind == DNATOK_KIND_CHAR)
+    if (h->kind == DNATOK_KIND_CHAR) {
+        if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
         return launch_char(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, d_lengths, nullptr,
                            d_status, st);
+    }
+    // k-mer: the status words are zeroed inside, unless the kernel that runs writes them itself
     return launch_kmer<false>(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, nullptr, d_lengths,
-                              nullptr, d_status, d_scratch, scratch_bytes, st);
+                              nullptr, d_status, d_scratch, scratch_bytes, st, true);
 }
 
 // ------------------------------------------------------------------ fused embedding gather

@@ -593,7 +593,7 @@ __device__ __forceinline__ int kmer_encode_windows(const KmerRow<IdT>& r, int ca
 template <typename IdT, bool FUSE_MASK>
 __device__ __forceinline__ void kmer_finish_row(const KmerRow<IdT>& r, int64_t row, int base, int cap, bool clipped,
                                                 const RowFormat& f, IdT* ids, void* mask, int32_t* lengths_out,
-                                                const int64_t* out_offsets, int32_t* status, int lane) {
+                                                const int64_t* out_offsets, int32_t* status, int lane, int32_t more_bits = 0) {
     const bool has_cls = f.cls_id >= 0, has_sep = f.sep_id >= 0;
     const bool ragged = f.out_stride == 0;
     const int n = base < cap ? base : cap;
@@ -602,7 +602,11 @@ __device__ __forceinline__ void kmer_finish_row(const KmerRow<IdT>& r, int64_t r
     const int shift = r.shift;
     if (lane == 0) {
         if (lengths_out) lengths_out[row] = (int32_t)T;
-        if (status && f.clip_is_error && clipped) atomicOr(status + row, 4);
+        if (status) {
+            const int32_t bits = more_bits | ((f.clip_is_error && clipped) ? 4 : 0);
+            if (f.store_status) status[row] = bits;
+            else if (bits) atomicOr(status + row, bits);
+        }
         if (has_cls) { orow[shift] = (IdT)f.cls_id; if (FUSE_MASK) (reinterpret_cast<IdT*>(mask) + (orow - ids))[shift] = 1; }
         if (has_sep) { orow[shift + T - 1] = (IdT)f.sep_id; if (FUSE_MASK) (reinterpret_cast<IdT*>(mask) + (orow - ids))[shift + T - 1] = 1; }
     }
@@ -646,11 +650,11 @@ kmer_warp_rows_kernel(const uint8_t* __restrict__ bytes, const int64_t* __restri
                                                   out_offsets);
     const int cap = (int)(f.cap_content < 0x7fffffff ? f.cap_content : 0x7fffffff);
     const int64_t mdelta = FUSE_MASK ? (reinterpret_cast<IdT*>(mask) - ids) : 0;
-    kmer_flag_long_row(offsets[row + 1] - offsets[row], status, row, lane);
+    const int32_t long_bit = offsets[row + 1] - offsets[row] > 0x7fffffff ? 1 : 0;    // cut at 2^31 - 1 bytes and reported
     bool clipped = false;
     const int base = kmer_encode_windows<IdT, K, AFFINE, FUSE_MASK>(r, cap, kmer_ids, affine_base, single_ids, mdelta, lane,
                                                                     0, r.n_win, 0, &clipped);
-    kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane);
+    kmer_finish_row<IdT, FUSE_MASK>(r, row, base, cap, clipped, f, ids, mask, lengths_out, out_offsets, status, lane, long_bit);
 }
 
 // Rows cut into segments of KSEG_WINDOWS windows.  Ticket t stands for segment t / n_rows of row
