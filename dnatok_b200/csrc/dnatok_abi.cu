@@ -41,6 +41,7 @@ std::atomic<int64_t> g_host_chunk_threshold{128ll << 20};    // batches below th
 std::atomic<int64_t> g_bpe_team_warps{0};                    // BPE: force this team width (warps per word); 0: choose by batch size
 std::atomic<int64_t> g_bpe_team_max{8};                      // BPE: widest team the automatic choice takes
 std::atomic<int64_t> g_kmer_overlap_launch{1};               // k-mer row kernel launched with programmatic stream serialisation
+std::atomic<int64_t> g_emit_overlap_launch{1};               // padded output kernel launched with programmatic stream serialisation
 std::atomic<int64_t> g_host_mask_early{1};                   // host path: masks whose row lengths follow from the byte counts are written at once
 std::atomic<int64_t> g_bpe_overlap_launch{1};                // BPE shared-memory-table kernel launched with programmatic stream serialisation
 std::atomic<int64_t> g_bpe_smem_table{1};                    // BPE: keep a small vocabulary's merge table in shared memory
@@ -511,16 +512,26 @@ int launch_emit(const DeviceTables& d, const SrcT* src, const int64_t* offsets, 
         const int64_t n_spans = spr * n_rows;
         const int64_t blocks = (n_spans + EMIT_WARPS - 1) / EMIT_WARPS;
         const unsigned grid = (unsigned)(blocks < (int64_t)d.sm_count * 32 ? blocks : (int64_t)d.sm_count * 32);
+        // programmatic stream serialisation, as for the k-mer row kernel
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(EMIT_THREADS);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_emit_overlap_launch.load() ? 1 : 0;
+        const int32_t* lut = d.lut256;
         if (id_bits == 64)
-            emit_padded_kernel<SrcT, int64_t, LUT, EMIT_SPAN><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
-                                                                                             (int64_t*)ids, mask, lengths, status, spr, n_spans);
+            cudaLaunchKernelEx(&cfg, emit_padded_kernel<SrcT, int64_t, LUT, EMIT_SPAN>, src, sb, se, offsets, counts, n_rows, lut, rf,
+                               (int64_t*)ids, mask, lengths, status, spr, n_spans);
         else if (wide)
-            emit_padded_kernel<uint8_t, int32_t, LUT, EMIT_SPAN_WIDE><<<grid, EMIT_THREADS, 0, st>>>(
-                reinterpret_cast<const uint8_t*>(src), sb, se, offsets, counts, n_rows, d.lut256, rf, (int32_t*)ids, mask, lengths,
-                status, spr, n_spans);
+            cudaLaunchKernelEx(&cfg, emit_padded_kernel<uint8_t, int32_t, LUT, EMIT_SPAN_WIDE>, reinterpret_cast<const uint8_t*>(src),
+                               sb, se, offsets, counts, n_rows, lut, rf, (int32_t*)ids, mask, lengths, status, spr, n_spans);
         else
-            emit_padded_kernel<SrcT, int32_t, LUT, EMIT_SPAN><<<grid, EMIT_THREADS, 0, st>>>(src, sb, se, offsets, counts, n_rows, d.lut256, rf,
-                                                                                             (int32_t*)ids, mask, lengths, status, spr, n_spans);
+            cudaLaunchKernelEx(&cfg, emit_padded_kernel<SrcT, int32_t, LUT, EMIT_SPAN>, src, sb, se, offsets, counts, n_rows, lut, rf,
+                               (int32_t*)ids, mask, lengths, status, spr, n_spans);
         LAUNCH_CHECK("emit_padded_kernel");
     } else {
         const int64_t bound = total_bytes + 2 * n_rows;
@@ -933,6 +944,7 @@ int dnatok_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "bpe_team_warps")) { g_bpe_team_warps = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_team_max")) { g_bpe_team_max = value; return DNATOK_OK; }
     if (!strcmp(name, "kmer_overlap_launch")) { g_kmer_overlap_launch = value; return DNATOK_OK; }
+    if (!strcmp(name, "emit_overlap_launch")) { g_emit_overlap_launch = value; return DNATOK_OK; }
     if (!strcmp(name, "host_mask_early")) { g_host_mask_early = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_overlap_launch")) { g_bpe_overlap_launch = value; return DNATOK_OK; }
     if (!strcmp(name, "bpe_smem_table")) { g_bpe_smem_table = value; return DNATOK_OK; }
@@ -1191,8 +1203,10 @@ int dnatok_encode(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_off
     if (!d_ids && n_rows) return fail(DNATOK_ERR_INVALID, "d_ids is NULL");
     if (fmt->mask_bits && !d_mask) return fail(DNATOK_ERR_INVALID, "mask requested but d_mask is NULL");
     if (h->kind == DNATOK_KIND_CHAR) {
-        if (d_status && n_rows) CUDA_TRY(cudaMemsetAsync(d_status, 0, (size_t)n_rows * 4, st));
-        return launch_char(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rf, fmt->id_bits, d_ids, d_mask, d_lengths, nullptr,
+        // one span of every row writes the row's status word: nothing is zeroed first
+        RowFormat rfc = rf;
+        rfc.store_status = 1;
+        return launch_char(h, *d, d_bytes, d_offsets, n_rows, total_bytes, rfc, fmt->id_bits, d_ids, d_mask, d_lengths, nullptr,
                            d_status, st);
     }
     // k-mer: the status words are zeroed inside, unless the kernel that runs writes them itself

@@ -40,6 +40,10 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
     constexpr int SZ = (int)sizeof(SrcT);
     constexpr int CHUNKS = SPAN * SZ / 16 + 1;               // 16-byte chunks covering a span at any alignment
     constexpr int VB = N * SZ;                                // source bytes under one output vector: 2, 4 or 8
+    // Launched with programmatic stream serialisation: the next launch of the stream may be set up while this grid
+    // drains, and this grid starts its work only once everything before it in the stream is complete and visible.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ int32_t s_lut[256];
     __shared__ uint4 s_win[EMIT_WARPS][CHUNKS + 1];
     if (USE_LUT) {
@@ -77,7 +81,11 @@ emit_padded_kernel(const SrcT* __restrict__ src, const uint8_t* __restrict__ src
         p.shift = f.pad_left ? stride - p.T : 0;
         if (p.cs == 0 && lane == 0) {
             if (lengths_out) lengths_out[p.row] = (int32_t)p.T;
-            if (status && f.clip_is_error && n_in > p.n) atomicOr(status + p.row, 4);
+            if (status) {
+                const int32_t bits = (f.clip_is_error && n_in > p.n) ? 4 : 0;
+                if (f.store_status) status[p.row] = bits;       // the caller left the words unset: written, not OR-ed
+                else if (bits) atomicOr(status + p.row, bits);
+            }
         }
         p.ncol = (int)(stride - p.cs < SPAN ? stride - p.cs : SPAN);
         p.t_lo = p.cs - (p.shift + (has_cls ? 1 : 0));        // content index under the span's first column

@@ -243,6 +243,7 @@ int dnatok_pack_fasta(const char* text, int64_t n_text, uint8_t* out_bytes, int6
  *   "kmer_overlap_launch"   1 (default): the k-mer row kernel is launched with programmatic stream serialisation, so
  *                           its blocks can be placed while the launch before it in the stream drains (they wait for
  *                           that launch to complete before touching memory); 0: plain launch
+ *   "emit_overlap_launch"   the same for the padded output kernel of the per-character path (default 1)
  *   "bpe_team_warps"        BPE: warps that work on one word (power of two up to 32; a word never gets fewer
  *                           than its length needs); 0 (default): chosen from the batch - the widest team that
  *                           keeps all words resident on half of the GPU and leaves a lane four positions
