@@ -92,6 +92,68 @@ typedef struct {
     Py_ssize_t lo, hi;
 } job_t;
 
+static void* copy_rows(void* p);
+
+/* Copy workers that outlive a call: a list is often packed piece by piece (each piece goes onto the link while the
+ * next is packed), and starting threads for every piece would cost more than the copy.  run_jobs() hands out the
+ * jobs of one call to the workers and the calling thread; one call at a time.  A forked child starts without workers. */
+static pthread_mutex_t pool_mu = PTHREAD_MUTEX_INITIALIZER, pool_run_mu = PTHREAD_MUTEX_INITIALIZER;
+static pthread_cond_t pool_start = PTHREAD_COND_INITIALIZER, pool_done = PTHREAD_COND_INITIALIZER;
+static void* pool_jobs = NULL;
+static size_t pool_job_size = 0;
+static int pool_n_jobs = 0, pool_next = 0, pool_left = 0, pool_threads = 0, pool_atfork_set = 0;
+static unsigned long pool_generation = 0;
+
+static void pool_take_jobs(void) {                 /* called with pool_mu held; returns with it held */
+    while (pool_next < pool_n_jobs) {
+        void* job = (char*)pool_jobs + pool_job_size * (size_t)pool_next++;
+        pthread_mutex_unlock(&pool_mu);
+        copy_rows(job);
+        pthread_mutex_lock(&pool_mu);
+        if (--pool_left == 0) pthread_cond_broadcast(&pool_done);
+    }
+}
+
+static void* pool_worker(void* unused) {
+    unsigned long seen = 0;
+    (void)unused;
+    pthread_mutex_lock(&pool_mu);
+    for (;;) {
+        while (seen == pool_generation) pthread_cond_wait(&pool_start, &pool_mu);
+        seen = pool_generation;
+        pool_take_jobs();
+    }
+    return NULL;
+}
+
+static void pool_child(void) {                     /* after fork(): the child has none of the threads */
+    pthread_mutex_init(&pool_mu, NULL);
+    pthread_mutex_init(&pool_run_mu, NULL);
+    pthread_cond_init(&pool_start, NULL);
+    pthread_cond_init(&pool_done, NULL);
+    pool_threads = 0; pool_n_jobs = 0; pool_next = 0; pool_left = 0;
+}
+
+static void run_jobs(void* jobs, size_t job_size, int n) {
+    pthread_mutex_lock(&pool_run_mu);
+    pthread_mutex_lock(&pool_mu);
+    if (!pool_atfork_set) { pthread_atfork(NULL, NULL, pool_child); pool_atfork_set = 1; }
+    while (pool_threads < n - 1) {
+        pthread_t th;
+        if (pthread_create(&th, NULL, pool_worker, NULL)) break;       /* fewer workers: the caller does more itself */
+        pthread_detach(th);
+        ++pool_threads;
+    }
+    pool_jobs = jobs; pool_job_size = job_size; pool_n_jobs = n; pool_next = 0; pool_left = n;
+    ++pool_generation;
+    pthread_cond_broadcast(&pool_start);
+    pool_take_jobs();
+    while (pool_left > 0) pthread_cond_wait(&pool_done, &pool_mu);
+    pool_n_jobs = 0;
+    pthread_mutex_unlock(&pool_mu);
+    pthread_mutex_unlock(&pool_run_mu);
+}
+
 static void* copy_rows(void* p) {
     const job_t* j = (const job_t*)p;
     for (Py_ssize_t i = j->lo; i < j->hi; ++i) {
@@ -161,14 +223,8 @@ static PyObject* pack_copy(PyObject* self, PyObject* args, PyObject* kw) {
             lo = hi;
         }
         Py_BEGIN_ALLOW_THREADS
-        pthread_t th[64];
-        int started[64];
-        for (int t = 1; t < threads; ++t) started[t] = pthread_create(&th[t], NULL, copy_rows, &jobs[t]) == 0;
-        copy_rows(&jobs[0]);
-        for (int t = 1; t < threads; ++t) {
-            if (started[t]) pthread_join(th[t], NULL);
-            else copy_rows(&jobs[t]);                        /* no thread to be had: do its share here */
-        }
+        if (threads <= 1) copy_rows(&jobs[0]);
+        else run_jobs(jobs, sizeof(job_t), threads);
         Py_END_ALLOW_THREADS
         result = Py_None;
         Py_INCREF(result);
