@@ -234,24 +234,30 @@ emit_ragged_kernel(const SrcT* __restrict__ src, const int64_t* __restrict__ off
         }
         __syncthreads();
         const int64_t r_lo = s_rows[0], r_hi = s_rows[1];
+        // A thread's elements rise through the tile, so the row under them only moves forward: its bounds and the place of
+        // its source stay in registers and are fetched again only when an element lies past the row's end.
+        int64_t lo = r_lo, row_start = 0, row_end = -1, src_at = 0;
         for (int64_t c = e0 + (int64_t)threadIdx.x * N; c < e1; c += (int64_t)EMIT_THREADS * N) {
             IdT vals[N];
-            int64_t lo = r_lo;
 #pragma unroll
             for (int e = 0; e < N; ++e) {
                 const int64_t g = c + e;
                 int32_t v = f.pad_id;
                 if (g < e1) {
-                    int64_t hi = r_hi;              // rows are ordered, so the search restarts at lo
-                    while (lo < hi) {
-                        const int64_t mid = (lo + hi + 1) >> 1;
-                        if (out_offsets[mid] <= g) lo = mid; else hi = mid - 1;
+                    if (g >= row_end) {
+                        int64_t hi = r_hi;          // rows are ordered, so the search restarts at lo
+                        while (lo < hi) {
+                            const int64_t mid = (lo + hi + 1) >> 1;
+                            if (out_offsets[mid] <= g) lo = mid; else hi = mid - 1;
+                        }
+                        row_start = out_offsets[lo];
+                        row_end = out_offsets[lo + 1];
+                        src_at = offsets[lo] - (has_cls ? 1 : 0);
                     }
-                    const int64_t t = g - out_offsets[lo];
-                    const int64_t T = out_offsets[lo + 1] - out_offsets[lo];
+                    const int64_t t = g - row_start;
                     if (has_cls && t == 0) v = f.cls_id;
-                    else if (has_sep && t == T - 1) v = f.sep_id;
-                    else v = emit_load<SrcT, USE_LUT>(src + offsets[lo] + t - (has_cls ? 1 : 0), s_lut);
+                    else if (has_sep && g == row_end - 1) v = f.sep_id;
+                    else v = emit_load<SrcT, USE_LUT>(src + src_at + t, s_lut);
                 }
                 vals[e] = (IdT)v;
             }
