@@ -308,7 +308,9 @@ __global__ void span_lengths_kernel(const int64_t* __restrict__ offsets, const i
     if (status && f.clip_is_error && n_in > n) atomicOr(status + i, 4);
 }
 
-// Exclusive scan of int32 lengths into int64 offsets, one block, chunk by chunk.
+// Exclusive scan of int32 lengths into int64 offsets, one block, 4,096 rows per trip: every thread takes four
+// consecutive lengths (one 16-byte load), so a batch of a few thousand rows is one load, one block-wide scan and
+// one round of stores instead of a chain of them.
 __global__ void __launch_bounds__(1024)
 scan_lengths_kernel(const int32_t* __restrict__ lengths, int64_t n_rows, int64_t* __restrict__ out_offsets) {
     __shared__ int64_t s_warp[32];
@@ -316,9 +318,18 @@ scan_lengths_kernel(const int32_t* __restrict__ lengths, int64_t n_rows, int64_t
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) { s_carry = 0; out_offsets[0] = 0; }
     __syncthreads();
-    for (int64_t base = 0; base < n_rows; base += 1024) {
-        const int64_t i = base + tid;
-        int64_t v = i < n_rows ? (int64_t)lengths[i] : 0;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(lengths) & 15) == 0;
+    for (int64_t base = 0; base < n_rows; base += 4096) {
+        const int64_t i = base + 4 * (int64_t)tid;
+        int32_t l[4] = {0, 0, 0, 0};
+        if (vec_ok && i + 4 <= n_rows) {
+            const int4 q = *reinterpret_cast<const int4*>(lengths + i);
+            l[0] = q.x; l[1] = q.y; l[2] = q.z; l[3] = q.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) if (i + e < n_rows) l[e] = lengths[i + e];
+        }
+        const int64_t v = (int64_t)l[0] + l[1] + l[2] + l[3];
         int64_t x = v;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -337,8 +348,13 @@ scan_lengths_kernel(const int32_t* __restrict__ lengths, int64_t n_rows, int64_t
             s_warp[lane] = w;
         }
         __syncthreads();
-        const int64_t incl = x + (warp ? s_warp[warp - 1] : 0) + s_carry;
-        if (i < n_rows) out_offsets[i + 1] = incl;
+        const int64_t incl = x + (warp ? s_warp[warp - 1] : 0) + s_carry;     // through this thread's four rows
+        int64_t run = incl - v;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            run += l[e];
+            if (i + e < n_rows) out_offsets[i + e + 1] = run;
+        }
         __syncthreads();
         if (tid == 1023) s_carry = incl;
         __syncthreads();

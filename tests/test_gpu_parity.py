@@ -794,6 +794,22 @@ def test_dnatok_flags_match_reference_outputs(golden):
             assert ids == case["ids"], tag
 
 
+def test_scan_lengths_at_trip_boundaries():
+    """dnatok_scan_lengths (row lengths -> ragged output offsets) around its 4,096-row trips, on a 16-byte aligned array
+    and on one that is not."""
+    import ctypes
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    for n in (1, 3, 4, 5, 1023, 1024, 4095, 4096, 4097, 8192, 100003):
+        a = torch.randint(0, 5000, (n,), dtype=torch.int32, device="cuda")
+        out = torch.empty(n + 1, dtype=torch.int64, device="cuda")
+        for src in (a, torch.cat([torch.zeros(1, dtype=torch.int32, device="cuda"), a])[1:]):
+            _cabi.check(L.dnatok_scan_lengths(ctypes.c_void_p(src.data_ptr()), n, ctypes.c_void_p(out.data_ptr()), None))
+            torch.cuda.synchronize()
+            want = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), torch.cumsum(src.to(torch.int64), 0)])
+            assert torch.equal(out, want), n
+
+
 def test_row_length_hint_flags_rows_outside_it():
     """A wrong dnatok_set_row_bytes_hint must not lose rows silently: they get a status bit."""
     import ctypes
