@@ -438,6 +438,76 @@ def test_bpe_table_with_late_created_operands_single_step(bpe_team_mode):
         assert ids[oo[i]:oo[i + 1]].tolist() == oracle.bpe_word(table, w, lut), i
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_bpe_random_merge_tables(seed):
+    _random_merge_tables(seed)
+
+
+@pytest.mark.parametrize("seed", [100, 101, 102])
+def test_bpe_random_merge_tables_every_way_of_running(seed, bpe_team_mode):
+    _random_merge_tables(seed)
+
+
+def _random_merge_tables(seed):
+    """Merge tables that no trainer produced: random pairs of already created tokens (so operands always come from
+    lower ranks), alphabets whose first ids lie below or above the small-id table, 20 to 700 merges; random words with
+    homopolymer stretches, one length class (padded, written by the merge kernel) and mixed lengths (ragged), against
+    the queue semantics of the checker."""
+    from dnatok_b200.tables import Specials, TokenizerSpec
+    from dnatok_b200.tokenizer import B200Tokenizer
+    from oracle import oracle
+    rng = np.random.default_rng(1000 + seed)
+    n_sym = int(rng.integers(2, 7))
+    first = int(rng.choice([5, 20, 31, 40, 300]))
+    lut = np.full(256, 1, np.int32)
+    letters = b"ACGTNR"[:n_sym]
+    for i, c in enumerate(letters):
+        lut[c] = first + i
+    tokens = [first + i for i in range(n_sym)]
+    n_merges = int(rng.integers(20, 700))
+    seen, a, b, o = set(), [], [], []
+    nxt = first + n_sym
+    while len(a) < n_merges:
+        # pairs lean towards early tokens, as a trained vocabulary's do
+        x = tokens[int(min(len(tokens) - 1, rng.exponential(len(tokens) / 3)))]
+        y = tokens[int(min(len(tokens) - 1, rng.exponential(len(tokens) / 3)))]
+        if (x, y) in seen:
+            continue
+        seen.add((x, y))
+        a.append(x); b.append(y); o.append(nxt)
+        tokens.append(nxt)
+        nxt += 1
+    a, b, o = (np.array(v, np.int32) for v in (a, b, o))
+    spec = TokenizerSpec("bpe", Specials(0, 1, 2, 3), nxt, lut, merge_a=a, merge_b=b, merge_out=o)
+    tok = B200Tokenizer(spec, device=0)
+    table = oracle.BpeTable(a, b, o)
+
+    def word(n):
+        out = []
+        while len(out) < n:
+            c = letters[int(rng.integers(0, n_sym))]
+            out += [c] * int(rng.choice([1, 1, 1, 2, 3, 7, 40]))
+        return bytes(out[:n])
+
+    # mixed lengths, ragged output
+    words = [word(int(n)) for n in rng.integers(1, 3000, 60)] + [word(1), word(2), word(1024), word(1025)]
+    flat, offs = H.pack_strs(words)
+    enc = run_device(tok, flat, offs, padding=False, add_special_tokens=False)
+    ids, oo = enc["input_ids"].cpu().numpy(), enc["offsets"].cpu().numpy()
+    want = [oracle.bpe_word(table, w, lut) for w in words]
+    for i in range(len(words)):
+        assert ids[oo[i]:oo[i + 1]].tolist() == want[i], (seed, i)
+    # one length class, padded, with special tokens
+    words = [word(int(n)) for n in rng.integers(600, 1025, 300)]
+    flat, offs = H.pack_strs(words)
+    enc = run_device(tok, flat, offs, padding="max_length", max_length=400, truncation=True)
+    ids, lens = enc["input_ids"].cpu().numpy(), enc["lengths"].cpu().numpy()
+    for i, w in enumerate(words):
+        t = oracle.bpe_word(table, w, lut)[:398]
+        assert ids[i, :len(t) + 2].tolist() == [2] + t + [3] and lens[i] == len(t) + 2, (seed, i)
+        assert (ids[i, len(t) + 2:] == 0).all()
+
+
 @pytest.mark.parametrize("name,rows,length,kw", [
     ("char", 8192, 1024, dict(padding="longest")),
     ("kmer6", 4096, 6000, dict(padding="max_length", max_length=1000, truncation=True, add_special_tokens=False)),
