@@ -438,6 +438,73 @@ def test_bpe_table_with_late_created_operands_single_step(bpe_team_mode):
         assert ids[oo[i]:oo[i + 1]].tolist() == oracle.bpe_word(table, w, lut), i
 
 
+@pytest.mark.parametrize("k", [1, 2, 3, 4, 5, 7, 8])
+@pytest.mark.parametrize("shuffled", [False, True])
+def test_kmer_other_window_lengths(k, shuffled):
+    """Every window length the kernels are built for (6 is covered by the benchmark shape), with the table in vocabulary
+    order (ids = base + index, no gather) and shuffled (gather): ragged rows with N runs and lower case, padded with both
+    sides and ragged, large batch (one warp per row) and few long rows (segments), against the checker."""
+    import dataclasses
+    from dnatok_b200.tables import Specials, TokenizerSpec
+    from dnatok_b200.tokenizer import B200Tokenizer
+    from oracle import oracle
+    rng = np.random.default_rng(40 + k)
+    n = 4 ** k
+    kmer_ids = np.arange(10, 10 + n, dtype=np.int32)
+    if shuffled:
+        kmer_ids = kmer_ids[rng.permutation(n)]
+    lut = np.full(256, 1, np.int32)
+    for i, c in enumerate(b"ACGTN"):
+        lut[c] = 4 + i
+    spec = TokenizerSpec("kmer", Specials(0, 1, 2, 3), 10 + n, lut, k=k, kmer_ids=kmer_ids)
+    tok = B200Tokenizer(spec, device=0)
+
+    def rows(lens):
+        out = []
+        for m in lens:
+            r = np.frombuffer(b"ACGT", np.uint8)[rng.integers(0, 4, int(m))].copy()
+            for _ in range(int(m) // 400 + (1 if m and rng.random() < 0.5 else 0)):
+                s0 = int(rng.integers(0, m)); r[s0:s0 + int(rng.integers(1, 30))] = ord("N")
+            if m > 3 and rng.random() < 0.3:
+                r[int(rng.integers(0, m))] = ord("a")
+            out.append(r)
+        flat = np.concatenate(out) if out else np.zeros(0, np.uint8)
+        return flat, np.concatenate([[0], np.cumsum([len(r) for r in out])]).astype(np.int64)
+
+    def check(flat, offs, **kw):
+        ids, counts = oracle.encode_ragged("kmer", flat, offs, lut256=lut, k=k, kmer_ids=kmer_ids, table=None, threads=2)
+        want_rows = oracle.rows(ids, offs, counts)
+        okw = dict(kw)
+        pad_left = okw.pop("pad_left", False)
+        tok.padding_side = "left" if pad_left else "right"
+        try:
+            enc = run_device(tok, flat, offs, **kw_strip(kw))
+        finally:
+            tok.padding_side = "right"
+        if kw.get("padding") is False:
+            got, oo = enc["input_ids"].cpu().numpy(), enc["offsets"].cpu().numpy()
+            for i, w in enumerate(want_rows):
+                assert got[oo[i]:oo[i + 1]].tolist() == list(w), (k, i)
+        else:
+            o_ids, o_mask = oracle.assemble(want_rows, pad_id=0, cls_id=2, sep_id=3, add_special=True,
+                                            max_length=okw.get("max_length", 0), truncation=okw.get("truncation", False),
+                                            padding=okw["padding"], pad_left=pad_left, id_dtype=np.int64, mask_dtype=np.int64)
+            assert np.array_equal(enc["input_ids"].cpu().numpy(), o_ids), k
+            assert np.array_equal(enc["attention_mask"].cpu().numpy(), o_mask), k
+
+    def kw_strip(kw):
+        return {a: b for a, b in kw.items() if a != "pad_left"}
+
+    lens = list(rng.integers(0, 3000, 1500)) + [0, 1, k - 1, k, k + 1, 64 * k, 64 * k + 1, 128 * k - 1, 256 * k, 257 * k + 3]
+    flat, offs = rows(lens)
+    check(flat, offs, padding="max_length", max_length=300, truncation=True)
+    check(flat, offs, padding="longest", pad_left=True)
+    check(flat, offs, padding=False, add_special_tokens=False)
+    flat, offs = rows([70000, 5, 40000 + k, 123457])          # few long rows: the segment encoder
+    check(flat, offs, padding="longest")
+    check(flat, offs, padding="max_length", max_length=5000, truncation=True, pad_left=True)
+
+
 @pytest.mark.parametrize("seed", range(12))
 def test_bpe_random_merge_tables(seed):
     _random_merge_tables(seed)
