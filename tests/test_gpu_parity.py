@@ -931,6 +931,65 @@ def test_dnatok_flags_match_reference_outputs(golden):
             assert ids == case["ids"], tag
 
 
+def test_bpe_padded_encode_without_lengths_or_status():
+    """dnatok_encode for a padded BPE batch writes ids and mask from the merge kernel; the row-length and status arrays
+    are optional there."""
+    import ctypes
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    handle = _cabi.Handle(H.spec("bpe4096"))
+    flat, offs = synth.pack_rows(synth.config3(batch=50, length=700, seed=9))
+    d_b, d_o = dev(flat, offs)
+    B, total, width = 50, len(flat), 200
+    need = L.dnatok_scratch_bytes(handle.ptr, B, total)
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    fmt = _cabi.Format(64, 64, 1, 0, width, width)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    outs = []
+    for with_rows in (True, False):
+        ids = torch.full((B, width), -7, dtype=torch.int64, device="cuda")
+        mask = torch.full((B, width), -7, dtype=torch.int64, device="cuda")
+        lengths = torch.zeros(B, dtype=torch.int32, device="cuda")
+        status = torch.full((B,), 99, dtype=torch.int32, device="cuda")          # not zeroed by the caller
+        _cabi.check(L.dnatok_encode(handle.ptr, p(d_b), p(d_o), B, total, ctypes.byref(fmt), p(ids), p(mask),
+                                    p(lengths) if with_rows else None, None, p(status) if with_rows else None,
+                                    p(scratch), need, None))
+        torch.cuda.synchronize()
+        outs.append((ids, mask))
+        if with_rows:
+            assert status.tolist() == [0] * B
+            assert torch.equal(lengths.to(torch.int64), mask.sum(dim=1))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    o_ids, o_mask = H.oracle_batch("bpe4096", flat, offs, padding="max_length", max_length=width, truncation=True)
+    assert np.array_equal(outs[0][0].cpu().numpy(), o_ids) and np.array_equal(outs[0][1].cpu().numpy(), o_mask)
+
+
+@pytest.mark.parametrize("name", ["char", "byte", "kmer6"])
+def test_status_words_need_no_zeroing_by_the_caller(name):
+    """dnatok_encode leaves every row's status word defined whatever the array held before: 0 for rows that fit,
+    DNATOK_ROW_CLIPPED for rows cut by a stride that no truncation asked for."""
+    import ctypes
+    from dnatok_b200 import _cabi
+    L = _cabi.lib()
+    handle = _cabi.Handle(H.spec(name))
+    rows = ["ACGT" * 10, "ACGTTGCA" * 300, "AC", "", "ACGTNNACGT" * 150]
+    flat, offs = H.pack_strs(rows)
+    d_b, d_o = dev(flat, offs)
+    B, total, width = len(rows), len(flat), 256
+    ids = torch.zeros((B, width), dtype=torch.int64, device="cuda")
+    mask = torch.zeros((B, width), dtype=torch.int64, device="cuda")
+    lengths = torch.zeros(B, dtype=torch.int32, device="cuda")
+    status = torch.full((B,), 0x55, dtype=torch.int32, device="cuda")
+    fmt = _cabi.Format(64, 64, 0, 0, 0, width)                  # no truncation asked for: the stride clips
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    _cabi.check(L.dnatok_encode(handle.ptr, p(d_b), p(d_o), B, total, ctypes.byref(fmt), p(ids), p(mask), p(lengths), None,
+                                p(status), None, 0, None))
+    torch.cuda.synchronize()
+    n_tok = [len(r) for r in H.oracle_rows(name, flat, offs)]
+    assert status.tolist() == [_cabi.ROW_CLIPPED if n > width else 0 for n in n_tok]
+    assert lengths.tolist() == [min(n, width) for n in n_tok]
+
+
 def test_scan_lengths_at_trip_boundaries():
     """dnatok_scan_lengths (row lengths -> ragged output offsets) around its 4,096-row trips, on a 16-byte aligned array
     and on one that is not."""
