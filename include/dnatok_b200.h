@@ -141,7 +141,8 @@ int64_t dnatok_max_tokens(const dnatok_handle* h, int64_t n_rows, int64_t total_
  *   d_out_offsets (int64[n_rows+1], input) gives each row's start; d_mask may be NULL.
  *   d_lengths must come from dnatok_prepare on the same batch, format and scratch.
  * dnatok_encode:  both steps.  Ragged: d_out_offsets is an output (exclusive scan of lengths).
- *   d_lengths and d_status may be NULL for char/k-mer padded output. */
+ *   d_lengths and d_status may be NULL for padded output (for BPE only in dnatok_encode, where the merge kernels write
+ *   the final rows themselves).  d_status needs no zeroing by the caller: every row's word is defined on return. */
 int dnatok_prepare(dnatok_handle* h, const uint8_t* d_bytes, const int64_t* d_offsets,
                    int64_t n_rows, int64_t total_bytes, const dnatok_format* fmt,
                    int32_t* d_lengths, int32_t* d_status, void* d_scratch, size_t scratch_bytes,
