@@ -31,6 +31,24 @@ def test_library_exports_every_declared_symbol():
     assert L.dnatok_version() == 1
 
 
+def test_every_documented_option_is_accepted():
+    """The tuning knobs listed in the header are the ones dnatok_set_option knows (set to their defaults here), and
+    an unknown name is an error."""
+    text = open(os.path.join(ROOT, "include", "dnatok_b200.h")).read()
+    block = text[text.index("Process-wide tuning knobs"):text.index("int dnatok_set_option")]
+    names = re.findall(r'^ \*   "([a-z_]+)"', block, flags=re.M)
+    defaults = {"host_chunk_bytes": 64 << 20, "host_chunk_threshold": 128 << 20, "host_mask_threads": -1, "host_mask_early": 1,
+                "host_mask_min_bytes": 16 << 20, "kmer_force_segments": 0, "kmer_poll_limit": 1 << 20,
+                "kmer_test_withhold_ticket": -1, "kmer_overlap_launch": 1, "emit_overlap_launch": 1, "bpe_team_warps": 0,
+                "bpe_team_max": 8, "bpe_overlap_launch": 1, "bpe_smem_table": 1, "bpe_fused_output": 1, "bpe_mixed_launch": 1,
+                "bpe_block_team_rows": -1}
+    assert sorted(names) == sorted(defaults)
+    L = _cabi.lib()
+    for n in names:
+        assert L.dnatok_set_option(n.encode(), defaults[n]) == 0, n
+    assert L.dnatok_set_option(b"no_such_knob", 1) != 0
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_cabi, "_LIB", None)
     monkeypatch.setattr(_cabi, "LIB_PATH", str(tmp_path / "nope.so"))
